@@ -1,0 +1,381 @@
+"""Python binding of the B200 C ABI (include/aig_b200.h) for tests and benchmarks.
+
+The product is the shared library ``libaig_b200.so`` built from ``csrc/`` and ``host/``; this module
+only loads it with ctypes, declares every entry point's signature, and offers thin helpers that take
+torch CUDA tensors (torch is used for device memory and streams, nothing else).  There is no
+fallback: if the library is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libaig_b200.so")
+
+c_int, c_float, c_size_t, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_size_t, ctypes.c_void_p
+P = c_void_p
+PP = ctypes.POINTER(c_void_p)
+PI = ctypes.POINTER(c_int)
+
+ACT_NONE, ACT_RELU, ACT_SWISH, ACT_LEAKY = 0, 1, 2, 3
+
+
+class ConvDesc(ctypes.Structure):
+    _fields_ = [(n, c_int) for n in ("batch", "in_c", "in_d", "in_h", "in_w", "out_c", "kd", "kh", "kw", "sd", "sh",
+                                     "sw", "pd", "ph", "pw", "act")] + [("slope", c_float), ("two_step", c_int)]
+
+
+# name -> argtypes (restype is int unless listed in _RESTYPES)
+SIGNATURES = {
+    "aig_ctx_create": [PP, c_int],
+    "aig_ctx_destroy": [P],
+    "aig_ctx_set_stream": [P, P],
+    "aig_ctx_stream": [P],
+    "aig_ctx_sync": [P],
+    "aig_last_error": [P],
+    "aig_device_sm_count": [P],
+    "aig_memcpy": [P, P, P, c_size_t],
+    "aig_graph_begin": [P],
+    "aig_graph_end": [P, PP],
+    "aig_graph_launch": [P, P],
+    "aig_graph_destroy": [P],
+    "aig_bgra_to_planar": [P, P, P, c_int],
+    "aig_convert_normalize": [P, P, P, c_size_t],
+    "aig_preprocess_bgra": [P, P, P, c_int, c_int],
+    "aig_unconvert_unnormalize": [P, P, P, c_size_t],
+    "aig_half_to_float": [P, P, P, c_size_t],
+    "aig_float_to_half": [P, P, P, c_size_t],
+    "aig_nchw_to_nhwc": [P, P, P, c_int, c_int, c_int],
+    "aig_nhwc_to_nchw": [P, P, P, c_int, c_int, c_int],
+    "aig_leaky_relu_forward": [P, P, c_int, c_float],
+    "aig_swish_forward": [P, P, c_int],
+    "aig_relu_forward": [P, P, c_int],
+    "aig_sigmoid_forward": [P, P, c_int, c_int, c_int],
+    "aig_tanh_tail_forward": [P, P, c_int, c_int, c_int],
+    "aig_add_forward": [P, P, P, c_int],
+    "aig_batchnorm_forward": [P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_int],
+    "aig_layernorm_forward": [P, P, P, P, P, P, P, c_int, c_int, c_int, c_float],
+    "aig_layernorm_rows_forward": [P, P, P, P, P, c_int, c_int, c_float],
+    "aig_spatial_attention_forward": [P] * 10 + [c_int] * 6,
+    "aig_spatial_mask_forward": [P, P, P, c_float, P, c_int, c_int, c_int],
+    "aig_global_avgpool_nhwc": [P, P, P, c_int, c_int, c_int],
+    "aig_adaptive_avgpool3d_ndhwc": [P, P, P] + [c_int] * 7,
+    "aig_conv_plan_create": [P, ctypes.POINTER(ConvDesc), PP],
+    "aig_conv_plan_destroy": [P],
+    "aig_conv_plan_out_dims": [P, PI, PI, PI],
+    "aig_conv_plan_set_weights": [P, P, P, P, P, P, P, c_float],
+    "aig_conv_forward": [P, P, P, P],
+    "aig_fc_plan_create": [P, c_int, c_int, c_int, c_int, c_float, c_int, PP],
+    "aig_fc_plan_set_weights": [P, P, P, P, P, P, P, c_float],
+    "aig_fc_plan_set_weights_out_in": [P, P, P],
+    "aig_conv0_plan_create": [P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, PP],
+    "aig_conv0_plan_create_3d": [P] + [c_int] * 12 + [c_float, PP],
+    "aig_conv0_plan_destroy": [P],
+    "aig_conv0_plan_out_dims": [P, PI, PI, PI],
+    "aig_conv0_plan_set_weights": [P, P, P, P, P, P, P, c_float],
+    "aig_conv0_forward_bgra": [P, P, P],
+    "aig_conv0_forward_nchw": [P, P, P],
+    "aig_actions_from_outputs": [P, P, c_int, c_int, c_int],
+}
+AIG_CNN_MAX_BLOCKS = 7
+
+
+class CnnConfig(ctypes.Structure):
+    _fields_ = [("batch", c_int), ("height", c_int), ("width", c_int), ("n_blocks", c_int),
+                ("widths", c_int * (AIG_CNN_MAX_BLOCKS + 1)), ("k0", c_int), ("n_out", c_int), ("n_sigmoid", c_int),
+                ("act", c_int), ("slope", c_float)]
+
+
+SIGNATURES.update({
+    "aig_cnn_create": [P, ctypes.POINTER(CnnConfig), PP],
+    "aig_cnn_destroy": [P],
+    "aig_cnn_last_error": [P],
+    "aig_cnn_checkpoint_bytes": [ctypes.POINTER(CnnConfig)],
+    "aig_cnn_load_memory": [P, P, c_size_t],
+    "aig_cnn_load_file": [P, ctypes.c_char_p],
+    "aig_cnn_forward": [P, P],
+    "aig_cnn_forward_graph": [P, P],
+    "aig_cnn_infer_host": [P, P, P],
+    "aig_cnn_outputs_half": [P],
+    "aig_cnn_outputs_f32": [P],
+    "aig_cnn_features": [P],
+    "aig_cnn_stage_output": [P, c_int, PI, PI, PI],
+    "aig_cnn_kernel_launches": [P],
+    "aig_cnn_profile_begin": [P, c_int],
+    "aig_cnn_profile_end": [P, ctypes.POINTER(ctypes.c_double), c_int, PI],
+    "aig_cnn_site_count": [P],
+    "aig_cnn_site_name": [P, c_int],
+    "aig_cnn_site_flops": [P, c_int],
+    "aig_cnn_site_bytes": [P, c_int],
+})
+_RESTYPES = {"aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
+             "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
+             "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
+             "aig_cnn_site_flops": ctypes.c_double, "aig_cnn_site_bytes": ctypes.c_double}
+
+_lib = None
+
+
+class AigError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("aig_b200 error %d: %s" % (code, msg))
+        self.code = code
+
+
+def lib():
+    """Load libaig_b200.so (fails loudly when it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                "libaig_b200.so is missing: build it with `python ai-gamer_b200/build.py` "
+                "(there is no fallback implementation)")
+        _lib = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.argtypes = args
+            fn.restype = _RESTYPES.get(name, c_int)
+    return _lib
+
+
+def ptr(t):
+    """Device (or host) address of a torch tensor / numpy array / None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return c_void_p(t.data_ptr())
+    return c_void_p(t.ctypes.data)
+
+
+class Context:
+    """One device + one stream (aig_ctx).  By default it adopts torch's current CUDA stream so that
+    calls interleave correctly with torch allocations and copies."""
+
+    def __init__(self, device=0, use_torch_stream=True):
+        self.handle = c_void_p()
+        rc = lib().aig_ctx_create(ctypes.byref(self.handle), device)
+        if rc != 0:
+            raise AigError(rc, lib().aig_last_error(None).decode())
+        self.device = device
+        if use_torch_stream:
+            import torch
+
+            self.set_stream(torch.cuda.current_stream(device).cuda_stream)
+
+    def check(self, rc):
+        if rc != 0:
+            raise AigError(rc, lib().aig_last_error(self.handle).decode())
+
+    def call(self, name, *args):
+        self.check(getattr(lib(), name)(self.handle, *args))
+
+    def set_stream(self, cuda_stream):
+        self.check(lib().aig_ctx_set_stream(self.handle, c_void_p(cuda_stream)))
+
+    def sync(self):
+        self.check(lib().aig_ctx_sync(self.handle))
+
+    @property
+    def sm_count(self):
+        return lib().aig_device_sm_count(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib().aig_ctx_destroy(self.handle)
+            self.handle = c_void_p()
+
+    # -- CUDA graph of the frame loop
+    def graph_begin(self):
+        self.check(lib().aig_graph_begin(self.handle))
+
+    def graph_end(self):
+        g = c_void_p()
+        self.check(lib().aig_graph_end(self.handle, ctypes.byref(g)))
+        return g
+
+    def graph_launch(self, g):
+        self.check(lib().aig_graph_launch(self.handle, g))
+
+
+class _Plan:
+    _destroy = None
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self.handle = c_void_p()
+        self._keep = []
+
+    def check(self, rc):
+        self.ctx.check(rc)
+
+    def close(self):
+        if self.handle:
+            getattr(lib(), self._destroy)(self.handle)
+            self.handle = c_void_p()
+
+    def out_dims(self):
+        d, h, w = c_int(), c_int(), c_int()
+        getattr(lib(), self._dims)(self.handle, ctypes.byref(d), ctypes.byref(h), ctypes.byref(w))
+        return d.value, h.value, w.value
+
+
+class ConvPlan(_Plan):
+    """aig_conv_plan: tcgen05 implicit-GEMM convolution on channels-last tensors."""
+    _destroy = "aig_conv_plan_destroy"
+    _dims = "aig_conv_plan_out_dims"
+
+    def __init__(self, ctx, batch, in_c, in_h, in_w, out_c, k, stride, pad, act=ACT_NONE, slope=0.01, two_step=False,
+                 in_d=1, kd=1, sd=1, pd=0):
+        super().__init__(ctx)
+        self.desc = ConvDesc(batch, in_c, in_d, in_h, in_w, out_c, kd, k, k, sd, stride, stride, pd, pad, pad, act, slope,
+                             1 if two_step else 0)
+        self.check(lib().aig_conv_plan_create(ctx.handle, ctypes.byref(self.desc), ctypes.byref(self.handle)))
+
+    def set_weights(self, w, bias, bn=None, eps=1e-6):
+        g, b, m, v = bn if bn is not None else (None, None, None, None)
+        self._keep = [w, bias, g, b, m, v]
+        self.check(lib().aig_conv_plan_set_weights(self.handle, ptr(w), ptr(bias), ptr(g), ptr(b), ptr(m), ptr(v), eps))
+
+    def forward(self, x, y, residual=None):
+        self.check(lib().aig_conv_forward(self.handle, ptr(x), ptr(residual), ptr(y)))
+        return y
+
+
+class FcPlan(_Plan):
+    """aig_fc_plan_*: the same kernel as ConvPlan on a [rows][in_c] matrix."""
+    _destroy = "aig_conv_plan_destroy"
+    _dims = "aig_conv_plan_out_dims"
+
+    def __init__(self, ctx, rows, in_c, out_c, act=ACT_NONE, slope=0.01, two_step=False):
+        super().__init__(ctx)
+        self.check(lib().aig_fc_plan_create(ctx.handle, rows, in_c, out_c, act, slope, 1 if two_step else 0,
+                                            ctypes.byref(self.handle)))
+
+    def set_weights(self, w_in_out, bias, bn=None, eps=1e-6):
+        g, b, m, v = bn if bn is not None else (None, None, None, None)
+        self.check(lib().aig_fc_plan_set_weights(self.handle, ptr(w_in_out), ptr(bias), ptr(g), ptr(b), ptr(m), ptr(v), eps))
+
+    def set_weights_out_in(self, w_out_in, bias):
+        self.check(lib().aig_fc_plan_set_weights_out_in(self.handle, ptr(w_out_in), ptr(bias)))
+
+    def forward(self, x, y, residual=None):
+        self.check(lib().aig_conv_forward(self.handle, ptr(x), ptr(residual), ptr(y)))
+        return y
+
+
+class Conv0Plan(_Plan):
+    """aig_conv0_plan: first-layer (3-channel) convolution with fused input conversion."""
+    _destroy = "aig_conv0_plan_destroy"
+    _dims = "aig_conv0_plan_out_dims"
+
+    def __init__(self, ctx, batch, in_h, in_w, out_c, k, stride, pad, act=ACT_NONE, slope=0.01, in_d=None, kd=1, sd=1, pd=0):
+        super().__init__(ctx)
+        if in_d is None:
+            self.check(lib().aig_conv0_plan_create(ctx.handle, batch, in_h, in_w, out_c, k, stride, pad, act, slope,
+                                                   ctypes.byref(self.handle)))
+        else:
+            self.check(lib().aig_conv0_plan_create_3d(ctx.handle, batch, in_d, in_h, in_w, out_c, kd, k, sd, stride, pd, pad,
+                                                      act, slope, ctypes.byref(self.handle)))
+
+    def set_weights(self, w, bias, bn=None, eps=1e-6):
+        g, b, m, v = bn if bn is not None else (None, None, None, None)
+        self.check(lib().aig_conv0_plan_set_weights(self.handle, ptr(w), ptr(bias), ptr(g), ptr(b), ptr(m), ptr(v), eps))
+
+    def forward_bgra(self, bgra, y):
+        self.check(lib().aig_conv0_forward_bgra(self.handle, ptr(bgra), ptr(y)))
+        return y
+
+    def forward_nchw(self, x, y):
+        self.check(lib().aig_conv0_forward_nchw(self.handle, ptr(x), ptr(y)))
+        return y
+
+
+class CnnEncoder:
+    """aig_cnn: the 2-D frame encoder (host C++ runner over the kernel ABI)."""
+
+    def __init__(self, ctx, batch, height, width, widths=(32, 64, 128, 256, 256), k0=5, n_out=18, n_sigmoid=16,
+                 act=ACT_SWISH, slope=0.01):
+        self.ctx = ctx
+        w = (c_int * (AIG_CNN_MAX_BLOCKS + 1))(*widths)
+        self.cfg = CnnConfig(batch, height, width, len(widths) - 1, w, k0, n_out, n_sigmoid, act, slope)
+        self.handle = c_void_p()
+        rc = lib().aig_cnn_create(ctx.handle, ctypes.byref(self.cfg), ctypes.byref(self.handle))
+        if rc != 0:
+            raise AigError(rc, lib().aig_last_error(ctx.handle).decode())
+        self.widths = tuple(widths)
+
+    def check(self, rc):
+        if rc != 0:
+            raise AigError(rc, lib().aig_cnn_last_error(self.handle).decode())
+
+    def checkpoint_bytes(self):
+        return lib().aig_cnn_checkpoint_bytes(ctypes.byref(self.cfg))
+
+    def load_bytes(self, blob):
+        buf = (ctypes.c_char * len(blob)).from_buffer_copy(blob)
+        self.check(lib().aig_cnn_load_memory(self.handle, ctypes.cast(buf, c_void_p), len(blob)))
+
+    def load_file(self, path):
+        self.check(lib().aig_cnn_load_file(self.handle, path.encode()))
+
+    def forward(self, bgra_dev, graph=False):
+        fn = lib().aig_cnn_forward_graph if graph else lib().aig_cnn_forward
+        self.check(fn(self.handle, ptr(bgra_dev)))
+
+    def infer_host(self, bgra_host, out_host):
+        self.check(lib().aig_cnn_infer_host(self.handle, ptr(bgra_host), ptr(out_host)))
+
+    def _view(self, addr, shape, dtype):
+        import torch
+
+        n = 1
+        for s in shape:
+            n *= s
+        out = torch.empty(shape, dtype=dtype, device="cuda:%d" % self.ctx.device)
+        esz = out.element_size()
+        self.ctx.call("aig_memcpy", c_void_p(out.data_ptr()), c_void_p(addr), n * esz)
+        self.ctx.sync()
+        return out
+
+    def outputs_half(self):
+        import torch
+
+        return self._view(lib().aig_cnn_outputs_half(self.handle), (self.cfg.batch, self.cfg.n_out), torch.float16)
+
+    def outputs_f32(self):
+        import torch
+
+        return self._view(lib().aig_cnn_outputs_f32(self.handle), (self.cfg.batch, self.cfg.n_out), torch.float32)
+
+    def features(self):
+        import torch
+
+        return self._view(lib().aig_cnn_features(self.handle), (self.cfg.batch, self.widths[-1]), torch.float16)
+
+    def stage_output(self, stage):
+        import torch
+
+        h, w, c = c_int(), c_int(), c_int()
+        addr = lib().aig_cnn_stage_output(self.handle, stage, ctypes.byref(h), ctypes.byref(w), ctypes.byref(c))
+        return self._view(addr, (self.cfg.batch, h.value, w.value, c.value), torch.float16)
+
+    @property
+    def kernel_launches(self):
+        return lib().aig_cnn_kernel_launches(self.handle)
+
+    def profile_begin(self, max_steps):
+        self.check(lib().aig_cnn_profile_begin(self.handle, max_steps))
+
+    def profile_end(self):
+        """[(site name, mean ms, algorithmic flops, algorithmic bytes)], steps recorded."""
+        n = lib().aig_cnn_site_count(self.handle)
+        ms = (ctypes.c_double * n)()
+        steps = c_int()
+        self.check(lib().aig_cnn_profile_end(self.handle, ms, n, ctypes.byref(steps)))
+        rows = [(lib().aig_cnn_site_name(self.handle, i).decode(), ms[i], lib().aig_cnn_site_flops(self.handle, i),
+                 lib().aig_cnn_site_bytes(self.handle, i)) for i in range(n)]
+        return rows, steps.value
+
+    def close(self):
+        if self.handle:
+            lib().aig_cnn_destroy(self.handle)
+            self.handle = c_void_p()

@@ -1,0 +1,613 @@
+// igemm_tcgen05.cu -- convolution (2-D / 3-D) and fully-connected forward as one implicit-GEMM
+// kernel for sm_100a: operands staged in shared memory by TMA (tiled mode, 128/64/32-byte swizzle),
+// tcgen05.mma with fp32 accumulators in TMEM (double buffered), fused epilogue
+// (bias + folded BatchNorm, residual add, ReLU/Swish/LeakyReLU, fp16 channels-last store).
+//
+// GEMM view: M = output pixels (batch*Do*Ho*Wo), N = output channels, K = taps * input channels.
+//   A (M x K): never materialised.  The input is channels-last [N][D][H][W][C]; for one filter tap and
+//     one block of BK channels, the rows of an M tile are `segs` runs of `tw` consecutive output
+//     pixels of one output row (tw*segs = 128); each run is one TMA box (BK channels x tw pixels,
+//     element stride = conv stride) whose out-of-range pixels (padding) are zero-filled by TMA.
+//   B (N x K): weights repacked once to [out_c][tap][in_c] (K-major), one TMA box per K block.
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
+// Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all
+// roles drain to the common exit where TMEM is freed.
+#include <vector>
+
+#include "aig_common.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kNumThreads = 192;
+constexpr int kMaxSegs = 16;
+
+struct IgemmParams {
+  int num_kb, cblocks, taps_hw, kw;           // K loop: kb -> (tap, cblock); tap -> (fd, fr, fs)
+  int sd, sh, sw, pd, ph, pw;
+  int DoHo, Ho, Wo;
+  int tw, segs, segs_per_row, total_rows;
+  int m_tiles, n_tiles;
+  int out_c;
+  int act, two_step;
+  float slope;
+  const float* scale;
+  const float* shift;
+  const __half* residual;
+  __half* y;
+  int* gerr;
+};
+
+template <int NT, int BK>
+struct IgemmCfg {
+  static constexpr int kABytes = kTileM * BK * 2;
+  static constexpr int kBBytes = NT * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*scale,shift*/ + 256 /*barriers*/;
+};
+
+template <int NT, int BK>
+__global__ void __launch_bounds__(kNumThreads, 1)
+igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const IgemmParams p) {
+  using Cfg = IgemmCfg<NT, BK>;
+  constexpr int kStages = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  const uint32_t sA = base;
+  const uint32_t sB = base + kStages * Cfg::kABytes;
+  float* s_scale = reinterpret_cast<float*>(sm + kStages * Cfg::kStageBytes);
+  float* s_shift = s_scale + 256;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kStages * Cfg::kStageBytes + 2048);
+  const uint32_t bar_full = smem_u32(bars);                    // [kStages]
+  const uint32_t bar_empty = bar_full + 8 * kStages;           // [kStages]
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;          // [2]
+  const uint32_t bar_tempty = bar_tfull + 16;                  // [2]
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (p.n_tiles == 1) {
+    for (int i = threadIdx.x; i < NT; i += kNumThreads) {
+      s_scale[i] = p.scale[i];
+      s_shift[i] = p.shift[i];
+    }
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 4);
+    }
+    *s_abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmapA);
+    tma_prefetch_desc(&tmapB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(s_tmem), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int n_tile = tile % p.n_tiles, m_tile = tile / p.n_tiles;
+        int seg_n[kMaxSegs], seg_z[kMaxSegs], seg_y[kMaxSegs], seg_x[kMaxSegs];
+        for (int s = 0; s < p.segs; ++s) {
+          const int g = m_tile * p.segs + s;
+          const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
+          const int n = row / p.DoHo, r2 = row - n * p.DoHo;
+          const int od = r2 / p.Ho, oh = r2 - od * p.Ho;
+          seg_n[s] = n;  // rows past the end give n >= batch: the box is out of range, filled with zeros
+          seg_z[s] = od * p.sd - p.pd;
+          seg_y[s] = oh * p.sh - p.ph;
+          seg_x[s] = wseg * p.tw * p.sw - p.pw;
+        }
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
+          const int fd = tap / p.taps_hw, rem = tap - fd * p.taps_hw;
+          const int fr = rem / p.kw, fs = rem - fr * p.kw;
+          if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, s_abort, p.gerr, 101)) { ok = false; break; }
+          mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
+          const uint32_t a_dst = sA + stage * Cfg::kABytes;
+          for (int s = 0; s < p.segs; ++s)
+            tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
+                        seg_z[s] + fd, seg_n[s]);
+          tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 201)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait_bounded(bar_full + 8 * stage, phase, s_abort, p.gerr, 202)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a0 = sA + stage * Cfg::kABytes, b0 = sB + stage * Cfg::kBBytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = umma_smem_desc(a0 + k * 32, BK * 2);
+            const uint64_t bdesc = umma_smem_desc(b0 + k * 32, BK * 2);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    const bool vec_ok = (p.out_c & 7) == 0;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int n_tile = tile % p.n_tiles, m_tile = tile / p.n_tiles;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      // scale/shift: staged in shared memory when there is a single N tile, else read from global
+      const float* sc = p.n_tiles == 1 ? s_scale : p.scale + n_tile * NT;
+      const float* sf = p.n_tiles == 1 ? s_shift : p.shift + n_tile * NT;
+      // which output pixel this TMEM lane holds
+      const int seg = row_in_tile / p.tw, j = row_in_tile - seg * p.tw;
+      const int g = m_tile * p.segs + seg;
+      const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
+      const int wo = wseg * p.tw + j;
+      const bool valid = row < p.total_rows && wo < p.Wo;
+      const size_t pix = (size_t)row * p.Wo + wo;
+      __half* yrow = p.y + pix * p.out_c;
+      const __half* rrow = p.residual ? p.residual + pix * p.out_c : nullptr;
+
+      if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 301)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t)(acc * NT) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < NT; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c0, r);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int v8 = 0; v8 < 4; ++v8) {
+            const int nl = c0 + v8 * 8;           // column inside the N tile
+            const int n = n_tile * NT + nl;       // output channel
+            if (n >= p.out_c) break;
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float a = __uint_as_float(r[v8 * 8 + e]);
+              if (p.two_step) {
+                a = __half2float(__float2half(a));
+                a = __half2float(__float2half(a + sf[nl + e]));  // shift == bias: no BatchNorm in this mode
+              } else {
+                a = a * sc[nl + e] + sf[nl + e];
+              }
+              v[e] = a;
+            }
+            if (vec_ok) {
+              if (rrow) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + n);
+                const __half* rh = reinterpret_cast<const __half*>(&rv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)  // the add stores fp16 before the activation (ResConvLayer.cpp:35-36)
+                  v[e] = __half2float(__float2half(__half2float(__float2half(v[e])) + __half2float(rh[e])));
+              }
+              uint4 o;
+              __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) oh[e] = __float2half(act_apply(v[e], p.act, p.slope));
+              *reinterpret_cast<uint4*>(yrow + n) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                if (n + e < p.out_c) {
+                  float a = v[e];
+                  if (rrow) a = __half2float(__float2half(__half2float(__float2half(a)) + __half2float(rrow[n + e])));
+                  yrow[n + e] = __float2half(act_apply(a, p.act, p.slope));
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+    }
+  }
+
+  // ------------------------------------------------------------------ common exit
+  if (*s_abort) {
+    // give copies / MMAs still in flight time to land before shared memory and TMEM go away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Weight repack / epilogue-parameter kernels (run once per LoadParameters).
+__global__ void repack_kcx_kernel(const __half* __restrict__ w, __half* __restrict__ packed, int K, int C, int taps) {
+  // w [K][C][taps] -> packed [k][tap*C + c]
+  const long long total = (long long)K * C * taps;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const long long r = i / C;
+    const int tap = (int)(r % taps), k = (int)(r / taps);
+    packed[i] = w[((size_t)k * C + c) * taps + tap];
+  }
+}
+__global__ void repack_fc_kernel(const __half* __restrict__ w_in_out, __half* __restrict__ packed, int inC, int outC) {
+  const long long total = (long long)inC * outC;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i % inC), o = (int)(i / inC);
+    packed[i] = w_in_out[(size_t)k * outC + o];
+  }
+}
+__global__ void fold_affine_kernel(float* scale, float* shift, __half* bias_out, const __half* bias, const float* gamma,
+                                   const float* beta, const float* mean, const float* var, float eps, int K, int Kpad) {
+  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < Kpad; k += gridDim.x * blockDim.x) {
+    float s = 0.f, t = 0.f, b = 0.f;
+    if (k < K) {
+      b = bias ? __half2float(bias[k]) : 0.f;
+      if (gamma) {
+        s = gamma[k] / sqrtf(var[k] + eps);
+        t = (b - mean[k]) * s + beta[k];
+      } else {
+        s = 1.f;
+        t = b;
+      }
+    }
+    scale[k] = s;
+    shift[k] = t;
+    bias_out[k] = __float2half(b);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+struct aig_conv_plan {
+  aig_ctx* ctx = nullptr;
+  aig_conv_desc d{};
+  int Do = 1, Ho = 1, Wo = 1;
+  bool is_fc = false;
+  int BK = 64, NT = 64, Kpad = 0, taps = 1, Ktot = 0;
+  IgemmParams prm{};
+  __half* w_packed = nullptr;
+  float* scale = nullptr;
+  float* shift = nullptr;
+  __half* bias_h = nullptr;
+  bool weights_set = false;
+  CUtensorMap tmapA{}, tmapB{};
+  const void* tmapA_ptr = nullptr;
+  int grid = 1;
+  size_t smem = 0;
+};
+
+namespace {
+
+template <int NT, int BK>
+int launch_igemm(aig_conv_plan* pl) {
+  using Cfg = IgemmCfg<NT, BK>;
+  static bool attr_set[64] = {};
+  aig_ctx* ctx = pl->ctx;
+  if (!attr_set[ctx->device & 63]) {
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(igemm_kernel<NT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[ctx->device & 63] = true;
+  }
+  igemm_kernel<NT, BK><<<pl->grid, kNumThreads, Cfg::kSmemBytes, ctx->stream>>>(pl->tmapA, pl->tmapB, pl->prm);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+template <int NT>
+int dispatch_bk(aig_conv_plan* pl) {
+  switch (pl->BK) {
+    case 64: return launch_igemm<NT, 64>(pl);
+    case 32: return launch_igemm<NT, 32>(pl);
+    case 16: return launch_igemm<NT, 16>(pl);
+  }
+  return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "igemm: unsupported BK %d", pl->BK);
+}
+
+int dispatch(aig_conv_plan* pl) {
+  switch (pl->NT) {
+    case 32: return dispatch_bk<32>(pl);
+    case 64: return dispatch_bk<64>(pl);
+    case 128: return dispatch_bk<128>(pl);
+    case 256: return dispatch_bk<256>(pl);
+  }
+  return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "igemm: unsupported NT %d", pl->NT);
+}
+
+CUtensorMapSwizzle swizzle_for(int bk) {
+  return bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+int encode_B(aig_conv_plan* pl) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {(cuuint64_t)pl->Ktot, (cuuint64_t)pl->Kpad};
+  cuuint64_t strides[1] = {(cuuint64_t)pl->Ktot * 2};
+  cuuint32_t box[2] = {(cuuint32_t)pl->BK, (cuuint32_t)pl->NT};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&pl->tmapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pl->w_packed, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(pl->BK), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed: %d", (int)r);
+  return AIG_OK;
+}
+
+int encode_A(aig_conv_plan* pl, const void* x) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const aig_conv_desc& d = pl->d;
+  cuuint64_t C = d.in_c, W = d.in_w, H = d.in_h, D = d.in_d, N = d.batch;
+  cuuint64_t dims[5] = {C, W, H, D, N};
+  cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, D * H * W * C * 2};
+  cuuint32_t box[5] = {(cuuint32_t)pl->BK, (cuuint32_t)(pl->prm.tw * d.sw), 1, 1, 1};
+  cuuint32_t estr[5] = {1, (cuuint32_t)d.sw, 1, 1, 1};
+  CUresult r = enc(&pl->tmapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(pl->BK), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed: %d", (int)r);
+  pl->tmapA_ptr = x;
+  return AIG_OK;
+}
+
+int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
+  const aig_conv_desc& d = pl->d;
+  // K blocking: the largest of 64/32/16 channels that divides in_c
+  if (d.in_c % 64 == 0) pl->BK = 64;
+  else if (d.in_c % 32 == 0) pl->BK = 32;
+  else if (d.in_c % 16 == 0) pl->BK = 16;
+  else return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "igemm needs in_c %% 16 == 0 (got %d); 3-channel inputs use the conv0 plans", d.in_c);
+  pl->taps = d.kd * d.kh * d.kw;
+  pl->Ktot = pl->taps * d.in_c;
+  // N tile: whole out_c when it fits one tile, else 256/128 wide tiles
+  if (d.out_c <= 32) pl->NT = 32;
+  else if (d.out_c <= 64) pl->NT = 64;
+  else if (d.out_c <= 128) pl->NT = 128;
+  else pl->NT = 256;
+  // keep (NT=256,BK=64) from exceeding shared memory: 4 stages of 48 KB fit
+  pl->Kpad = ceil_div(d.out_c, pl->NT) * pl->NT;
+  // M tiling: runs of tw output pixels along W; tw in {8..128} minimising padding, ties -> larger tw
+  int best_tw = 8;
+  long long best_cost = -1;
+  for (int tw = 8; tw <= 128; tw *= 2) {
+    if (tw * d.sw > 256) break;
+    const long long cost = (long long)ceil_div(pl->Wo, tw) * tw;
+    if (best_cost < 0 || cost <= best_cost) {
+      best_cost = cost;
+      best_tw = tw;
+    }
+  }
+  IgemmParams& p = pl->prm;
+  p.tw = best_tw;
+  p.segs = kTileM / best_tw;
+  p.segs_per_row = ceil_div(pl->Wo, best_tw);
+  p.total_rows = d.batch * pl->Do * pl->Ho;
+  const long long total_segs = (long long)p.total_rows * p.segs_per_row;
+  p.m_tiles = (int)ceil_div_ll(total_segs, p.segs);
+  p.n_tiles = pl->Kpad / pl->NT;
+  p.cblocks = d.in_c / pl->BK;
+  p.num_kb = pl->taps * p.cblocks;
+  p.taps_hw = d.kh * d.kw;
+  p.kw = d.kw;
+  p.sd = d.sd; p.sh = d.sh; p.sw = d.sw;
+  p.pd = d.pd; p.ph = d.ph; p.pw = d.pw;
+  p.DoHo = pl->Do * pl->Ho;
+  p.Ho = pl->Ho;
+  p.Wo = pl->Wo;
+  p.out_c = d.out_c;
+  p.act = d.act;
+  p.slope = d.slope;
+  p.two_step = d.two_step;
+  p.gerr = ctx->d_err;
+  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  pl->grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  if (pl->grid < 1) pl->grid = 1;
+  AIG_CUDA_OK(ctx, cudaMalloc(&pl->w_packed, (size_t)pl->Kpad * pl->Ktot * sizeof(__half)));
+  AIG_CUDA_OK(ctx, cudaMemsetAsync(pl->w_packed, 0, (size_t)pl->Kpad * pl->Ktot * sizeof(__half), ctx->stream));
+  AIG_CUDA_OK(ctx, cudaMalloc(&pl->scale, pl->Kpad * sizeof(float)));
+  AIG_CUDA_OK(ctx, cudaMalloc(&pl->shift, pl->Kpad * sizeof(float)));
+  AIG_CUDA_OK(ctx, cudaMalloc(&pl->bias_h, pl->Kpad * sizeof(__half)));
+  p.scale = pl->scale;
+  p.shift = pl->shift;
+  return encode_B(pl);
+}
+
+int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const float* b, const float* m, const float* v,
+               float eps) {
+  aig_ctx* ctx = pl->ctx;
+  if (pl->d.two_step && g) return aig_fail(ctx, AIG_ERR_INVALID, "two_step plans reproduce conv+bias only; BatchNorm cannot be folded");
+  if (g && !(b && m && v)) return aig_fail(ctx, AIG_ERR_INVALID, "BatchNorm needs gamma, beta, mean and var");
+  fold_affine_kernel<<<ceil_div(pl->Kpad, 128), 128, 0, ctx->stream>>>(pl->scale, pl->shift, pl->bias_h, (const __half*)bias,
+                                                                        g, b, m, v, eps, pl->d.out_c, pl->Kpad);
+  AIG_LAUNCH_OK(ctx);
+  pl->weights_set = true;
+  return AIG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int aig_conv_plan_create(aig_ctx* ctx, const aig_conv_desc* desc, aig_conv_plan** out) {
+  if (!ctx || !desc || !out) return AIG_ERR_INVALID;
+  *out = nullptr;
+  DeviceGuard g(ctx->device);
+  const aig_conv_desc& d = *desc;
+  AIG_REQUIRE(ctx, d.batch > 0 && d.in_c > 0 && d.in_d > 0 && d.in_h > 0 && d.in_w > 0 && d.out_c > 0, "conv plan: bad extents");
+  AIG_REQUIRE(ctx, d.kd > 0 && d.kh > 0 && d.kw > 0 && d.sd > 0 && d.sh > 0 && d.sw > 0 && d.pd >= 0 && d.ph >= 0 && d.pw >= 0,
+              "conv plan: bad filter geometry");
+  AIG_REQUIRE(ctx, d.sw <= 8, "conv plan: stride along W above 8 is not supported by the TMA traversal stride");
+  AIG_REQUIRE(ctx, d.in_d + 2 * d.pd >= d.kd && d.in_h + 2 * d.ph >= d.kh && d.in_w + 2 * d.pw >= d.kw, "conv plan: filter larger than padded input");
+  aig_conv_plan* pl = new aig_conv_plan();
+  pl->ctx = ctx;
+  pl->d = d;
+  pl->Do = (d.in_d + 2 * d.pd - d.kd) / d.sd + 1;
+  pl->Ho = (d.in_h + 2 * d.ph - d.kh) / d.sh + 1;
+  pl->Wo = (d.in_w + 2 * d.pw - d.kw) / d.sw + 1;
+  const int rc = plan_finish(ctx, pl);
+  if (rc != AIG_OK) {
+    aig_conv_plan_destroy(pl);
+    return rc;
+  }
+  *out = pl;
+  return AIG_OK;
+}
+
+int aig_conv_plan_destroy(aig_conv_plan* pl) {
+  if (!pl) return AIG_OK;
+  DeviceGuard g(pl->ctx->device);
+  cudaStreamSynchronize(pl->ctx->stream);
+  cudaFree(pl->w_packed);
+  cudaFree(pl->scale);
+  cudaFree(pl->shift);
+  cudaFree(pl->bias_h);
+  delete pl;
+  return AIG_OK;
+}
+
+int aig_conv_plan_out_dims(const aig_conv_plan* pl, int* od, int* oh, int* ow) {
+  if (!pl) return AIG_ERR_INVALID;
+  if (od) *od = pl->Do;
+  if (oh) *oh = pl->Ho;
+  if (ow) *ow = pl->Wo;
+  return AIG_OK;
+}
+
+int aig_conv_plan_set_weights(aig_conv_plan* pl, const aig_half* w, const aig_half* bias, const float* bn_gamma,
+                              const float* bn_beta, const float* bn_mean, const float* bn_var, float bn_eps) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, w != nullptr, "conv set_weights: null weights");
+  AIG_REQUIRE(ctx, !pl->is_fc, "conv set_weights called on an FC plan");
+  const long long total = (long long)pl->d.out_c * pl->Ktot;
+  long long blocks = ceil_div_ll(total, 256);
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  repack_kcx_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const __half*)w, pl->w_packed, pl->d.out_c, pl->d.in_c, pl->taps);
+  AIG_LAUNCH_OK(ctx);
+  return set_affine(pl, bias, bn_gamma, bn_beta, bn_mean, bn_var, bn_eps);
+}
+
+int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* residual, aig_half* y) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, x && y, "conv forward: null pointer");
+  AIG_REQUIRE(ctx, pl->weights_set, "conv forward: weights not set");
+  AIG_REQUIRE(ctx, ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)residual & 15) == 0,
+              "conv forward: tensors must be 16-byte aligned");
+  if (pl->tmapA_ptr != x) {
+    const int rc = encode_A(pl, x);
+    if (rc != AIG_OK) return rc;
+  }
+  pl->prm.residual = (const __half*)residual;
+  pl->prm.y = (__half*)y;
+  return dispatch(pl);
+}
+
+int aig_fc_plan_create(aig_ctx* ctx, int rows, int in_c, int out_c, int act, float slope, int two_step, aig_conv_plan** out) {
+  if (!ctx || !out) return AIG_ERR_INVALID;
+  *out = nullptr;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, rows > 0 && in_c > 0 && out_c > 0, "fc plan: bad extents");
+  aig_conv_plan* pl = new aig_conv_plan();
+  pl->ctx = ctx;
+  pl->is_fc = true;
+  aig_conv_desc d{};
+  d.batch = 1; d.in_c = in_c; d.in_d = 1; d.in_h = 1; d.in_w = rows; d.out_c = out_c;
+  d.kd = d.kh = d.kw = 1; d.sd = d.sh = d.sw = 1; d.pd = d.ph = d.pw = 0;
+  d.act = act; d.slope = slope; d.two_step = two_step;
+  pl->d = d;
+  pl->Do = 1; pl->Ho = 1; pl->Wo = rows;
+  const int rc = plan_finish(ctx, pl);
+  if (rc != AIG_OK) {
+    aig_conv_plan_destroy(pl);
+    return rc;
+  }
+  *out = pl;
+  return AIG_OK;
+}
+
+int aig_fc_plan_set_weights(aig_conv_plan* pl, const aig_half* w_in_out, const aig_half* bias, const float* bn_gamma,
+                            const float* bn_beta, const float* bn_mean, const float* bn_var, float bn_eps) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, w_in_out != nullptr && pl->is_fc, "fc set_weights: bad arguments");
+  const long long total = (long long)pl->d.out_c * pl->d.in_c;
+  long long blocks = ceil_div_ll(total, 256);
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  repack_fc_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const __half*)w_in_out, pl->w_packed, pl->d.in_c, pl->d.out_c);
+  AIG_LAUNCH_OK(ctx);
+  return set_affine(pl, bias, bn_gamma, bn_beta, bn_mean, bn_var, bn_eps);
+}
+
+int aig_fc_plan_set_weights_out_in(aig_conv_plan* pl, const aig_half* w_out_in, const aig_half* bias) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, w_out_in != nullptr && pl->is_fc, "fc set_weights_out_in: bad arguments");
+  AIG_CUDA_OK(ctx, cudaMemcpyAsync(pl->w_packed, w_out_in, (size_t)pl->d.out_c * pl->d.in_c * sizeof(__half),
+                                   cudaMemcpyDeviceToDevice, ctx->stream));
+  return set_affine(pl, bias, nullptr, nullptr, nullptr, nullptr, 0.f);
+}
+
+}  // extern "C"

@@ -1,0 +1,211 @@
+/* aig_b200.h -- C ABI of the B200 (sm_100a) implementation of AI-gamer's frame->action forward path.
+ *
+ * Everything here is `extern "C"`, takes plain pointers and sizes, and returns an int status
+ * (0 = AIG_OK, negative = error; `aig_last_error` gives the text).  Device pointers are raw CUDA
+ * device addresses; fp16 tensors are `uint16_t`-sized IEEE binary16 values (`__half` on the caller's
+ * side).  Nothing throws across this boundary and there is no CPU fallback: every entry point
+ * launches CUDA kernels on the context's stream or fails.
+ *
+ * Each declaration cites the reference interface it replaces (paths relative to the reference
+ * project's "AI gamer/" directory).
+ */
+#ifndef AIG_B200_H
+#define AIG_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t aig_half; /* IEEE binary16 bit pattern (device `__half`) */
+
+enum {
+  AIG_OK = 0,
+  AIG_ERR_INVALID = -1,     /* bad argument / unsupported shape */
+  AIG_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+  AIG_ERR_TIMEOUT = -3,     /* a bounded device-side wait expired (kernel returned early) */
+  AIG_ERR_UNSUPPORTED = -4, /* shape outside what the sm_100a kernels cover */
+  AIG_ERR_IO = -5           /* checkpoint file problem */
+};
+
+/* activation codes used by the fused epilogues */
+enum { AIG_ACT_NONE = 0, AIG_ACT_RELU = 1, AIG_ACT_SWISH = 2, AIG_ACT_LEAKY = 3 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Context.  Replaces InitCUDA() (CudaStuff.cu:21-51: device 0, global launch shape GS/BS) and the
+ * cudnnCreate/cublasCreate handles the reference threads through every layer constructor
+ * (Infer.cpp:76-79, NN.h:17-18).  One context = one device + one stream; calls on one context are
+ * issued in order on its stream; different contexts are independent. */
+typedef struct aig_ctx aig_ctx;
+int aig_ctx_create(aig_ctx** out, int device);
+int aig_ctx_destroy(aig_ctx* ctx);
+/* Use an existing cudaStream_t (passed as void*) instead of the context's own stream. */
+int aig_ctx_set_stream(aig_ctx* ctx, void* cuda_stream);
+void* aig_ctx_stream(aig_ctx* ctx);
+/* Synchronise the stream and report any deferred kernel error (including AIG_ERR_TIMEOUT raised by a
+ * bounded device-side wait).  The device error word is cleared. */
+int aig_ctx_sync(aig_ctx* ctx);
+const char* aig_last_error(aig_ctx* ctx);
+int aig_device_sm_count(aig_ctx* ctx);
+/* Asynchronous copy on the context's stream (any direction; the checkCUDA(cudaMemcpy(...)) calls of
+ * the reference's LoadParameters/SaveParameters and Infer.cpp:112). */
+int aig_memcpy(aig_ctx* ctx, void* dst, const void* src, size_t bytes);
+
+/* CUDA-graph capture of everything issued on the context's stream between begin and end; the
+ * frame loop (Infer.cpp:96-114) is replayed with aig_graph_launch. */
+typedef struct aig_graph aig_graph;
+int aig_graph_begin(aig_ctx* ctx);
+int aig_graph_end(aig_ctx* ctx, aig_graph** out);
+int aig_graph_launch(aig_ctx* ctx, aig_graph* g);
+int aig_graph_destroy(aig_graph* g);
+
+/* ---------------------------------------------------------------------------------------------
+ * Preprocessing and conversions. */
+/* ARGBtoRGBplanar (CudaStuff.cu:63-74, NvDisplayCap.h:68-69): BGRA bytes -> R,G,B planes. */
+int aig_bgra_to_planar(aig_ctx* ctx, const uint8_t* src, uint8_t* dst, int n);
+/* ConvertAndNormalize (CudaStuff.cu:150-157): out = half(float(u8)/255.0f). */
+int aig_convert_normalize(aig_ctx* ctx, aig_half* out, const uint8_t* in, size_t n);
+/* Both of the above in one pass: BGRA frames [B][H*W][4] -> fp16 NCHW [B][3][H*W]
+ * (GrabFrameInt8 + ConvertAndNormalize, Infer.cpp:103,109). */
+int aig_preprocess_bgra(aig_ctx* ctx, const uint8_t* bgra, aig_half* out_nchw, int frames, int hw);
+/* UnConvertAndUnNormalize (CudaStuff.cu:158-165). */
+int aig_unconvert_unnormalize(aig_ctx* ctx, uint8_t* out, const aig_half* in, size_t n);
+/* ConvertHalfToFloat / ConvertFloatToHalf (CudaStuff.cu:166-181). */
+int aig_half_to_float(aig_ctx* ctx, const aig_half* src, float* dst, size_t n);
+int aig_float_to_half(aig_ctx* ctx, const float* src, aig_half* dst, size_t n);
+/* Layout changes between the operator API's NCHW and the kernels' channels-last layout.
+ * `hw` is the product of the spatial extents (D*H*W for 5-D tensors). */
+int aig_nchw_to_nhwc(aig_ctx* ctx, const aig_half* src, aig_half* dst, int batch, int c, int hw);
+int aig_nhwc_to_nchw(aig_ctx* ctx, const aig_half* src, aig_half* dst, int batch, int c, int hw);
+
+/* ---------------------------------------------------------------------------------------------
+ * Element-wise operators, all in place like the reference. */
+/* LeakyReluForward (CudaStuff.cu:400-405). */
+int aig_leaky_relu_forward(aig_ctx* ctx, aig_half* data, int size, float negative_slope);
+/* SwishForward (CudaStuff.cu:416-424). */
+int aig_swish_forward(aig_ctx* ctx, aig_half* data, int size);
+/* Activate::Forward (Activate.cpp:17-21; cudnnActivationForward RELU). */
+int aig_relu_forward(aig_ctx* ctx, aig_half* data, int size);
+/* SigmoidForward (CudaStuff.cu:437-446): sigmoid where idx % num_ctrls < num_buts. */
+int aig_sigmoid_forward(aig_ctx* ctx, aig_half* data, int num_ctrls, int num_buts, int size);
+/* Not in the reference: tanh where idx % num_ctrls >= num_buts (mouse-axis outputs). */
+int aig_tanh_tail_forward(aig_ctx* ctx, aig_half* data, int num_ctrls, int num_buts, int size);
+/* cudnnAddTensor(alpha=1, beta=1) as used by ResConvLayer::Forward (ResConvLayer.cpp:35): m += r. */
+int aig_add_forward(aig_ctx* ctx, aig_half* m, const aig_half* r, int size);
+/* BatchNorm::Forward, inference branch (BatchNorm.cpp:55-63).  x,y [B][C][HW] (NCHW); parameters
+ * fp32; per_activation != 0 indexes parameters by c*HW+i (CUDNN_BATCHNORM_PER_ACTIVATION). */
+int aig_batchnorm_forward(aig_ctx* ctx, const aig_half* x, aig_half* y, const float* gamma,
+                          const float* beta, const float* mean, const float* var, int batch, int c,
+                          int hw, float eps, int per_activation);
+
+/* ---------------------------------------------------------------------------------------------
+ * Normalisation / spatial attention / pooling. */
+/* LayerNormForward (CudaStuff.cu:457-515): statistics per channel over N*HW, written to mean/
+ * variance; eps is an argument (the reference hard-codes 1e-7).  Every channel gets statistics
+ * (the reference's launch covers only the first ceil(C/BS) channels). */
+int aig_layernorm_forward(aig_ctx* ctx, aig_half* out, const aig_half* in, const float* gamma,
+                          const float* beta, float* mean, float* variance, int n, int c, int hw,
+                          float eps);
+/* Not in the reference: row-wise LayerNorm over the last dimension (rows x c). */
+int aig_layernorm_rows_forward(aig_ctx* ctx, aig_half* out, const aig_half* in, const float* gamma,
+                               const float* beta, int rows, int c, float eps);
+/* SpatialAttentionForward (CudaStuff.cu:747-760 -> kernel :673-746, scalar branch).  `group` is the
+ * softmax-sum group size, i.e. the reference's launch block size BS (64 on its build target);
+ * batch*in_h*in_w must be a multiple of it. */
+int aig_spatial_attention_forward(aig_ctx* ctx, const aig_half* in, const aig_half* key_w,
+                                  const aig_half* query_w, const aig_half* value_w,
+                                  aig_half* key_map, aig_half* query_map, aig_half* value_map,
+                                  aig_half* attention_scores, aig_half* out, int batch, int in_c,
+                                  int att_c, int in_h, int in_w, int group);
+/* Not in the reference: "1x1 conv -> sigmoid mask" attention on a channels-last tensor
+ * x,y [batch][hw][c]: m = sigmoid(x . w1 + b1), y = half(x*m). */
+int aig_spatial_mask_forward(aig_ctx* ctx, const aig_half* x_nhwc, const aig_half* w1, float b1,
+                             aig_half* y_nhwc, int batch, int hw, int c);
+/* Not in the reference: mean over hw of a channels-last tensor -> [batch][c]. */
+int aig_global_avgpool_nhwc(aig_ctx* ctx, const aig_half* x_nhwc, aig_half* y, int batch, int hw, int c);
+/* Not in the reference: adaptive average pool of channels-last [batch][d][h][w][c] over d and
+ * ph x pw spatial cells -> [batch][c*ph*pw] in (c, ph, pw) order. */
+int aig_adaptive_avgpool3d_ndhwc(aig_ctx* ctx, const aig_half* x, aig_half* y, int batch, int d, int h,
+                                 int w, int c, int ph, int pw);
+
+/* ---------------------------------------------------------------------------------------------
+ * Convolution / fully-connected plans: tcgen05 implicit GEMM, operands staged by TMA,
+ * accumulators in TMEM.  A plan freezes the shapes like the reference's layer constructors do
+ * (ConvLayer.cpp:4-50 builds descriptors and picks an algorithm once).  Activations are
+ * channels-last (NDHWC) fp16; weights are given in the reference file layouts and repacked on the
+ * device by the set_weights calls.
+ *
+ * Epilogue: v = acc; if two_step: v = half(v), v = half(v + bias)   [ConvLayer.cpp:76-77]
+ *           else v = acc*scale[k] + shift[k]  (bias and inference BatchNorm folded)
+ *           if residual: v = half(v) + residual                      [ResConvLayer.cpp:35]
+ *           y = half(act(v)). */
+typedef struct aig_conv_desc {
+  int batch, in_c, in_d, in_h, in_w; /* in_d = 1 for 2-D */
+  int out_c;
+  int kd, kh, kw;   /* kd = 1 for 2-D */
+  int sd, sh, sw;   /* strides */
+  int pd, ph, pw;   /* symmetric zero padding */
+  int act;          /* AIG_ACT_* */
+  float slope;      /* LeakyReLU slope */
+  int two_step;     /* 1: reproduce the reference's conv->half, +bias->half roundings, no BN fold */
+} aig_conv_desc;
+typedef struct aig_conv_plan aig_conv_plan;
+/* ConvLayer::ConvLayer / ConvLayer3D::ConvLayer3D (ConvLayer.cpp:4-50, ConvLayer3D.cpp:3-82). */
+int aig_conv_plan_create(aig_ctx* ctx, const aig_conv_desc* desc, aig_conv_plan** out);
+int aig_conv_plan_destroy(aig_conv_plan* plan);
+/* Output extents (ConvLayer.cpp:48-49 writes them back through its int* arguments). */
+int aig_conv_plan_out_dims(const aig_conv_plan* plan, int* out_d, int* out_h, int* out_w);
+/* ConvLayer::LoadParameters (ConvLayer.cpp:96-107): w fp16 [K][C][kd][kh][kw], bias fp16 [K]
+ * (device pointers).  bn_* (fp32 [K], device, may be null = no BatchNorm) are the inference
+ * BatchNorm parameters that follow the conv (BatchNorm.cpp:55-63); they are folded into the
+ * epilogue's scale/shift. */
+int aig_conv_plan_set_weights(aig_conv_plan* plan, const aig_half* w, const aig_half* bias,
+                              const float* bn_gamma, const float* bn_beta, const float* bn_mean,
+                              const float* bn_var, float bn_eps);
+/* ConvLayer::Forward (+ fused BatchNorm/activation/residual).  x NDHWC, y NDHWC,
+ * residual NDHWC of the output shape or null. */
+int aig_conv_forward(aig_conv_plan* plan, const aig_half* x, const aig_half* residual, aig_half* y);
+
+/* FCLayer (FCLayer.cpp:4-53): y[b][o] = sum_k x[b][k] * W[k*out_c + o] + bias[o].  Same kernel and
+ * epilogue as the convolution; `rows` = batch (or batch*time for per-step heads). */
+int aig_fc_plan_create(aig_ctx* ctx, int rows, int in_c, int out_c, int act, float slope, int two_step,
+                       aig_conv_plan** out);
+/* FCLayer::LoadParameters (FCLayer.cpp:70-81): W fp16 [in_c][out_c], bias fp16 [out_c] or null;
+ * bn_* = per-activation BatchNorm after the FC (NN.cpp:46), or null. */
+int aig_fc_plan_set_weights(aig_conv_plan* plan, const aig_half* w_in_out, const aig_half* bias,
+                            const float* bn_gamma, const float* bn_beta, const float* bn_mean,
+                            const float* bn_var, float bn_eps);
+/* Same, with the matrix given as [out_c][in_c] (the LSTM blob's orientation). */
+int aig_fc_plan_set_weights_out_in(aig_conv_plan* plan, const aig_half* w_out_in, const aig_half* bias);
+
+/* First-layer convolutions (3 input channels), CUDA-core/tensor kernels with the input conversion
+ * fused into the load.
+ * 2-D: BGRA uint8 frames [B][H][W][4] -> y NHWC fp16 [B][Ho][Wo][K]; the BGRA->RGB split and
+ * /255 normalisation (CudaStuff.cu:63-74,150-157) happen in the load, then conv k x k, stride s,
+ * pad p over (R,G,B) planes, scale/shift (bias + BatchNorm folded) and activation. */
+typedef struct aig_conv0_plan aig_conv0_plan;
+int aig_conv0_plan_create(aig_ctx* ctx, int batch, int in_h, int in_w, int out_c, int k, int stride,
+                          int pad, int act, float slope, aig_conv0_plan** out);
+/* First layer of the 3-D temporal encoder (ConvLayer3D.cpp:3-82 with 3 input channels): input
+ * planar fp16 [B][3][D][H][W], output channels-last [B][Do][Ho][Wo][K]. */
+int aig_conv0_plan_create_3d(aig_ctx* ctx, int batch, int in_d, int in_h, int in_w, int out_c, int kd,
+                             int khw, int sd, int shw, int pd, int phw, int act, float slope,
+                             aig_conv0_plan** out);
+int aig_conv0_plan_destroy(aig_conv0_plan* plan);
+int aig_conv0_plan_out_dims(const aig_conv0_plan* plan, int* out_d, int* out_h, int* out_w);
+int aig_conv0_plan_set_weights(aig_conv0_plan* plan, const aig_half* w_kcrs, const aig_half* bias,
+                               const float* bn_gamma, const float* bn_beta, const float* bn_mean,
+                               const float* bn_var, float bn_eps);
+int aig_conv0_forward_bgra(aig_conv0_plan* plan, const uint8_t* bgra, aig_half* y_nhwc);
+/* Same convolution from an already normalised planar fp16 NCHW input (the operator-API path). */
+int aig_conv0_forward_nchw(aig_conv0_plan* plan, const aig_half* x_nchw, aig_half* y_nhwc);
+
+/* Output decisions of Infer::ProcessOutput (Infer.cpp:8-57) as a pure function on host values:
+ * actions[i] = p[i] > 0.5 for i < n_buttons, (int)(p[i]*256.0f) otherwise. */
+int aig_actions_from_outputs(const float* p, int* actions, int frames, int n_ctrls, int n_buttons);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIG_B200_H */

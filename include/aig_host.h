@@ -1,0 +1,72 @@
+/* aig_host.h -- C ABI of the host-side model runners built on the kernel ABI (aig_b200.h).
+ *
+ * These replace the reference's model container and frame loop for the inference path:
+ * NN::NN / NN::Forward (NN.cpp:11-100) and the body of Infer::Inference (Infer.cpp:96-114).
+ * They own the per-layer plans and activation buffers, load parameters from a checkpoint in the
+ * reference's byte layout, and replay the whole forward as one CUDA graph.
+ */
+#ifndef AIG_HOST_H
+#define AIG_HOST_H
+#include "aig_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AIG_CNN_MAX_BLOCKS 7
+
+/* 2-D frame encoder: Conv(3->widths[0], k0 x k0, stride 2, pad k0/2)+BN+act, n_blocks ResConv
+ * blocks widths[i]->widths[i+1] (ResConvLayer.cpp:13-21), mask attention, global average pool,
+ * FC -> n_out, sigmoid on the first n_sigmoid outputs and tanh on the rest. */
+typedef struct aig_cnn_config {
+  int batch, height, width;
+  int n_blocks;
+  int widths[AIG_CNN_MAX_BLOCKS + 1];
+  int k0;
+  int n_out, n_sigmoid;
+  int act;      /* AIG_ACT_* used after every BatchNorm and after the residual add */
+  float slope;
+} aig_cnn_config;
+
+typedef struct aig_cnn aig_cnn;
+/* NN::NN, layer construction part (NN.cpp:33-61). */
+int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out);
+int aig_cnn_destroy(aig_cnn* m);
+const char* aig_cnn_last_error(aig_cnn* m);
+/* Size in bytes of the checkpoint this network reads. */
+size_t aig_cnn_checkpoint_bytes(const aig_cnn_config* cfg);
+/* NN::NN, checkpoint part (NN.cpp:13-20,67-75): header int32 width,height then every layer's
+ * LoadParameters payload in construction order.  `blob` is host memory. */
+int aig_cnn_load_memory(aig_cnn* m, const void* blob, size_t bytes);
+int aig_cnn_load_file(aig_cnn* m, const char* path);
+/* NN::Forward (NN.cpp:93-100) preceded by the frame preprocessing (Infer.cpp:103,109) on BGRA
+ * frames [batch][height][width][4] resident in device memory.  Asynchronous on the context stream. */
+int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev);
+/* The same work replayed from a CUDA graph captured on first use. */
+int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev);
+/* One frame step with host buffers (Infer.cpp:103-112): host->device copy of the frames, forward,
+ * half->float, device->host copy of [batch][n_out] floats, stream synchronise. */
+int aig_cnn_infer_host(aig_cnn* m, const uint8_t* bgra_host, float* out_host);
+/* Device views of the last forward's results. */
+const aig_half* aig_cnn_outputs_half(aig_cnn* m);  /* [batch][n_out] after sigmoid/tanh */
+const float* aig_cnn_outputs_f32(aig_cnn* m);      /* the same as fp32 (ConvertHalfToFloat) */
+const aig_half* aig_cnn_features(aig_cnn* m);      /* [batch][widths[n_blocks]] pooled features */
+/* Channels-last output of stage 0 (first conv) .. n_blocks (last ResConv), for layer-wise checks. */
+const aig_half* aig_cnn_stage_output(aig_cnn* m, int stage, int* h, int* w, int* c);
+/* Kernels launched by one aig_cnn_forward. */
+int aig_cnn_kernel_launches(aig_cnn* m);
+/* Per-launch device timing of aig_cnn_forward (eager path) with CUDA events on the context stream:
+ * begin() arms it for up to max_steps forwards; end() synchronises and writes the mean milliseconds
+ * of every launch site (aig_cnn_site_count of them, in launch order).  site_flops/site_bytes are the
+ * algorithmic 2*MAC and bytes of one launch, the numerators of the roofline figures. */
+int aig_cnn_profile_begin(aig_cnn* m, int max_steps);
+int aig_cnn_profile_end(aig_cnn* m, double* mean_ms, int capacity, int* steps);
+int aig_cnn_site_count(aig_cnn* m);
+const char* aig_cnn_site_name(aig_cnn* m, int i);
+double aig_cnn_site_flops(aig_cnn* m, int i);
+double aig_cnn_site_bytes(aig_cnn* m, int i);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIG_HOST_H */

@@ -1,0 +1,69 @@
+"""CPU-side checks of the boundary: the CUDA library builds, loads, and exports every symbol the
+public headers declare (no compute calls are made -- there is no GPU here), error paths that need no
+device behave, and the checkpoint writer produces the byte layout the loader expects."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import __graft_entry__ as entry
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    return entry.build()
+
+
+def declared_symbols():
+    names = []
+    for hdr in ("aig_b200.h", "aig_host.h"):
+        text = open(os.path.join(ROOT, "include", hdr)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names += re.findall(r"\b(aig_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = ctypes.CDLL(pkg.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) > 60
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, "declared in include/*.h but not exported: %s" % missing
+
+
+def test_python_binding_declares_every_symbol(pkg):
+    missing = [n for n in declared_symbols() if n not in pkg.SIGNATURES]
+    assert not missing, "no ctypes signature for: %s" % missing
+
+
+def test_no_device_is_an_error_not_a_fallback(pkg):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(pkg.AigError):
+        pkg.Context(0, use_torch_stream=False)
+
+
+def test_host_side_actions(pkg):
+    p = np.array([[0.6] * 14 + [0.5, -0.25]], np.float32)
+    out = np.zeros((1, 16), np.int32)
+    rc = pkg.lib().aig_actions_from_outputs(pkg.ptr(p), pkg.ptr(out), 1, 16, 14)
+    assert rc == 0
+    assert out[0].tolist() == [1] * 14 + [128, -64]
+    assert pkg.lib().aig_actions_from_outputs(None, pkg.ptr(out), 1, 16, 14) == -1
+
+
+def test_checkpoint_size_matches_writer(pkg):
+    from ai_gamer_b200 import synth as SY
+
+    widths = (32, 64, 128, 256, 256)
+    w = (ctypes.c_int * 8)(*widths)
+    cfg = pkg.CnnConfig(4, 144, 256, 4, w, 5, 18, 16, pkg.ACT_SWISH, 0.01)
+    blob = SY.serialize_cnn_checkpoint(SY.make_cnn_params(0, widths=widths), 256, 144)
+    assert pkg.lib().aig_cnn_checkpoint_bytes(ctypes.byref(cfg)) == len(blob)
+    assert np.frombuffer(blob[:8], np.int32).tolist() == [256, 144]  # NN.cpp:118-119: width then height
