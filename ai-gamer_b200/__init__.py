@@ -159,6 +159,13 @@ class Context:
         if use_torch_stream:
             import torch
 
+            if torch.cuda.current_stream(device).cuda_stream == 0:
+                # the legacy default stream cannot be captured into a CUDA graph: switch torch (and this
+                # context) to a fresh stream; work already queued on the default stream is waited for
+                s = torch.cuda.Stream(device)
+                s.wait_stream(torch.cuda.current_stream(device))
+                torch.cuda.set_stream(s)
+                self._torch_stream = s
             self.set_stream(torch.cuda.current_stream(device).cuda_stream)
 
     def check(self, rc):

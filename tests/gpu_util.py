@@ -59,18 +59,47 @@ def ulp16_diff(a, b):
     return np.abs(key(a) - key(b))
 
 
-def assert_close16(got, want, max_ulp=1, frac_exact=None, what=""):
+def assert_close16(got, want, max_ulp=1, frac_exact=None, what="", atol=0.0):
+    """Every element within max_ulp fp16 ulps of the oracle, or within atol in absolute terms (results
+    formed by cancellation sit near zero, where an fp16 ulp is far below the accumulation error)."""
     d = ulp16_diff(got, want)
+    if atol > 0:
+        ok = np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64)) <= atol
+        d = np.where(ok, np.minimum(d, max_ulp), d)
     assert d.max() <= max_ulp, "%s: max fp16 ulp distance %d > %d (%d of %d differ)" % (
         what, d.max(), max_ulp, (d > 0).sum(), d.size)
     if frac_exact is not None:
         assert (d == 0).mean() >= frac_exact, "%s: only %.4f bit-exact" % (what, (d == 0).mean())
 
 
+def assert_two_step(got, want, bias, what="", frac_exact=0.99):
+    """Check of the reference's conv/FC rounding sequence y = half(half(acc) + bias): fp32 accumulation
+    on the tensor cores against the oracle's double accumulation may move half(acc) by one fp16 ulp at
+    the magnitude of acc = y - bias, which the bias add can carry into a smaller binade of y.  So the
+    bound is one ulp of max(|y|, |y - bias|); almost all elements must be bit-exact."""
+    got = np.asarray(got, np.float64)
+    want64 = np.asarray(want, np.float64)
+    scale = np.maximum(np.abs(want64), np.abs(want64 - np.asarray(bias, np.float64)))
+    ulp = np.maximum(2.0 ** (np.floor(np.log2(np.maximum(scale, 2.0 ** -14))) - 10), 2.0 ** -24)
+    bad = np.abs(got - want64) > ulp * 1.0001
+    assert not bad.any(), "%s: %d of %d beyond one ulp of the accumulator" % (what, bad.sum(), bad.size)
+    exact = (got == want64).mean()
+    assert exact >= frac_exact, "%s: only %.4f bit-exact" % (what, exact)
+
+
 def rel_err(got, want, floor=1e-2):
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
     return np.abs(got - want) / np.maximum(np.abs(want), floor)
+
+
+def scaled_err(got, want):
+    """max |got - want| relative to max(|want|, rms(want)): element-wise relative error with a floor at
+    the tensor's own scale, so that near-zero activations do not dominate."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    rms = float(np.sqrt(np.mean(want * want))) + 1e-12
+    return float((np.abs(got - want) / np.maximum(np.abs(want), rms)).max())
 
 
 def ref_cuda():

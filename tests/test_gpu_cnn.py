@@ -8,7 +8,8 @@ from oracle import pipelines as PL
 
 gpu = pytest.mark.gpu
 
-REL_TOL = 2e-2  # tolerance on key/mouse outputs for fp16 compute with fp32 accumulation
+REL_TOL = 2e-2    # relative tolerance on the key/mouse outputs (fp16 compute, fp32 accumulation)
+STAGE_TOL = 1e-2  # intermediate activations: max error relative to max(|value|, rms of the tensor)
 
 
 @pytest.fixture(scope="module")
@@ -44,15 +45,20 @@ def test_cnn_encoder_matches_oracle(env, trivial):
     # layer by layer first: a failure names the first stage that drifts
     for i, st in enumerate(stages):
         got = U.nchw(U.host(enc.stage_output(i)))
-        err = U.rel_err(got, st, 0.05)
-        assert err.max() < REL_TOL, "stage %d: max rel err %.4f" % (i, err.max())
+        err = U.scaled_err(got, st)
+        assert err < STAGE_TOL, "stage %d: max scaled err %.4f" % (i, err)
     got_feat = U.host(enc.features())
     assert U.rel_err(got_feat, feat, 0.02).max() < REL_TOL
     got = U.host(enc.outputs_f32())
     assert np.array_equal(got.astype(np.float16), U.host(enc.outputs_half()))
     assert U.rel_err(got, want.astype(np.float32), 0.05).max() < REL_TOL
-    agree = (O.actions(got, 18, 16) == O.actions(want.astype(np.float32), 18, 16)).all(axis=1).mean()
-    assert agree >= 0.999
+    # decisions (Infer.cpp:8-57): button thresholds must agree wherever the oracle is not within the
+    # tolerance of the 0.5 threshold; the mouse deltas (int(p*256)) may differ by one count
+    a_got, a_want = O.actions(got, 18, 16), O.actions(want.astype(np.float32), 18, 16)
+    clear = np.abs(want.astype(np.float32)[:, :16] - 0.5) > 2e-3
+    assert (a_got[:, :16] == a_want[:, :16])[clear].all()
+    assert (a_got[:, :16] == a_want[:, :16]).mean() >= 0.999
+    assert np.abs(a_got[:, 16:] - a_want[:, 16:]).max() <= 1
     # graph replay and the host-buffer frame step give the same bytes
     enc.forward(d_frames, graph=True)
     c.sync()
