@@ -67,6 +67,19 @@ SIGNATURES = {
     "aig_fc_plan_create": [P, c_int, c_int, c_int, c_int, c_float, c_int, PP],
     "aig_fc_plan_set_weights": [P, P, P, P, P, P, P, c_float],
     "aig_fc_plan_set_weights_out_in": [P, P, P],
+    "aig_fc_plan_set_output_f32": [P, c_int],
+    "aig_fc_plan_add_bias": [P, P],
+    "aig_lstm_weight_count": [c_int, c_int, c_int, c_int],
+    "aig_lstm_plan_create": [P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, PP],
+    "aig_lstm_plan_destroy": [P],
+    "aig_lstm_plan_set_weights": [P, P],
+    "aig_lstm_forward": [P, P, P, P, P, c_int],
+    "aig_mha_plan_create": [P, c_int, c_int, c_int, c_int, c_float, c_int, PP],
+    "aig_mha_plan_destroy": [P],
+    "aig_mha_plan_set_weights": [P, P, P, P, P],
+    "aig_mha_forward": [P, P, P, c_int],
+    "aig_mha_step": [P, P, P, c_int],
+    "aig_mha_reset": [P],
     "aig_conv0_plan_create": [P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, PP],
     "aig_conv0_plan_create_3d": [P] + [c_int] * 12 + [c_float, PP],
     "aig_conv0_plan_destroy": [P],
@@ -110,7 +123,8 @@ SIGNATURES.update({
 _RESTYPES = {"aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
-             "aig_cnn_site_flops": ctypes.c_double, "aig_cnn_site_bytes": ctypes.c_double}
+             "aig_cnn_site_flops": ctypes.c_double, "aig_cnn_site_bytes": ctypes.c_double,
+             "aig_lstm_weight_count": c_size_t}
 
 _lib = None
 
@@ -386,3 +400,45 @@ class CnnEncoder:
         if self.handle:
             lib().aig_cnn_destroy(self.handle)
             self.handle = c_void_p()
+
+
+class LstmPlan(_Plan):
+    """aig_lstm_plan: hoisted input projection + persistent recurrent kernel."""
+    _destroy = "aig_lstm_plan_destroy"
+
+    def __init__(self, ctx, seq_len, layers, hidden, batch, in_c, clip=5.0, double_bias=True, batch_major=False):
+        super().__init__(ctx)
+        self.check(lib().aig_lstm_plan_create(ctx.handle, seq_len, layers, hidden, batch, in_c, clip, 1 if double_bias else 0,
+                                              1 if batch_major else 0, ctypes.byref(self.handle)))
+
+    def set_weights(self, blob):
+        self._keep = [blob]
+        self.check(lib().aig_lstm_plan_set_weights(self.handle, ptr(blob)))
+
+    def forward(self, x, y, h_state=None, c_state=None, use_state=False):
+        self.check(lib().aig_lstm_forward(self.handle, ptr(x), ptr(y), ptr(h_state), ptr(c_state), 1 if use_state else 0))
+        return y
+
+
+class MhaPlan(_Plan):
+    """aig_mha_plan: projections + tcgen05 attention tile kernel (+ ring KV cache step)."""
+    _destroy = "aig_mha_plan_destroy"
+
+    def __init__(self, ctx, batch, seq_len, embed, heads, rope_base=0.0, window=0):
+        super().__init__(ctx)
+        self.check(lib().aig_mha_plan_create(ctx.handle, batch, seq_len, embed, heads, rope_base, window, ctypes.byref(self.handle)))
+
+    def set_weights(self, wq, wk, wv, wo):
+        self._keep = [wq, wk, wv, wo]
+        self.check(lib().aig_mha_plan_set_weights(self.handle, ptr(wq), ptr(wk), ptr(wv), ptr(wo)))
+
+    def forward(self, x, y, pos0=0):
+        self.check(lib().aig_mha_forward(self.handle, ptr(x), ptr(y), pos0))
+        return y
+
+    def step(self, x, y, position):
+        self.check(lib().aig_mha_step(self.handle, ptr(x), ptr(y), position))
+        return y
+
+    def reset(self):
+        self.check(lib().aig_mha_reset(self.handle))

@@ -36,6 +36,7 @@ struct IgemmParams {
   const float* shift;
   const __half* residual;
   __half* y;
+  float* y32;  // when set, the result is stored as fp32 here instead of fp16 in y
   int* gerr;
 };
 
@@ -218,7 +219,18 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               }
               v[e] = a;
             }
-            if (vec_ok) {
+            if (p.y32) {
+              // fp32 output (pre-activations consumed by the LSTM recurrence): no rounding, no activation
+              float* o32 = p.y32 + pix * p.out_c + n;
+              if ((p.out_c & 7) == 0) {
+                *reinterpret_cast<float4*>(o32) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(o32 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (n + e < p.out_c) o32[e] = v[e];
+              }
+            } else if (vec_ok) {
               if (rrow) {
                 const uint4 rv = *reinterpret_cast<const uint4*>(rrow + n);
                 const __half* rh = reinterpret_cast<const __half*>(&rv);
@@ -302,6 +314,11 @@ __global__ void fold_affine_kernel(float* scale, float* shift, __half* bias_out,
   }
 }
 
+__global__ void add_bias_kernel(float* shift, const __half* bias2, int K) {
+  const int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < K) shift[k] += __half2float(bias2[k]);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -331,6 +348,7 @@ struct aig_conv_plan {
   float* shift = nullptr;
   __half* bias_h = nullptr;
   bool weights_set = false;
+  bool out_f32 = false;
   CUtensorMap tmapA{}, tmapB{};
   const void* tmapA_ptr = nullptr;
   int grid = 1;
@@ -559,7 +577,8 @@ int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* resid
     if (rc != AIG_OK) return rc;
   }
   pl->prm.residual = (const __half*)residual;
-  pl->prm.y = (__half*)y;
+  pl->prm.y = pl->out_f32 ? nullptr : (__half*)y;
+  pl->prm.y32 = pl->out_f32 ? (float*)y : nullptr;
   return dispatch(pl);
 }
 
@@ -598,6 +617,23 @@ int aig_fc_plan_set_weights(aig_conv_plan* pl, const aig_half* w_in_out, const a
   repack_fc_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const __half*)w_in_out, pl->w_packed, pl->d.in_c, pl->d.out_c);
   AIG_LAUNCH_OK(ctx);
   return set_affine(pl, bias, bn_gamma, bn_beta, bn_mean, bn_var, bn_eps);
+}
+
+int aig_fc_plan_set_output_f32(aig_conv_plan* pl, int enable) {
+  if (!pl) return AIG_ERR_INVALID;
+  AIG_REQUIRE(pl->ctx, !enable || (pl->d.act == AIG_ACT_NONE && !pl->d.two_step), "fp32 output is for plain affine epilogues");
+  pl->out_f32 = enable != 0;
+  return AIG_OK;
+}
+
+int aig_fc_plan_add_bias(aig_conv_plan* pl, const aig_half* bias2) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, bias2 != nullptr && pl->weights_set, "fc add_bias: set the weights first");
+  add_bias_kernel<<<ceil_div(pl->d.out_c, 128), 128, 0, ctx->stream>>>(pl->shift, (const __half*)bias2, pl->d.out_c);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
 }
 
 int aig_fc_plan_set_weights_out_in(aig_conv_plan* pl, const aig_half* w_out_in, const aig_half* bias) {

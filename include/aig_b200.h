@@ -179,6 +179,13 @@ int aig_fc_plan_set_weights(aig_conv_plan* plan, const aig_half* w_in_out, const
 /* Same, with the matrix given as [out_c][in_c] (the LSTM blob's orientation). */
 int aig_fc_plan_set_weights_out_in(aig_conv_plan* plan, const aig_half* w_out_in, const aig_half* bias);
 
+/* Store the result as fp32 (`y` of aig_conv_forward is then a float*): used for the LSTM's input
+ * projection, whose pre-activations must not be rounded before the recurrent sum. */
+int aig_fc_plan_set_output_f32(aig_conv_plan* plan, int enable);
+/* Add a second bias vector (cuDNN's LSTM keeps separate input and recurrent biases,
+ * LSTMLayer.cpp:9-40 default bias mode); call after the set_weights function. */
+int aig_fc_plan_add_bias(aig_conv_plan* plan, const aig_half* bias2);
+
 /* First-layer convolutions (3 input channels), CUDA-core/tensor kernels with the input conversion
  * fused into the load.
  * 2-D: BGRA uint8 frames [B][H][W][4] -> y NHWC fp16 [B][Ho][Wo][K]; the BGRA->RGB split and
@@ -200,6 +207,53 @@ int aig_conv0_plan_set_weights(aig_conv0_plan* plan, const aig_half* w_kcrs, con
 int aig_conv0_forward_bgra(aig_conv0_plan* plan, const uint8_t* bgra, aig_half* y_nhwc);
 /* Same convolution from an already normalised planar fp16 NCHW input (the operator-API path). */
 int aig_conv0_forward_nchw(aig_conv0_plan* plan, const aig_half* x_nchw, aig_half* y_nhwc);
+
+/* ---------------------------------------------------------------------------------------------
+ * LSTM.  Replaces LSTMLayer (LSTMLayer.cpp:4-40 constructor, :75-104 Forward: cudnnRNNForwardInference,
+ * seq-major x [T][B][in] -> y [T][B][hidden], cell clip +-5, two bias vectors) and the cuDNN-8 variant
+ * (LSTMLayerv8.cpp:8-39,78-82: batch-major [B][T][.], single bias, no clip).
+ * The reference treats the weights as one opaque library blob of weightCount_ halves
+ * (LSTMLayer.cpp:29-35,139-146).  This library defines the blob as: for each layer
+ * W_i,W_f,W_g,W_o ([hidden][in_l] row-major) then R_i,R_f,R_g,R_o ([hidden][hidden]); then for each
+ * layer bW_i..bW_o and, with double_bias, bR_i..bR_o.  h and c are rounded to fp16 every step.
+ * Not in the reference: carried state (h_state/c_state, [layers][B][hidden]) for streaming. */
+typedef struct aig_lstm_plan aig_lstm_plan;
+size_t aig_lstm_weight_count(int in_c, int hidden, int layers, int double_bias);
+int aig_lstm_plan_create(aig_ctx* ctx, int seq_len, int layers, int hidden, int batch, int in_c,
+                         float clip, int double_bias, int batch_major, aig_lstm_plan** out);
+int aig_lstm_plan_destroy(aig_lstm_plan* plan);
+/* LSTMLayer::LoadParameters (LSTMLayer.cpp:139-146): the blob stays where it is (device memory,
+ * 16-byte aligned) and must outlive the plan's forwards. */
+int aig_lstm_plan_set_weights(aig_lstm_plan* plan, const aig_half* blob);
+/* LSTMLayer::Forward.  y holds the top layer's h for every step (the reference returns the pointer
+ * to the last step's rows, LSTMLayer.cpp:103).  h_state/c_state may be null; they are read as the
+ * initial state when use_state != 0 and always receive the final state when non-null. */
+int aig_lstm_forward(aig_lstm_plan* plan, const aig_half* x, aig_half* y, aig_half* h_state,
+                     aig_half* c_state, int use_state);
+
+/* ---------------------------------------------------------------------------------------------
+ * Multi-head self-attention.  Replaces MultiHeadAttentionLayer (MHALayer.cpp:4-91 constructor,
+ * :128-146 Forward: cudnnMultiHeadAttnForward with q = k = v = input, four E x E projection
+ * matrices wq,wk,wv,wo (:42-45), `heads` heads of E/heads, scale 1/sqrt(E/heads), causal window
+ * [0, i+1), no biases, no residual).  Matrices are [in][out] like FCLayer; head h uses output
+ * columns h*d .. h*d+d-1.
+ * Not in the reference: rotary position embedding (rope_base > 0; half-split pairs (j, j+d/2),
+ * angle = position * rope_base^(-2j/d)) and a ring key/value cache of `window` slots for
+ * step-by-step use (aig_mha_step). */
+typedef struct aig_mha_plan aig_mha_plan;
+int aig_mha_plan_create(aig_ctx* ctx, int batch, int seq_len, int embed, int heads, float rope_base,
+                        int window, aig_mha_plan** out);
+int aig_mha_plan_destroy(aig_mha_plan* plan);
+/* MultiHeadAttentionLayer::LoadParameters (MHALayer.cpp:191-210): wq, wk, wv, wo, each fp16 [E][E]. */
+int aig_mha_plan_set_weights(aig_mha_plan* plan, const aig_half* wq, const aig_half* wk,
+                             const aig_half* wv, const aig_half* wo);
+/* Full-sequence forward: x, y [B][T][E]; positions pos0 .. pos0+T-1; step t attends to
+ * max(0, t-window+1) .. t (window <= 0: all earlier steps). */
+int aig_mha_forward(aig_mha_plan* plan, const aig_half* x, aig_half* y, int pos0);
+/* Streaming: one new step per sequence, x,y [B][E], appended to the ring cache at `position`
+ * (absolute frame index; the cache holds the last `window` steps).  aig_mha_reset empties it. */
+int aig_mha_step(aig_mha_plan* plan, const aig_half* x, aig_half* y, int position);
+int aig_mha_reset(aig_mha_plan* plan);
 
 /* Output decisions of Infer::ProcessOutput (Infer.cpp:8-57) as a pure function on host values:
  * actions[i] = p[i] > 0.5 for i < n_buttons, (int)(p[i]*256.0f) otherwise. */
