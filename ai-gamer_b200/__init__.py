@@ -74,6 +74,7 @@ SIGNATURES = {
     "aig_lstm_plan_destroy": [P],
     "aig_lstm_plan_set_weights": [P, P],
     "aig_lstm_forward": [P, P, P, P, P, c_int],
+    "aig_lstm_forward_noalloc": [P, P, P, P, c_int, c_int, c_int, c_int, c_float, c_int],
     "aig_mha_plan_create": [P, c_int, c_int, c_int, c_int, c_float, c_int, PP],
     "aig_mha_plan_destroy": [P],
     "aig_mha_plan_set_weights": [P, P, P, P, P],

@@ -498,3 +498,146 @@ int aig_lstm_forward(aig_lstm_plan* pl, const aig_half* x, aig_half* y, aig_half
 }
 
 }  // extern "C"
+
+// =============================================================================================
+// Allocation-free single-layer LSTM forward.
+//
+// For callers that must not allocate device memory once they are running: a frame loop that shares
+// the GPU with the game it plays (cudaMalloc/cudaFree synchronise the whole device and stall every
+// other stream, and the game may already own nearly all of the memory), or a host application that
+// reserves its whole device budget at start-up and forbids later allocations.  Everything the plan
+// based entry points keep in cudaMalloc'ed buffers -- the hoisted input projection, the zero initial
+// state and the step-barrier counter -- lives here in one fixed array in the library's device image.
+//
+// The array is part of the module: every GPU that loads the library holds kNoAllocBytes until the
+// process exits.  All calls on a device share it, so two calls that overlap on the GPU (different
+// streams) race; serialise them.  It keeps the previous call's contents, so each call clears the parts
+// that must start at zero (the barrier counter and the zero state) on its stream before use.
+namespace {
+
+constexpr size_t kNoAllocProjFloats = (size_t)1 << 19;                       // 2 MiB of fp32 projections
+constexpr int kNoAllocMaxBatch = kRows;                                      // one batch group
+constexpr int kNoAllocMaxHidden = 512;
+constexpr size_t kNoAllocProjBytes = kNoAllocProjFloats * sizeof(float);
+constexpr size_t kNoAllocStateBytes = (size_t)kNoAllocMaxBatch * kNoAllocMaxHidden * sizeof(__half);
+constexpr size_t kNoAllocCounterOff = kNoAllocProjBytes + kNoAllocStateBytes;
+constexpr size_t kNoAllocBytes = kNoAllocCounterOff + 256;
+
+// In host code this name is only a handle for the runtime's symbol table, not a device address: the
+// device address is fetched once per device with cudaGetSymbolAddress below and that is what kernels get.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+unsigned char* g_noalloc_ptr[64] = {};  // per device, filled by the first call on that device
+
+// gx[row][j] = sum_k x[row][k] * W[j][k] + bW[j] (+ bR[j]); 32x32 output tile per block, fp32 accumulate.
+__global__ void noalloc_projection_kernel(const __half* __restrict__ x, const __half* __restrict__ W,
+                                          const __half* __restrict__ bW, const __half* __restrict__ bR,
+                                          float* __restrict__ gx, int rows, int in_c, int out_c) {
+  __shared__ float sx[32][33], sw[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
+  const int row0 = blockIdx.y * 32, col0 = blockIdx.x * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < in_c; k0 += 32) {
+    for (int i = ty; i < 32; i += 8) {
+      const int r = row0 + i, c = col0 + i, k = k0 + tx;
+      sx[i][tx] = (r < rows && k < in_c) ? __half2float(x[(size_t)r * in_c + k]) : 0.f;
+      sw[i][tx] = (c < out_c && k < in_c) ? __half2float(W[(size_t)c * in_c + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) {
+      const float wv = sw[tx][kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(sx[ty + 8 * i][kk], wv, acc[i]);
+    }
+    __syncthreads();
+  }
+  const int c = col0 + tx;
+  if (c < out_c) {
+    const float b = __half2float(bW[c]) + (bR ? __half2float(bR[c]) : 0.f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = row0 + ty + 8 * i;
+      if (r < rows) gx[(size_t)r * out_c + c] = acc[i] + b;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Single-layer, seq-major LSTM forward with zero initial state: x [T][B][in] -> y [T][B][hidden], the blob
+// laid out as aig_lstm_plan_set_weights expects for one layer.  Asynchronous on the context's stream; no
+// device or pinned memory is allocated or freed.  The first call on a device resolves the scratch array's
+// device address (cudaGetSymbolAddress); make that first call before any stream capture begins.
+int aig_lstm_forward_noalloc(aig_ctx* ctx, const aig_half* x, const aig_half* blob, aig_half* y, int seq_len, int batch,
+                             int in_c, int hidden, float clip, int double_bias) {
+  if (!ctx) return AIG_ERR_INVALID;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, x && blob && y && seq_len > 0 && batch > 0 && in_c > 0 && hidden > 0, "lstm noalloc: bad arguments");
+  AIG_REQUIRE(ctx, ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)blob & 15) == 0,
+              "lstm noalloc: tensors must be 16-byte aligned");
+  if (hidden % 64 != 0 || hidden > kNoAllocMaxHidden)
+    return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "lstm noalloc: hidden must be a multiple of 64 and at most %d (got %d)", kNoAllocMaxHidden, hidden);
+  if (batch > kNoAllocMaxBatch)
+    return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "lstm noalloc: batch %d exceeds the maximum of %d", batch, kNoAllocMaxBatch);
+  if (in_c % 8 != 0) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "lstm noalloc: in_c must be a multiple of 8 (got %d)", in_c);
+  const size_t proj = (size_t)seq_len * batch * 4 * hidden;
+  if (proj > kNoAllocProjFloats)
+    return aig_fail(ctx, AIG_ERR_UNSUPPORTED,
+                    "lstm noalloc: seq_len*batch*4*hidden = %zu exceeds the fixed scratch of %zu floats (%zu bytes)", proj,
+                    kNoAllocProjFloats, kNoAllocProjBytes);
+  constexpr int U = 16;
+  const int NC = hidden / U, nkb = hidden / kKB;
+  const size_t smem = (size_t)nkb * (kRows + 4 * U) * 128 + 1024 + 256;
+  // ---- once per device: resolve the symbol, set the kernel's shared-memory limit
+  unsigned char*& base = g_noalloc_ptr[ctx->device & 63];
+  if (!base) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) return aig_fail(ctx, AIG_ERR_CUDA, "lstm noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    base = static_cast<unsigned char*>(p);
+  }
+  AIG_CUDA_OK(ctx, cudaFuncSetAttribute(lstm_recurrent_kernel<U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  float* gx = reinterpret_cast<float*>(base);
+  __half* zero_state = reinterpret_cast<__half*>(base + kNoAllocProjBytes);
+  unsigned int* counter = reinterpret_cast<unsigned int*>(base + kNoAllocCounterOff);
+  int per_sm = 0;
+  AIG_CUDA_OK(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, lstm_recurrent_kernel<U>, kThreads, smem));
+  if (per_sm * ctx->sm_count < NC) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "lstm noalloc: %d CTAs cannot be co-resident", NC);
+  // ---- what must start at zero
+  AIG_CUDA_OK(ctx, cudaMemsetAsync(counter, 0, 256, ctx->stream));
+  AIG_CUDA_OK(ctx, cudaMemsetAsync(zero_state, 0, (size_t)batch * hidden * sizeof(__half), ctx->stream));
+  // ---- hoisted input projection into the scratch
+  const __half* hb = reinterpret_cast<const __half*>(blob);
+  const size_t w_off = 0, r_off = (size_t)4 * hidden * in_c, bw_off = r_off + (size_t)4 * hidden * hidden,
+               br_off = bw_off + (size_t)4 * hidden;
+  const int rows = seq_len * batch;
+  noalloc_projection_kernel<<<dim3(ceil_div(4 * hidden, 32), ceil_div(rows, 32)), 256, 0, ctx->stream>>>(
+      (const __half*)x, hb + w_off, hb + bw_off, double_bias ? hb + br_off : nullptr, gx, rows, in_c, 4 * hidden);
+  AIG_LAUNCH_OK(ctx);
+  // ---- recurrence
+  CUtensorMap mR, mY, mH0;
+  int rc = encode_2d(ctx, &mR, hb + r_off, hidden, (uint64_t)4 * hidden, (uint64_t)hidden * 2, kKB, U);
+  if (rc == AIG_OK) rc = encode_3d(ctx, &mY, y, hidden, batch, seq_len, (uint64_t)hidden * 2, (uint64_t)batch * hidden * 2, kKB, kRows);
+  if (rc == AIG_OK) rc = encode_3d(ctx, &mH0, zero_state, hidden, batch, 1, (uint64_t)hidden * 2, (uint64_t)batch * hidden * 2, kKB, kRows);
+  if (rc != AIG_OK) return rc;
+  LstmParams prm{};
+  prm.T = seq_len; prm.B = batch; prm.H = hidden; prm.U = U; prm.NC = NC; prm.groups = 1;
+  prm.clip = clip;
+  prm.gx = gx;
+  prm.gx_sT = (long long)batch * 4 * hidden;
+  prm.gx_sB = (long long)4 * hidden;
+  prm.y = (__half*)y;
+  prm.y_sT = (long long)batch * hidden;
+  prm.y_sB = hidden;
+  prm.c0 = nullptr; prm.hT = nullptr; prm.cT = nullptr;
+  prm.counter = counter;
+  prm.gerr = ctx->d_err;
+  void* args[] = {(void*)&mR, (void*)&mY, (void*)&mH0, (void*)&prm};
+  AIG_CUDA_OK(ctx, cudaLaunchCooperativeKernel((const void*)lstm_recurrent_kernel<U>, dim3(NC), dim3(kThreads), args, smem, ctx->stream));
+  return AIG_OK;
+}
+
+}  // extern "C"

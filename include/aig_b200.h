@@ -231,6 +231,20 @@ int aig_lstm_plan_set_weights(aig_lstm_plan* plan, const aig_half* blob);
 int aig_lstm_forward(aig_lstm_plan* plan, const aig_half* x, aig_half* y, aig_half* h_state,
                      aig_half* c_state, int use_state);
 
+/* No counterpart in the reference.  Single-layer LSTM forward (seq-major x [T][B][in] -> y [T][B][hidden],
+ * zero initial state, one layer's blob as above) that allocates nothing: its scratch (input
+ * projection, zero state, step-barrier counter) is a fixed 2.1 MB array inside the library's device
+ * image, held by every GPU that loads the library until the process exits.  Meant for callers that
+ * may not call cudaMalloc while running -- a frame loop sharing the GPU with the game it plays
+ * (cudaMalloc/cudaFree synchronise the whole device and the game may own almost all memory) or a host
+ * that reserves its device budget up front.  Limits: batch <= 128, hidden a multiple of 64 and <= 512,
+ * in_c a multiple of 8, seq_len*batch*4*hidden <= 524288 (2 MiB of fp32); larger shapes return
+ * AIG_ERR_UNSUPPORTED.  All calls on a device share the array: calls that overlap on the GPU race, so
+ * serialise them; each call clears what must start at zero.  The first call on a device looks up the
+ * array's device address and should come before any stream capture. */
+int aig_lstm_forward_noalloc(aig_ctx* ctx, const aig_half* x, const aig_half* blob, aig_half* y,
+                             int seq_len, int batch, int in_c, int hidden, float clip, int double_bias);
+
 /* ---------------------------------------------------------------------------------------------
  * Multi-head self-attention.  Replaces MultiHeadAttentionLayer (MHALayer.cpp:4-91 constructor,
  * :128-146 Forward: cudnnMultiHeadAttnForward with q = k = v = input, four E x E projection
