@@ -77,6 +77,18 @@ __device__ __forceinline__ float act_apply(float v, int act, float slope) {
   }
 }
 
+// Same activations for the fused epilogues, where the result is rounded to fp16 anyway: exp and the
+// reciprocal go through the special-function unit (ex2.approx / rcp, ~2^-21 relative error) instead of
+// the multi-instruction IEEE sequences.
+__device__ __forceinline__ float act_apply_fast(float v, int act, float slope) {
+  switch (act) {
+    case AIG_ACT_RELU: return v > 0.f ? v : 0.f;
+    case AIG_ACT_SWISH: return v * __frcp_rn(1.0f + __expf(-v));
+    case AIG_ACT_LEAKY: return v < 0.f ? v * slope : v;
+    default: return v;
+  }
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

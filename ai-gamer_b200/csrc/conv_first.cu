@@ -5,6 +5,7 @@
 // output tile is staged in shared memory and each thread produces one output pixel x 32 channels.
 // Output is channels-last fp16 with bias + folded BatchNorm + activation applied.
 #include "aig_common.cuh"
+#include "conv_first_tc.h"
 
 namespace {
 
@@ -166,6 +167,7 @@ struct aig_conv0_plan {
   bool weights_set = false;
   size_t smem = 0;
   dim3 grid;
+  ConvFirstTc* tc = nullptr;  // tensor-core path when the filter geometry has an instantiation
 };
 
 static int conv0_create(aig_ctx* ctx, int batch, int D, int H, int W, int K, int kd, int k, int sd, int s, int pd, int pad,
@@ -205,6 +207,14 @@ static int conv0_create(aig_ctx* ctx, int batch, int D, int H, int W, int K, int
   p.w = pl->w; p.scale = pl->scale; p.shift = pl->shift;
   AIG_CUDA_OK(ctx, cudaFuncSetAttribute(conv_first_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   AIG_CUDA_OK(ctx, cudaFuncSetAttribute(conv_first_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  ConvFirstGeom geo{batch, D, H, W, p.Do, p.Ho, p.Wo, K, kd, k, sd, s, pd, pad, act, slope};
+  if (conv_first_tc_supported(geo)) {
+    const int rc = conv_first_tc_create(ctx, geo, pl->scale, pl->shift, &pl->tc);
+    if (rc != AIG_OK) {
+      aig_conv0_plan_destroy(pl);
+      return rc;
+    }
+  }
   *out = pl;
   return AIG_OK;
 }
@@ -225,6 +235,7 @@ int aig_conv0_plan_destroy(aig_conv0_plan* pl) {
   if (!pl) return AIG_OK;
   DeviceGuard g(pl->ctx->device);
   cudaStreamSynchronize(pl->ctx->stream);
+  conv_first_tc_destroy(pl->tc);
   cudaFree(pl->w);
   cudaFree(pl->scale);
   cudaFree(pl->shift);
@@ -252,6 +263,10 @@ int aig_conv0_plan_set_weights(aig_conv0_plan* pl, const aig_half* w, const aig_
       (const __half*)w, (const __half*)bias, bn_gamma, bn_beta, bn_mean, bn_var, bn_eps, pl->w, pl->scale, pl->shift,
       pl->p.K, pl->p.Kpad, taps);
   AIG_LAUNCH_OK(ctx);
+  if (pl->tc) {
+    const int rc = conv_first_tc_set_weights(pl->tc, (const __half*)w);
+    if (rc != AIG_OK) return rc;
+  }
   pl->weights_set = true;
   return AIG_OK;
 }
@@ -263,6 +278,7 @@ int aig_conv0_forward_bgra(aig_conv0_plan* pl, const uint8_t* bgra, aig_half* y)
   AIG_REQUIRE(ctx, bgra && y && pl->weights_set, "conv0 forward: null pointer or weights not set");
   AIG_REQUIRE(ctx, pl->p.D == 1 && pl->p.kd == 1, "conv0 forward_bgra: 2-D plans only");
   AIG_REQUIRE(ctx, ((uintptr_t)bgra & 3) == 0 && ((uintptr_t)y & 15) == 0, "conv0 forward: misaligned tensors");
+  if (pl->tc) return conv_first_tc_forward(pl->tc, bgra, true, (__half*)y);
   conv_first_kernel<true><<<pl->grid, kTH * kTW, pl->smem, ctx->stream>>>(bgra, (__half*)y, pl->p);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
@@ -274,6 +290,7 @@ int aig_conv0_forward_nchw(aig_conv0_plan* pl, const aig_half* x, aig_half* y) {
   DeviceGuard g(ctx->device);
   AIG_REQUIRE(ctx, x && y && pl->weights_set, "conv0 forward: null pointer or weights not set");
   AIG_REQUIRE(ctx, ((uintptr_t)y & 15) == 0, "conv0 forward: misaligned output");
+  if (pl->tc) return conv_first_tc_forward(pl->tc, x, false, (__half*)y);
   conv_first_kernel<false><<<pl->grid, kTH * kTW, pl->smem, ctx->stream>>>(x, (__half*)y, pl->p);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;

@@ -1,0 +1,318 @@
+// conv_first_tc.cu -- first-layer (3 input channels) convolution on the tensor cores.
+//
+// K = 3*kd*k*k (75 for the 5x5 frame encoder, 81 for the 3x3x3 clip encoder) is too ragged for TMA
+// boxes, so the im2col rows are gathered by 128 producer threads: each builds one output pixel's row
+// (all taps x 3 channels, converted from BGRA bytes with the reference's /255 arithmetic or read from
+// planar fp16) in registers and writes it as 16-byte chunks in the 128-byte-swizzled K-major layout
+// tcgen05.mma expects.  K is padded to 128 (two 64-element blocks); the padding stays zero.
+// The whole weight matrix (out_c x 128) sits in shared memory for the life of the CTA.
+// Warps: 0..3 producers, 4..7 epilogue (TMEM lane quarters 0..3), 8 = MMA issuer + TMEM owner.
+// A tiles and TMEM accumulators are double buffered; every wait is bounded.
+#include "aig_common.cuh"
+#include "conv_first_tc.h"
+
+namespace {
+
+constexpr int kThreads = 288;
+constexpr int kRows = 128;
+constexpr int kABytes = 2 * kRows * 128;  // two K blocks of 128 rows x 128 B
+
+struct TcParams {
+  ConvFirstGeom g;
+  long long total_px;
+  int tiles;
+  int NT;
+  const float* scale;
+  const float* shift;
+  int* gerr;
+};
+
+__device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+template <int KD, int KHW, bool BGRA>
+__global__ void __launch_bounds__(kThreads, 2)
+conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const uint4* __restrict__ wimg, const TcParams p) {
+  constexpr int TAPS = KD * KHW * KHW;
+  constexpr int KTOT = 3 * TAPS;
+  constexpr int NCH = (KTOT + 7) / 8;     // 16-byte chunks per row that carry data
+  constexpr int KSTEPS = (KTOT + 15) / 16;
+  static_assert(KTOT <= 128, "filter too large for the single-tile K");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  uint8_t* sA = sm;                                   // 2 stages x kABytes
+  uint8_t* sB = sA + 2 * kABytes;                     // 2 K blocks x NT rows x 128 B
+  float* s_scale = reinterpret_cast<float*>(sB + 2 * p.NT * 128);
+  float* s_shift = s_scale + 256;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_shift + 256);
+  const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 16, bar_tfull = bar_afull + 32, bar_tempty = bar_afull + 48;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const ConvFirstGeom& g = p.g;
+
+  // one-time staging: zero both A stages (the K padding is never written again), weights, scale/shift
+  for (int i = threadIdx.x; i < 2 * kABytes / 16; i += kThreads) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < 2 * p.NT * 128 / 16; i += kThreads) reinterpret_cast<uint4*>(sB)[i] = wimg[i];
+  for (int i = threadIdx.x; i < p.NT; i += kThreads) {
+    s_scale[i] = p.scale[i];
+    s_shift[i] = p.shift[i];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_afull + 8 * s, kRows);
+      mbar_init(bar_aempty + 8 * s, 1);
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);
+    }
+    *s_abort = 0;
+    fence_mbar_init();
+  }
+  const uint32_t tmem_cols = 2 * p.NT <= 32 ? 32 : (2 * p.NT <= 64 ? 64 : (2 * p.NT <= 128 ? 128 : (2 * p.NT <= 256 ? 256 : 512)));
+  if (warp == 8) {
+    tmem_alloc(smem_u32(s_tmem), tmem_cols);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ producers: one im2col row each
+    const int r = threadIdx.x;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+      const long long px = (long long)tile * kRows + r;
+      const bool valid = px < p.total_px;
+      int ow = 0, oh = 0, od = 0, n = 0;
+      if (valid) {
+        long long t = px;
+        ow = (int)(t % g.Wo); t /= g.Wo;
+        oh = (int)(t % g.Ho); t /= g.Ho;
+        od = (int)(t % g.Do); n = (int)(t / g.Do);
+      }
+      const int iw0 = ow * g.s - g.pad, ih0 = oh * g.s - g.pad, id0 = od * g.sd - g.pd;
+      __align__(16) __half hv[NCH * 8];
+#pragma unroll
+      for (int i = KTOT; i < NCH * 8; ++i) hv[i] = __ushort_as_half((unsigned short)0);
+#pragma unroll
+      for (int fd = 0; fd < KD; ++fd) {
+        const int id = id0 + fd;
+#pragma unroll
+        for (int fr = 0; fr < KHW; ++fr) {
+          const int ih = ih0 + fr;
+          const bool rok = valid && id >= 0 && id < g.D && ih >= 0 && ih < g.H;
+#pragma unroll
+          for (int fs = 0; fs < KHW; ++fs) {
+            const int iw = iw0 + fs;
+            const bool ok = rok && iw >= 0 && iw < g.W;
+            const int t = (fd * KHW + fr) * KHW + fs;
+            if (BGRA) {
+              // bytes B,G,R,A; channels of the network are R,G,B; half(float(u8)/255) == half(float(u8)*(1/255))
+              // for all 256 byte values
+              uint32_t pxl = 0;
+              if (ok) pxl = reinterpret_cast<const uint32_t*>(xin)[((size_t)n * g.H + ih) * g.W + iw];
+              const float k255 = 1.0f / 255.0f;
+              hv[t * 3 + 0] = __float2half_rn((float)((pxl >> 16) & 0xFFu) * k255);
+              hv[t * 3 + 1] = __float2half_rn((float)((pxl >> 8) & 0xFFu) * k255);
+              hv[t * 3 + 2] = __float2half_rn((float)(pxl & 0xFFu) * k255);
+            } else {
+              const __half* src = reinterpret_cast<const __half*>(xin);
+              const size_t plane = (size_t)g.D * g.H * g.W;
+              const size_t off = (((size_t)n * 3) * g.D + id) * g.H * g.W + (size_t)ih * g.W + iw;
+#pragma unroll
+              for (int c = 0; c < 3; ++c) hv[t * 3 + c] = ok ? src[off + c * plane] : __ushort_as_half((unsigned short)0);
+            }
+          }
+        }
+      }
+      if (!mbar_wait_bounded(bar_aempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 601)) break;
+      uint8_t* a = sA + st * kABytes;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j)
+        *reinterpret_cast<uint4*>(a + (j >> 3) * (kRows * 128) + swz(r, j & 7)) = reinterpret_cast<const uint4*>(hv)[j];
+      fence_proxy_async_smem();
+      mbar_arrive(bar_afull + 8 * st);
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(kRows, p.NT);
+      int it = 0;
+      for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait_bounded(bar_tempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 602)) break;
+        if (!mbar_wait_bounded(bar_afull + 8 * st, ph, s_abort, p.gerr, 603)) break;
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(sA) + st * kABytes, b0 = smem_u32(sB);
+#pragma unroll
+        for (int i = 0; i < KSTEPS; ++i) {
+          const int kb = i >> 2, k = i & 3;
+          umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
+                      umma_smem_desc(b0 + kb * (p.NT * 128) + k * 32, 128), idesc, i != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_aempty + 8 * st);
+        umma_commit(bar_tfull + 8 * st);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 4..7)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const bool vec_ok = (g.K & 7) == 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+      const long long px = (long long)tile * kRows + r;
+      const bool valid = px < p.total_px;
+      __half* yrow = y + (size_t)px * g.K;
+      if (!mbar_wait_bounded(bar_tfull + 8 * st, ph, s_abort, p.gerr, 604)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t)(st * p.NT) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.NT; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(t_addr + c0, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int v8 = 0; v8 < 2; ++v8) {
+            const int n0 = c0 + v8 * 8;
+            if (n0 >= g.K) break;
+            if (vec_ok) {
+              uint4 o;
+              __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                oh[e] = __float2half(act_apply_fast(__uint_as_float(v[v8 * 8 + e]) * s_scale[n0 + e] + s_shift[n0 + e], g.act, g.slope));
+              *reinterpret_cast<uint4*>(yrow + n0) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (n0 + e < g.K)
+                  yrow[n0 + e] = __float2half(act_apply_fast(__uint_as_float(v[v8 * 8 + e]) * s_scale[n0 + e] + s_shift[n0 + e], g.act, g.slope));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * st);
+    }
+  }
+
+  if (*s_abort) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// w [K][3][taps] fp16 -> shared-memory image: 2 K blocks x NT rows x 128 B, 128-byte swizzle, K index = tap*3 + c
+__global__ void pack_wimg_kernel(const __half* __restrict__ w, __half* __restrict__ img, int K, int NT, int taps) {
+  const int total = 2 * NT * 64;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int kk = i % 128, n = i / 128;  // kk = K index 0..127, n = output channel row
+    const int kb = kk >> 6, kl = kk & 63;
+    __half v = __ushort_as_half((unsigned short)0);
+    if (n < K && kk < 3 * taps) {
+      const int tap = kk / 3, c = kk - tap * 3;
+      v = w[((size_t)n * 3 + c) * taps + tap];
+    }
+    const size_t off = (size_t)kb * NT * 128 + (size_t)n * 128 + (((kl >> 3) ^ (n & 7)) << 4) + (kl & 7) * 2;
+    *reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(img) + off) = v;
+  }
+}
+
+template <int KD, int KHW>
+int launch_tc(ConvFirstTc* t, const void* x, bool bgra, __half* y);
+
+}  // namespace
+
+struct ConvFirstTc {
+  aig_ctx* ctx = nullptr;
+  TcParams prm{};
+  __half* wimg = nullptr;
+  size_t smem = 0;
+  int grid = 1;
+};
+
+namespace {
+
+template <int KD, int KHW>
+int launch_tc(ConvFirstTc* t, const void* x, bool bgra, __half* y) {
+  aig_ctx* ctx = t->ctx;
+  if (bgra) {
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(conv_first_tc_kernel<KD, KHW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t->smem));
+    conv_first_tc_kernel<KD, KHW, true><<<t->grid, kThreads, t->smem, ctx->stream>>>(x, y, reinterpret_cast<const uint4*>(t->wimg), t->prm);
+  } else {
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(conv_first_tc_kernel<KD, KHW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t->smem));
+    conv_first_tc_kernel<KD, KHW, false><<<t->grid, kThreads, t->smem, ctx->stream>>>(x, y, reinterpret_cast<const uint4*>(t->wimg), t->prm);
+  }
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+}  // namespace
+
+bool conv_first_tc_supported(const ConvFirstGeom& g) {
+  const bool geom = (g.kd == 1 && (g.k == 2 || g.k == 3 || g.k == 5)) || (g.kd == 3 && g.k == 3);
+  return geom && g.K <= 256;
+}
+
+int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scale, const float* shift, ConvFirstTc** out) {
+  *out = nullptr;
+  ConvFirstTc* t = new ConvFirstTc();
+  t->ctx = ctx;
+  TcParams& p = t->prm;
+  p.g = g;
+  p.total_px = (long long)g.batch * g.Do * g.Ho * g.Wo;
+  p.tiles = (int)ceil_div_ll(p.total_px, kRows);
+  p.NT = ceil_div(g.K, 16) * 16;
+  p.scale = scale;
+  p.shift = shift;
+  p.gerr = ctx->d_err;
+  t->smem = (size_t)2 * kABytes + (size_t)2 * p.NT * 128 + 2048 + 256 + 1024;
+  // two CTAs per SM: the gather of one hides behind the conversion / epilogue work of the other
+  t->grid = p.tiles < 2 * ctx->sm_count ? p.tiles : 2 * ctx->sm_count;
+  if (cudaMalloc(&t->wimg, (size_t)2 * p.NT * 128) != cudaSuccess) {
+    delete t;
+    return aig_fail(ctx, AIG_ERR_CUDA, "conv0: weight image allocation failed");
+  }
+  *out = t;
+  return AIG_OK;
+}
+
+void conv_first_tc_destroy(ConvFirstTc* t) {
+  if (!t) return;
+  cudaFree(t->wimg);
+  delete t;
+}
+
+int conv_first_tc_set_weights(ConvFirstTc* t, const __half* w) {
+  aig_ctx* ctx = t->ctx;
+  const int taps = t->prm.g.kd * t->prm.g.k * t->prm.g.k;
+  pack_wimg_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg, t->prm.g.K, t->prm.NT, taps);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int conv_first_tc_forward(ConvFirstTc* t, const void* x, bool bgra, __half* y) {
+  const ConvFirstGeom& g = t->prm.g;
+  if (g.kd == 1 && g.k == 5) return launch_tc<1, 5>(t, x, bgra, y);
+  if (g.kd == 1 && g.k == 3) return launch_tc<1, 3>(t, x, bgra, y);
+  if (g.kd == 1 && g.k == 2) return launch_tc<1, 2>(t, x, bgra, y);
+  if (g.kd == 3 && g.k == 3) return launch_tc<3, 3>(t, x, bgra, y);
+  return aig_fail(t->ctx, AIG_ERR_UNSUPPORTED, "conv0: no tensor-core instantiation for this filter");
+}

@@ -9,8 +9,8 @@
 //     pixels of one output row (tw*segs = 128); each run is one TMA box (BK channels x tw pixels,
 //     element stride = conv stride) whose out-of-range pixels (padding) are zero-filled by TMA.
 //   B (N x K): weights repacked once to [out_c][tap][in_c] (K-major), one TMA box per K block.
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 2..5 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..9 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
 // Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all
 // roles drain to the common exit where TMEM is freed.
 #include <vector>
@@ -20,7 +20,7 @@
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kMaxSegs = 16;
 
 struct IgemmParams {
@@ -87,7 +87,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 4);
+      mbar_init(bar_tempty + 8 * a, 8);
     }
     *s_abort = 0;
     fence_mbar_init();
@@ -170,8 +170,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    // two warps per TMEM lane quarter, each taking half of the tile's columns: the activation math of one
+    // warp hides behind the TMEM loads and stores of the other on the same scheduler
     const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int col_lo = ((warp - 2) >> 2) * (NT / 2), col_hi = col_lo + NT / 2;
     const int row_in_tile = q * 32 + lane;
     const bool vec_ok = (p.out_c & 7) == 0;
     int it = 0;
@@ -197,13 +200,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t)(acc * NT) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 0; c0 < NT; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_addr + c0, r);
+      for (int c0 = col_lo; c0 < col_hi; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x16(t_addr + c0, r);
         tmem_ld_wait();
         if (valid) {
 #pragma unroll
-          for (int v8 = 0; v8 < 4; ++v8) {
+          for (int v8 = 0; v8 < 2; ++v8) {
             const int nl = c0 + v8 * 8;           // column inside the N tile
             const int n = n_tile * NT + nl;       // output channel
             if (n >= p.out_c) break;
@@ -241,7 +244,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               uint4 o;
               __half* oh = reinterpret_cast<__half*>(&o);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) oh[e] = __float2half(act_apply(v[e], p.act, p.slope));
+              for (int e = 0; e < 8; ++e) oh[e] = __float2half(act_apply_fast(v[e], p.act, p.slope));
               *reinterpret_cast<uint4*>(yrow + n) = o;
             } else {
 #pragma unroll
@@ -249,7 +252,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
                 if (n + e < p.out_c) {
                   float a = v[e];
                   if (rrow) a = __half2float(__float2half(__half2float(__float2half(a)) + __half2float(rrow[n + e])));
-                  yrow[n + e] = __float2half(act_apply(a, p.act, p.slope));
+                  yrow[n + e] = __float2half(act_apply_fast(a, p.act, p.slope));
                 }
               }
             }
