@@ -121,11 +121,42 @@ SIGNATURES.update({
     "aig_cnn_site_flops": [P, c_int],
     "aig_cnn_site_bytes": [P, c_int],
 })
+
+
+class SeqConfig(ctypes.Structure):
+    _fields_ = [("batch", c_int), ("seq_len", c_int), ("in_c", c_int), ("hidden", c_int), ("layers", c_int), ("heads", c_int),
+                ("n_out", c_int), ("n_sigmoid", c_int), ("rope_base", c_float), ("window", c_int)]
+
+
+SIGNATURES.update({
+    "aig_seq_create": [P, ctypes.POINTER(SeqConfig), PP],
+    "aig_seq_destroy": [P],
+    "aig_seq_last_error": [P],
+    "aig_seq_param_bytes": [ctypes.POINTER(SeqConfig)],
+    "aig_seq_load_memory": [P, P, c_size_t],
+    "aig_seq_forward": [P, P, c_int],
+    "aig_seq_step": [P, P],
+    "aig_seq_reset": [P],
+    "aig_seq_outputs_half": [P],
+    "aig_seq_outputs_f32": [P],
+    "aig_seq_lstm_output": [P],
+    "aig_agent_create": [P, ctypes.POINTER(CnnConfig), ctypes.POINTER(SeqConfig), PP],
+    "aig_agent_destroy": [P],
+    "aig_agent_last_error": [P],
+    "aig_agent_param_bytes": [ctypes.POINTER(CnnConfig), ctypes.POINTER(SeqConfig)],
+    "aig_agent_load_memory": [P, P, c_size_t],
+    "aig_agent_step": [P, P],
+    "aig_agent_step_host": [P, P, P],
+    "aig_agent_reset": [P],
+    "aig_agent_outputs_f32": [P],
+})
 _RESTYPES = {"aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
              "aig_cnn_site_flops": ctypes.c_double, "aig_cnn_site_bytes": ctypes.c_double,
-             "aig_lstm_weight_count": c_size_t}
+             "aig_lstm_weight_count": c_size_t, "aig_seq_last_error": ctypes.c_char_p, "aig_seq_param_bytes": c_size_t,
+             "aig_seq_outputs_half": c_void_p, "aig_seq_outputs_f32": c_void_p, "aig_seq_lstm_output": c_void_p,
+             "aig_agent_last_error": ctypes.c_char_p, "aig_agent_param_bytes": c_size_t, "aig_agent_outputs_f32": c_void_p}
 
 _lib = None
 

@@ -142,6 +142,31 @@ def make_seq_params(seed=0, d=512, hid=512, layers=2, heads=8, n_out=18):
     return p
 
 
+def serialize_seq_params(p):
+    """Sequence-head blob in layer order: LSTM blob (LSTMLayer.cpp:139-146), MHA wq,wk,wv,wo
+    (MHALayer.cpp:191-210), LayerNorm gamma,beta (LayerNorm.cpp:50-61), FC W,b (FCLayer.cpp:70-81)."""
+    parts = [np.ascontiguousarray(p["lstm"], F16).tobytes()]
+    parts += [np.ascontiguousarray(p[k], F16).tobytes() for k in ("wq", "wk", "wv", "wo")]
+    parts += [np.ascontiguousarray(p["ln_g"], np.float32).tobytes(), np.ascontiguousarray(p["ln_b"], np.float32).tobytes()]
+    parts += [np.ascontiguousarray(p["fcW"], F16).tobytes(), np.ascontiguousarray(p["fcb"], F16).tobytes()]
+    return b"".join(parts)
+
+
+def make_agent_params(seed=0, widths=(32, 64, 128, 256, 256), d=512, layers=2, heads=8, n_out=18):
+    """Streaming agent = frame encoder + bridge FC (features -> d) + sequence head."""
+    rng = np.random.default_rng(seed + 17)
+    cnn = make_cnn_params(seed, widths=widths, n_out=n_out)
+    seq = make_seq_params(seed + 1, d=d, hid=d, layers=layers, heads=heads, n_out=n_out)
+    bw = xavier_uniform(rng, (widths[-1], d), widths[-1], d)
+    bb = np.zeros(d, F16)
+    return dict(cnn=cnn, seq=seq, bw=bw, bb=bb)
+
+
+def serialize_agent_params(p, width, height):
+    return b"".join([serialize_cnn_checkpoint(p["cnn"], width, height), p["bw"].tobytes(), p["bb"].tobytes(),
+                     serialize_seq_params(p["seq"])])
+
+
 def make_embeddings(seed, T, B, d):
     rng = np.random.default_rng(seed + 3000003)
     return rng.standard_normal((T, B, d)).astype(F16)

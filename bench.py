@@ -112,6 +112,32 @@ def cpu_oracle_rate(frames_per_sample, repeats):
     return frames_per_sample / float(np.median(times)), times
 
 
+def streaming_latency(pkg, ctx, SY, n_frames):
+    """p50/p99 frame->action latency of the full streaming agent at batch 1: pinned host frame in,
+    fp32 outputs on the host out (aig_agent_step_host), one frame at a time, carried LSTM state and
+    a 64-slot attention ring cache."""
+    import torch
+    from ai_gamer_b200 import runners as R
+
+    agent = R.Agent(ctx, 1, HEIGHT, WIDTH, widths=WIDTHS, d=512, layers=2, heads=8, n_out=N_OUT, n_sigmoid=N_SIG, window=64)
+    agent.load_bytes(SY.serialize_agent_params(SY.make_agent_params(0, widths=WIDTHS), WIDTH, HEIGHT))
+    rng = np.random.default_rng(7)
+    frames = [torch.from_numpy(rng.integers(0, 256, (1, HEIGHT, WIDTH, 4), dtype=np.uint8)).pin_memory() for _ in range(8)]
+    out = torch.empty((1, N_OUT), dtype=torch.float32).pin_memory()
+    for i in range(20):
+        agent.step_host(frames[i % 8], out)
+    agent.reset()
+    lat = []
+    for i in range(n_frames):
+        t0 = time.perf_counter()
+        agent.step_host(frames[i % 8], out)
+        lat.append((time.perf_counter() - t0) * 1e3)
+    agent.close()
+    lat = np.array(lat)
+    return {"workload": "streaming agent (cnn + fc + 2xLSTM512 + MHA8x64 ring-64 + LN + FC), batch 1, %d frames" % n_frames,
+            "p50_ms": float(np.percentile(lat, 50)), "p99_ms": float(np.percentile(lat, 99)), "mean_ms": float(lat.mean())}
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's layer math on the host cores (oracle port)."""
     if rank != 0:
@@ -149,6 +175,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for short profiler captures)")
+    ap.add_argument("--no-latency", action="store_true", help="skip the batch-1 streaming latency leg")
+    ap.add_argument("--latency-frames", type=int, default=1000)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -235,6 +263,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
 
+    latency = None
+    if rank == 0 and not args.no_latency:
+        latency = streaming_latency(pkg, ctx, SY, args.latency_frames)
+
     if rank == 0:
         peaks = measured_peaks()
         value = world * B * args.steps / (ms * 1e-3)
@@ -245,6 +277,7 @@ def main():
                            "gbs": round(nbytes_ / (lms * 1e-3) / 1e9, 1) if lms > 0 else None})
         conv_sites = [(n, m_, f) for n, m_, f, _ in sites if f > 0 and m_ > 0]
         top = max(conv_sites, key=lambda r: r[1])
+        top_kernel = "conv_first_tc_kernel (tcgen05)" if top[0].startswith("conv0") else "igemm_kernel (tcgen05)"
         achieved = top[2] / (top[1] * 1e-3) / 1e12
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
@@ -262,7 +295,8 @@ def main():
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": B * HEIGHT * WIDTH * 4,
                     "d2h_bytes_per_step": B * N_OUT * 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": args.steps * enc.kernel_launches,
-            "roofline": {"bound": "tensor", "kernel": "igemm_kernel (tcgen05) @ " + top[0], "achieved": achieved, "peak": peaks["tensor"],
+            "latency": latency,
+            "roofline": {"bound": "tensor", "kernel": top_kernel + " @ " + top[0], "achieved": achieved, "peak": peaks["tensor"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tensor"], "traffic": traffic, "peak_source": peaks["source"] + " (sustained bf16)",
                          "whole_step_tflops": FLOP_PER_FRAME * B / (ms / args.steps * 1e-3) / 1e12,
                          "whole_step_frac": FLOP_PER_FRAME * B / (ms / args.steps * 1e-3) / 1e12 / peaks["tensor"]},

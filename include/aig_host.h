@@ -66,6 +66,49 @@ const char* aig_cnn_site_name(aig_cnn* m, int i);
 double aig_cnn_site_flops(aig_cnn* m, int i);
 double aig_cnn_site_bytes(aig_cnn* m, int i);
 
+/* ---------------------------------------------------------------------------------------------
+ * Sequence head: LSTMLayer (layers x hidden, double bias, clip 5) -> MultiHeadAttentionLayer (causal,
+ * heads x 64, optional RoPE, optional sliding window) -> row LayerNorm (eps 1e-5) -> FCLayer ->
+ * sigmoid on the first n_sigmoid outputs / tanh on the rest, chained like NN::Forward chains layers.
+ * seq_len <= 128; hidden a multiple of 64, <= 512, hidden / heads == 64; in_c a multiple of 16. */
+typedef struct aig_seq_config {
+  int batch, seq_len;
+  int in_c, hidden, layers, heads;
+  int n_out, n_sigmoid;
+  float rope_base; /* 0 = no rotary embedding */
+  int window;      /* attention window in steps = ring cache slots; <= 0: whole sequence (cache of seq_len slots) */
+} aig_seq_config;
+typedef struct aig_seq aig_seq;
+int aig_seq_create(aig_ctx* ctx, const aig_seq_config* cfg, aig_seq** out);
+int aig_seq_destroy(aig_seq* m);
+const char* aig_seq_last_error(aig_seq* m);
+size_t aig_seq_param_bytes(const aig_seq_config* cfg);
+/* Parameters in layer order: LSTM blob, MHA wq/wk/wv/wo, LayerNorm gamma/beta, FC W/b (host memory). */
+int aig_seq_load_memory(aig_seq* m, const void* blob, size_t bytes);
+/* Full sequence: emb [batch][seq_len][in_c] fp16 (device); positions pos0 .. pos0+seq_len-1. */
+int aig_seq_forward(aig_seq* m, const aig_half* emb, int pos0);
+/* Streaming: one new step per sequence, emb_t [batch][in_c]; LSTM state and the ring cache carry over. */
+int aig_seq_step(aig_seq* m, const aig_half* emb_t);
+int aig_seq_reset(aig_seq* m);
+const aig_half* aig_seq_outputs_half(aig_seq* m); /* [batch][seq_len][n_out] (forward) or [batch][n_out] (step) */
+const float* aig_seq_outputs_f32(aig_seq* m);
+const aig_half* aig_seq_lstm_output(aig_seq* m);  /* top-layer h, [batch][seq_len][hidden] / [batch][hidden] */
+
+/* ---------------------------------------------------------------------------------------------
+ * Streaming agent: frame encoder -> FC (features -> in_c) -> sequence head step; one call per frame,
+ * the loop body of Infer::Inference (Infer.cpp:96-114).  The two configs must have the same batch. */
+typedef struct aig_agent aig_agent;
+int aig_agent_create(aig_ctx* ctx, const aig_cnn_config* cnn, const aig_seq_config* seq, aig_agent** out);
+int aig_agent_destroy(aig_agent* a);
+const char* aig_agent_last_error(aig_agent* a);
+size_t aig_agent_param_bytes(const aig_cnn_config* cnn, const aig_seq_config* seq);
+/* Blob: encoder checkpoint, bridge FC (half W[feat][in_c], half b[in_c]), sequence head blob. */
+int aig_agent_load_memory(aig_agent* a, const void* blob, size_t bytes);
+int aig_agent_step(aig_agent* a, const uint8_t* bgra_dev);
+int aig_agent_step_host(aig_agent* a, const uint8_t* bgra_host, float* out_host);
+int aig_agent_reset(aig_agent* a);
+const float* aig_agent_outputs_f32(aig_agent* a);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,92 @@
+"""GPU parity of the host-side runners for the sequence head (LSTM -> MHA -> LayerNorm -> FC) and
+the streaming agent (frame encoder -> FC -> sequence-head step with carried state and ring cache)
+against the oracle compositions.  Streaming must reproduce the full-sequence forward step by step."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from oracle import pipelines as PL
+
+gpu = pytest.mark.gpu
+TOL = 2e-2  # relative tolerance on the outputs (fp16 compute), see the north-star statement
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from tests import gpu_util as U
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return U
+
+
+def _seq_head(U, batch, seq_len, d, heads, window):
+    from ai_gamer_b200 import runners as R
+
+    return R.SeqHead(U.ctx(), batch, seq_len, in_c=d, hidden=d, layers=2, heads=heads, rope_base=10000.0, window=window)
+
+
+@gpu
+def test_sequence_head_full_and_streaming(env):
+    U = env
+    U.pkg()
+    B, T, d, heads = 4, 16, 128, 2
+    p = PL.make_seq_params(5, d=d, hid=d, layers=2, heads=heads)
+    emb = PL.make_embeddings(5, T, B, d)                    # [T][B][d]
+    y, a, logits, want = PL.seq_forward(p, emb, rope_base=10000.0, window=0)
+    head = _seq_head(U, B, T, d, heads, 0)
+    blob = PL.serialize_seq_params(p)
+    assert len(blob) == head.param_bytes()
+    head.load_bytes(blob)
+    emb_bt = np.ascontiguousarray(emb.transpose(1, 0, 2))    # the runner is batch-major
+    head.forward(U.dev(emb_bt))
+    got_y = U.host(head.lstm_output())
+    assert np.abs(got_y.astype(np.float32) - y.transpose(1, 0, 2).astype(np.float32)).max() < 6e-3
+    got = U.host(head.outputs_f32())
+    assert U.rel_err(got, want.astype(np.float32), 0.05).max() < TOL
+    # streaming: the same sequence one frame at a time
+    outs = []
+    for t in range(T):
+        head.step(U.dev(np.ascontiguousarray(emb[t])))
+        outs.append(U.host(head.outputs_f32(step=True)))
+    got_s = np.stack(outs, axis=1)
+    assert U.rel_err(got_s, want.astype(np.float32), 0.05).max() < TOL
+    assert np.abs(got_s - got).max() < 5e-3, "streaming and full-sequence forward disagree"
+    # reset starts a new sequence
+    head.reset()
+    head.step(U.dev(np.ascontiguousarray(emb[0])))
+    assert np.abs(U.host(head.outputs_f32(step=True)) - got_s[:, 0]).max() < 1e-6
+    head.close()
+
+
+@gpu
+def test_streaming_agent_matches_oracle(env):
+    U = env
+    import torch
+
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    B, H, W, widths, d, heads, window, steps = 2, 32, 64, (32, 64), 128, 2, 8, 12
+    p = PL.make_agent_params(3, widths=widths, d=d, layers=2, heads=heads)
+    frames = [PL.make_frames(100 + t, B, H, W) for t in range(steps)]
+    emb = np.stack([O.fc(PL.cnn_forward(p["cnn"], f)[0], p["bw"], p["bb"]) for f in frames])   # [T][B][d]
+    _, _, _, want = PL.seq_forward(p["seq"], emb, rope_base=10000.0, window=window)             # [B][T][n_out]
+    agent = R.Agent(U.ctx(), B, H, W, widths=widths, d=d, layers=2, heads=heads, window=window)
+    blob = PL.serialize_agent_params(p, W, H)
+    assert len(blob) == agent.param_bytes()
+    agent.load_bytes(blob)
+    outs = []
+    for t in range(steps):
+        agent.step(U.dev(frames[t]))
+        outs.append(U.host(agent.outputs_f32()))
+    got = np.stack(outs, axis=1)
+    assert U.rel_err(got, want.astype(np.float32), 0.05).max() < TOL
+    # the host-buffer frame step returns the same numbers
+    agent.reset()
+    out_h = torch.empty((B, 18), dtype=torch.float32).pin_memory()
+    for t in range(3):
+        agent.step_host(torch.from_numpy(frames[t]).pin_memory(), out_h)
+        assert np.array_equal(out_h.numpy(), got[:, t])
+    agent.close()
