@@ -59,6 +59,7 @@ SIGNATURES = {
     "aig_spatial_mask_forward": [P, P, P, c_float, P, c_int, c_int, c_int],
     "aig_global_avgpool_nhwc": [P, P, P, c_int, c_int, c_int],
     "aig_adaptive_avgpool3d_ndhwc": [P, P, P] + [c_int] * 7,
+    "aig_cnn_head_forward": [P, P, P, c_float, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int],
     "aig_conv_plan_create": [P, ctypes.POINTER(ConvDesc), PP],
     "aig_conv_plan_destroy": [P],
     "aig_conv_plan_out_dims": [P, PI, PI, PI],
@@ -109,6 +110,8 @@ SIGNATURES.update({
     "aig_cnn_forward": [P, P],
     "aig_cnn_forward_graph": [P, P],
     "aig_cnn_infer_host": [P, P, P],
+    "aig_cnn_submit_host": [P, c_int, P, P],
+    "aig_cnn_wait": [P, c_int],
     "aig_cnn_outputs_half": [P],
     "aig_cnn_outputs_f32": [P],
     "aig_cnn_features": [P],
@@ -376,6 +379,12 @@ class CnnEncoder:
 
     def infer_host(self, bgra_host, out_host):
         self.check(lib().aig_cnn_infer_host(self.handle, ptr(bgra_host), ptr(out_host)))
+
+    def submit_host(self, slot, bgra_host, out_host):
+        self.check(lib().aig_cnn_submit_host(self.handle, slot, ptr(bgra_host), ptr(out_host)))
+
+    def wait(self, slot):
+        self.check(lib().aig_cnn_wait(self.handle, slot))
 
     def _view(self, addr, shape, dtype):
         import torch

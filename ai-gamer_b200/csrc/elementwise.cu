@@ -477,6 +477,51 @@ __global__ void adaptive_avgpool3d_kernel(const __half* __restrict__ x, __half* 
   }
 }
 
+// Fused output head of the frame encoder, one CTA per frame: mask attention (x . w1 + b1 -> sigmoid ->
+// x*m), global average pool, FC with the reference's two roundings (FCLayer.cpp:50-51), sigmoid on the
+// first n_sig outputs / tanh on the rest (Sigmoid.cpp:8-12), fp16 and fp32 results.  Same arithmetic
+// and rounding points as the stand-alone kernels above; x is read once from HBM.
+__global__ void cnn_head_kernel(const __half* __restrict__ x, const __half* __restrict__ w1, float b1,
+                                const __half* __restrict__ fcw, const __half* __restrict__ fcb, __half* __restrict__ feat,
+                                __half* __restrict__ out_h, float* __restrict__ out_f, int HW, int C, int n_out, int n_sig) {
+  extern __shared__ uint8_t head_smem[];
+  __half* sx = reinterpret_cast<__half*>(head_smem);                 // [HW][C]
+  float* s_mask = reinterpret_cast<float*>(sx + (size_t)HW * C);     // [HW]
+  float* s_pool = s_mask + HW;                                       // [C]
+  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+  const __half* xb = x + (size_t)b * HW * C;
+  const int nvec = HW * C / 8;
+  for (int i = tid; i < nvec; i += blockDim.x) reinterpret_cast<uint4*>(sx)[i] = reinterpret_cast<const uint4*>(xb)[i];
+  __syncthreads();
+  for (int p = warp; p < HW; p += nwarps) {
+    float s = 0.f;
+    for (int c = lane; c < C; c += 32) s += __half2float(sx[p * C + c]) * __half2float(w1[c]);
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) s_mask[p] = 1.0f / (1.0f + expf(-(s + b1)));
+  }
+  __syncthreads();
+  for (int c = tid; c < C; c += blockDim.x) {
+    float s = 0.f;
+    for (int p = 0; p < HW; ++p) s += __half2float(__float2half(__half2float(sx[p * C + c]) * s_mask[p]));
+    const __half h = __float2half(s / (float)HW);
+    feat[(size_t)b * C + c] = h;
+    s_pool[c] = __half2float(h);
+  }
+  __syncthreads();
+  for (int o = warp; o < n_out; o += nwarps) {
+    float acc = 0.f;
+    for (int c = lane; c < C; c += 32) acc = fmaf(s_pool[c], __half2float(fcw[(size_t)c * n_out + o]), acc);
+    for (int k = 16; k > 0; k >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, k);
+    if (lane == 0) {
+      const float t = __half2float(__float2half(acc));
+      const float y = __half2float(__float2half(t + (fcb ? __half2float(fcb[o]) : 0.f)));
+      const __half v = o < n_sig ? __float2half(1.0f / (1.0f + expf(-y))) : __float2half(tanhf(y));
+      out_h[(size_t)b * n_out + o] = v;
+      out_f[(size_t)b * n_out + o] = __half2float(v);
+    }
+  }
+}
+
 }  // namespace
 
 // ============================================================================================
@@ -698,6 +743,24 @@ int aig_global_avgpool_nhwc(aig_ctx* ctx, const aig_half* x_nhwc, aig_half* y, i
   if (batch == 0) return AIG_OK;
   global_avgpool_nhwc_kernel<<<grid_for(ctx, (long long)batch * c), kThreads, 0, ctx->stream>>>(
       (const __half*)x_nhwc, (__half*)y, batch, hw, c);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int aig_cnn_head_forward(aig_ctx* ctx, const aig_half* x_nhwc, const aig_half* mask_w, float mask_b, const aig_half* fc_w,
+                         const aig_half* fc_b, aig_half* feat, aig_half* out_half, float* out_f32, int batch, int hw, int c,
+                         int n_out, int n_sigmoid) {
+  AIG_ENTER(ctx);
+  AIG_REQUIRE(ctx, x_nhwc && mask_w && fc_w && feat && out_half && out_f32, "aig_cnn_head_forward: null pointer");
+  AIG_REQUIRE(ctx, batch >= 0 && hw > 0 && c > 0 && n_out > 0 && n_sigmoid >= 0 && n_sigmoid <= n_out && (hw * c) % 8 == 0,
+              "aig_cnn_head_forward: bad extents");
+  const size_t smem = (size_t)hw * c * 2 + (size_t)(hw + c) * 4;
+  if (smem > 200 * 1024) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "aig_cnn_head_forward: %d x %d feature map does not fit shared memory", hw, c);
+  if (batch == 0) return AIG_OK;
+  AIG_CUDA_OK(ctx, cudaFuncSetAttribute(cnn_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  cnn_head_kernel<<<batch, 256, smem, ctx->stream>>>((const __half*)x_nhwc, (const __half*)mask_w, mask_b, (const __half*)fc_w,
+                                                     (const __half*)fc_b, (__half*)feat, (__half*)out_half, out_f32, hw, c, n_out,
+                                                     n_sigmoid);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }

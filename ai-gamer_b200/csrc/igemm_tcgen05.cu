@@ -5,10 +5,14 @@
 //
 // GEMM view: M = output pixels (batch*Do*Ho*Wo), N = output channels, K = taps * input channels.
 //   A (M x K): never materialised.  The input is channels-last [N][D][H][W][C]; for one filter tap and
-//     one block of BK channels, the rows of an M tile are `segs` runs of `tw` consecutive output
-//     pixels of one output row (tw*segs = 128); each run is one TMA box (BK channels x tw pixels,
-//     element stride = conv stride) whose out-of-range pixels (padding) are zero-filled by TMA.
+//     one block of BK channels, the rows of a 128-row sub-tile are `segs` runs of `tw` consecutive
+//     output pixels of one output row (tw*segs = 128); each run is one TMA box (BK channels x tw
+//     pixels, element stride = conv stride) whose out-of-range pixels (padding) are zero-filled by TMA.
 //   B (N x K): weights repacked once to [out_c][tap][in_c] (K-major), one TMA box per K block.
+// A CTA tile is MS sub-tiles of 128 rows that share every weight block: operand traffic from L2, not
+// the tensor pipe, bounds these layers (measured ~22 B/clk/SM), the weight block is up to 2/3 of a
+// stage, and a tcgen05.mma costs the same ~200 clk for N = 64 as for N = 256, so sub-tiles are added
+// until the MS accumulators fill the 256 TMEM columns of one buffer.
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2..9 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
 // Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all
@@ -22,13 +26,15 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kNumThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 constexpr int kMaxSegs = 16;
+constexpr int kMaxSub = 4;
+constexpr int kSmemBudget = 227 * 1024 - 1024 /*align*/ - 2048 /*scale,shift*/ - 256 /*barriers*/;
 
 struct IgemmParams {
   int num_kb, cblocks, taps_hw, kw;           // K loop: kb -> (tap, cblock); tap -> (fd, fr, fs)
   int sd, sh, sw, pd, ph, pw;
   int DoHo, Ho, Wo;
   int tw, segs, segs_per_row, total_rows;
-  int m_tiles, n_tiles;
+  int m_super, n_tiles;                       // CTA tiles along M (MS sub-tiles each) and along N
   int out_c;
   int act, two_step;
   float slope;
@@ -40,21 +46,154 @@ struct IgemmParams {
   int* gerr;
 };
 
-template <int NT, int BK>
+template <int NT, int BK, int MS>
 struct IgemmCfg {
-  static constexpr int kABytes = kTileM * BK * 2;
+  static constexpr int kSubBytes = kTileM * BK * 2;
+  static constexpr int kABytes = MS * kSubBytes;
   static constexpr int kBBytes = NT * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+  static constexpr int kStagesRaw = kSmemBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kTmemCols = 2 * NT < 32 ? 32 : 2 * NT;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 2048 /*scale,shift*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = 2 * MS * NT < 32 ? 32 : 2 * MS * NT;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 2048 + 256;
+  static_assert(kStages >= 2, "tile too large for a two-stage pipeline");
+  static_assert(kTmemCols <= 512, "accumulators exceed TMEM");
 };
 
-template <int NT, int BK>
+// ---- specialised epilogue for the common case (scale/shift + optional residual + activation, fp16
+// vector stores).  Everything that does not change inside a tile is a template parameter, so one
+// output element costs an FFMA, the activation and half a packed convert instead of a chain of
+// run-time mode checks; scale/shift arrive as float4 loads that overlap the TMEM load.
+template <int ACT>
+__device__ __forceinline__ float act_ct(float v, float slope) {
+  if (ACT == AIG_ACT_RELU) return fmaxf(v, 0.f);
+  if (ACT == AIG_ACT_SWISH) return v * __frcp_rn(1.0f + __expf(-v));
+  if (ACT == AIG_ACT_LEAKY) return v < 0.f ? v * slope : v;
+  return v;
+}
+
+template <int ACT, bool RES>
+__device__ __forceinline__ void epi_fused_cols(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
+                                               const float* __restrict__ sc, const float* __restrict__ sf,
+                                               const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
+                                               bool valid) {
+#pragma unroll 1
+  for (int c0 = col_lo; c0 < col_hi; c0 += 16) {
+    uint32_t r[16];
+    tmem_ld_32x16(t_addr + c0, r);
+    float s[16], h[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = reinterpret_cast<const float4*>(sc + c0)[i];
+      const float4 b = reinterpret_cast<const float4*>(sf + c0)[i];
+      s[4 * i] = a.x; s[4 * i + 1] = a.y; s[4 * i + 2] = a.z; s[4 * i + 3] = a.w;
+      h[4 * i] = b.x; h[4 * i + 1] = b.y; h[4 * i + 2] = b.z; h[4 * i + 3] = b.w;
+    }
+    const int n0 = n_base + c0;
+    uint4 rv[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (RES && valid) {
+      if (n0 < out_c) rv[0] = *reinterpret_cast<const uint4*>(rrow + n0);
+      if (n0 + 8 < out_c) rv[1] = *reinterpret_cast<const uint4*>(rrow + n0 + 8);
+    }
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+      for (int v8 = 0; v8 < 2; ++v8) {
+        if (n0 + v8 * 8 >= out_c) break;
+        const __half2* rh = reinterpret_cast<const __half2*>(&rv[v8]);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+          const int e = v8 * 8 + e2 * 2;
+          float a0 = fmaf(__uint_as_float(r[e]), s[e], h[e]);
+          float a1 = fmaf(__uint_as_float(r[e + 1]), s[e + 1], h[e + 1]);
+          if (RES) {
+            // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
+            const float2 m = __half22float2(__floats2half2_rn(a0, a1));
+            const float2 rr = __half22float2(rh[e2]);
+            const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+            a0 = t.x;
+            a1 = t.y;
+          }
+          oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+        }
+        *reinterpret_cast<uint4*>(yrow + n0 + v8 * 8) = o;
+      }
+    }
+  }
+}
+
+// Generic epilogue: the reference's two-step rounding, fp32 output, or channel counts that are not a
+// multiple of 8 (scalar stores).  Rare paths; run-time checks are acceptable here.
+__device__ __forceinline__ void epi_generic_cols(uint32_t t_addr, int col_lo, int col_hi, int n_base, const IgemmParams& p,
+                                                 const float* sc, const float* sf, const __half* rrow, __half* yrow,
+                                                 float* y32row, bool valid) {
+  const bool vec_ok = (p.out_c & 7) == 0;
+#pragma unroll 1
+  for (int c0 = col_lo; c0 < col_hi; c0 += 16) {
+    uint32_t r[16];
+    tmem_ld_32x16(t_addr + c0, r);
+    tmem_ld_wait();
+    if (!valid) continue;
+#pragma unroll
+    for (int v8 = 0; v8 < 2; ++v8) {
+      const int nl = c0 + v8 * 8;
+      const int n = n_base + nl;
+      if (n >= p.out_c) break;
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float a = __uint_as_float(r[v8 * 8 + e]);
+        if (p.two_step) {
+          a = __half2float(__float2half(a));
+          a = __half2float(__float2half(a + sf[nl + e]));  // shift == bias: no BatchNorm in this mode
+        } else {
+          a = a * sc[nl + e] + sf[nl + e];
+        }
+        v[e] = a;
+      }
+      if (y32row) {
+        float* o32 = y32row + n;
+        if (vec_ok) {
+          *reinterpret_cast<float4*>(o32) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(o32 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            if (n + e < p.out_c) o32[e] = v[e];
+        }
+      } else if (vec_ok) {
+        if (rrow) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(rrow + n);
+          const __half* rh = reinterpret_cast<const __half*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            v[e] = __half2float(__float2half(__half2float(__float2half(v[e])) + __half2float(rh[e])));
+        }
+        uint4 o;
+        __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) oh[e] = __float2half(act_apply_fast(v[e], p.act, p.slope));
+        *reinterpret_cast<uint4*>(yrow + n) = o;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (n + e < p.out_c) {
+            float a = v[e];
+            if (rrow) a = __half2float(__float2half(__half2float(__float2half(a)) + __half2float(rrow[n + e])));
+            yrow[n + e] = __float2half(act_apply_fast(a, p.act, p.slope));
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int NT, int BK, int MS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const IgemmParams p) {
-  using Cfg = IgemmCfg<NT, BK>;
+  using Cfg = IgemmCfg<NT, BK, MS>;
   constexpr int kStages = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -103,7 +242,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.m_super * p.n_tiles;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -112,10 +251,11 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int n_tile = tile % p.n_tiles, m_tile = tile / p.n_tiles;
-        int seg_n[kMaxSegs], seg_z[kMaxSegs], seg_y[kMaxSegs], seg_x[kMaxSegs];
-        for (int s = 0; s < p.segs; ++s) {
-          const int g = m_tile * p.segs + s;
+        const int n_tile = tile % p.n_tiles, m_sup = tile / p.n_tiles;
+        int seg_n[MS * kMaxSegs], seg_z[MS * kMaxSegs], seg_y[MS * kMaxSegs], seg_x[MS * kMaxSegs];
+        const int nseg = MS * p.segs;
+        for (int s = 0; s < nseg; ++s) {
+          const int g = m_sup * nseg + s;  // sub-tile (m_sup*MS + s/segs), run s%segs
           const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
           const int n = row / p.DoHo, r2 = row - n * p.DoHo;
           const int od = r2 / p.Ho, oh = r2 - od * p.Ho;
@@ -130,11 +270,12 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const int fr = rem / p.kw, fs = rem - fr * p.kw;
           if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, s_abort, p.gerr, 101)) { ok = false; break; }
           mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
+          // the weight block first: every sub-tile's MMAs need it
+          tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
           const uint32_t a_dst = sA + stage * Cfg::kABytes;
-          for (int s = 0; s < p.segs; ++s)
+          for (int s = 0; s < nseg; ++s)
             tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
                         seg_z[s] + fd, seg_n[s]);
-          tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -152,16 +293,18 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 201)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * NT);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait_bounded(bar_full + 8 * stage, phase, s_abort, p.gerr, 202)) { ok = false; break; }
-          tc_fence_after();
           const uint32_t a0 = sA + stage * Cfg::kABytes, b0 = sB + stage * Cfg::kBBytes;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = umma_smem_desc(a0 + k * 32, BK * 2);
-            const uint64_t bdesc = umma_smem_desc(b0 + k * 32, BK * 2);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int sub = 0; sub < MS; ++sub) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adesc = umma_smem_desc(a0 + sub * Cfg::kSubBytes + k * 32, BK * 2);
+              const uint64_t bdesc = umma_smem_desc(b0 + k * 32, BK * 2);
+              umma_f16_ss(d_tmem + (uint32_t)(sub * NT), adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -176,87 +319,44 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     const int col_lo = ((warp - 2) >> 2) * (NT / 2), col_hi = col_lo + NT / 2;
     const int row_in_tile = q * 32 + lane;
-    const bool vec_ok = (p.out_c & 7) == 0;
+    const bool fast = (p.out_c & 7) == 0 && !p.two_step && !p.y32;
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const int n_tile = tile % p.n_tiles, m_tile = tile / p.n_tiles;
+      const int n_tile = tile % p.n_tiles, m_sup = tile / p.n_tiles;
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       // scale/shift: staged in shared memory when there is a single N tile, else read from global
       const float* sc = p.n_tiles == 1 ? s_scale : p.scale + n_tile * NT;
       const float* sf = p.n_tiles == 1 ? s_shift : p.shift + n_tile * NT;
-      // which output pixel this TMEM lane holds
-      const int seg = row_in_tile / p.tw, j = row_in_tile - seg * p.tw;
-      const int g = m_tile * p.segs + seg;
-      const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
-      const int wo = wseg * p.tw + j;
-      const bool valid = row < p.total_rows && wo < p.Wo;
-      const size_t pix = (size_t)row * p.Wo + wo;
-      __half* yrow = p.y + pix * p.out_c;
-      const __half* rrow = p.residual ? p.residual + pix * p.out_c : nullptr;
-
+      const int nb = n_tile * NT;
       if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 301)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + (uint32_t)(acc * NT) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-      for (int c0 = col_lo; c0 < col_hi; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld_32x16(t_addr + c0, r);
-        tmem_ld_wait();
-        if (valid) {
-#pragma unroll
-          for (int v8 = 0; v8 < 2; ++v8) {
-            const int nl = c0 + v8 * 8;           // column inside the N tile
-            const int n = n_tile * NT + nl;       // output channel
-            if (n >= p.out_c) break;
-            float v[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float a = __uint_as_float(r[v8 * 8 + e]);
-              if (p.two_step) {
-                a = __half2float(__float2half(a));
-                a = __half2float(__float2half(a + sf[nl + e]));  // shift == bias: no BatchNorm in this mode
-              } else {
-                a = a * sc[nl + e] + sf[nl + e];
-              }
-              v[e] = a;
-            }
-            if (p.y32) {
-              // fp32 output (pre-activations consumed by the LSTM recurrence): no rounding, no activation
-              float* o32 = p.y32 + pix * p.out_c + n;
-              if ((p.out_c & 7) == 0) {
-                *reinterpret_cast<float4*>(o32) = make_float4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<float4*>(o32 + 4) = make_float4(v[4], v[5], v[6], v[7]);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (n + e < p.out_c) o32[e] = v[e];
-              }
-            } else if (vec_ok) {
-              if (rrow) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + n);
-                const __half* rh = reinterpret_cast<const __half*>(&rv);
-#pragma unroll
-                for (int e = 0; e < 8; ++e)  // the add stores fp16 before the activation (ResConvLayer.cpp:35-36)
-                  v[e] = __half2float(__float2half(__half2float(__float2half(v[e])) + __half2float(rh[e])));
-              }
-              uint4 o;
-              __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-              for (int e = 0; e < 8; ++e) oh[e] = __float2half(act_apply_fast(v[e], p.act, p.slope));
-              *reinterpret_cast<uint4*>(yrow + n) = o;
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                if (n + e < p.out_c) {
-                  float a = v[e];
-                  if (rrow) a = __half2float(__float2half(__half2float(__float2half(a)) + __half2float(rrow[n + e])));
-                  yrow[n + e] = __float2half(act_apply_fast(a, p.act, p.slope));
-                }
-              }
-            }
+      for (int sub = 0; sub < MS; ++sub) {
+        // which output pixel this TMEM lane holds
+        const int seg = row_in_tile / p.tw, j = row_in_tile - seg * p.tw;
+        const int g = (m_sup * MS + sub) * p.segs + seg;
+        const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
+        const int wo = wseg * p.tw + j;
+        const bool valid = row < p.total_rows && wo < p.Wo;
+        const size_t pix = (size_t)row * p.Wo + wo;
+        __half* yrow = p.y + pix * p.out_c;
+        const __half* rrow = p.residual ? p.residual + pix * p.out_c : nullptr;
+        const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q * 32) << 16);
+        if (fast) {
+#define AIG_EPI(ACT)                                                                                                  \
+  if (rrow) epi_fused_cols<ACT, true>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid);      \
+  else epi_fused_cols<ACT, false>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid)
+          switch (p.act) {
+            case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
+            case AIG_ACT_SWISH: AIG_EPI(AIG_ACT_SWISH); break;
+            case AIG_ACT_LEAKY: AIG_EPI(AIG_ACT_LEAKY); break;
+            default: AIG_EPI(AIG_ACT_NONE); break;
           }
+#undef AIG_EPI
+        } else {
+          epi_generic_cols(t_addr, col_lo, col_hi, nb, p, sc, sf, rrow, yrow, p.y32 ? p.y32 + pix * p.out_c : nullptr, valid);
         }
       }
       tc_fence_before();
@@ -297,12 +397,12 @@ __global__ void repack_fc_kernel(const __half* __restrict__ w_in_out, __half* __
     packed[i] = w_in_out[(size_t)k * outC + o];
   }
 }
-__global__ void fold_affine_kernel(float* scale, float* shift, __half* bias_out, const __half* bias, const float* gamma,
-                                   const float* beta, const float* mean, const float* var, float eps, int K, int Kpad) {
+__global__ void fold_affine_kernel(float* scale, float* shift, const __half* bias, const float* gamma, const float* beta,
+                                   const float* mean, const float* var, float eps, int K, int Kpad) {
   for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < Kpad; k += gridDim.x * blockDim.x) {
-    float s = 0.f, t = 0.f, b = 0.f;
+    float s = 0.f, t = 0.f;
     if (k < K) {
-      b = bias ? __half2float(bias[k]) : 0.f;
+      const float b = bias ? __half2float(bias[k]) : 0.f;
       if (gamma) {
         s = gamma[k] / sqrtf(var[k] + eps);
         t = (b - mean[k]) * s + beta[k];
@@ -313,10 +413,8 @@ __global__ void fold_affine_kernel(float* scale, float* shift, __half* bias_out,
     }
     scale[k] = s;
     shift[k] = t;
-    bias_out[k] = __float2half(b);
   }
 }
-
 __global__ void add_bias_kernel(float* shift, const __half* bias2, int K) {
   const int k = blockIdx.x * blockDim.x + threadIdx.x;
   if (k < K) shift[k] += __half2float(bias2[k]);
@@ -344,54 +442,58 @@ struct aig_conv_plan {
   aig_conv_desc d{};
   int Do = 1, Ho = 1, Wo = 1;
   bool is_fc = false;
-  int BK = 64, NT = 64, Kpad = 0, taps = 1, Ktot = 0;
+  int BK = 64, NT = 64, MS = 1, Kpad = 0, taps = 1, Ktot = 0;
   IgemmParams prm{};
   __half* w_packed = nullptr;
   float* scale = nullptr;
   float* shift = nullptr;
-  __half* bias_h = nullptr;
   bool weights_set = false;
   bool out_f32 = false;
   CUtensorMap tmapA{}, tmapB{};
   const void* tmapA_ptr = nullptr;
   int grid = 1;
-  size_t smem = 0;
 };
 
 namespace {
 
-template <int NT, int BK>
+template <int NT, int BK, int MS>
 int launch_igemm(aig_conv_plan* pl) {
-  using Cfg = IgemmCfg<NT, BK>;
+  using Cfg = IgemmCfg<NT, BK, MS>;
   static bool attr_set[64] = {};
   aig_ctx* ctx = pl->ctx;
   if (!attr_set[ctx->device & 63]) {
-    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(igemm_kernel<NT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(igemm_kernel<NT, BK, MS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set[ctx->device & 63] = true;
   }
-  igemm_kernel<NT, BK><<<pl->grid, kNumThreads, Cfg::kSmemBytes, ctx->stream>>>(pl->tmapA, pl->tmapB, pl->prm);
+  igemm_kernel<NT, BK, MS><<<pl->grid, kNumThreads, Cfg::kSmemBytes, ctx->stream>>>(pl->tmapA, pl->tmapB, pl->prm);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }
 
-template <int NT>
+template <int NT, int MS>
 int dispatch_bk(aig_conv_plan* pl) {
   switch (pl->BK) {
-    case 64: return launch_igemm<NT, 64>(pl);
-    case 32: return launch_igemm<NT, 32>(pl);
-    case 16: return launch_igemm<NT, 16>(pl);
+    case 64: return launch_igemm<NT, 64, MS>(pl);
+    case 32: return launch_igemm<NT, 32, MS>(pl);
+    case 16: return launch_igemm<NT, 16, MS>(pl);
   }
   return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "igemm: unsupported BK %d", pl->BK);
 }
 
 int dispatch(aig_conv_plan* pl) {
-  switch (pl->NT) {
-    case 32: return dispatch_bk<32>(pl);
-    case 64: return dispatch_bk<64>(pl);
-    case 128: return dispatch_bk<128>(pl);
-    case 256: return dispatch_bk<256>(pl);
+  const int key = pl->NT * 10 + pl->MS;
+  switch (key) {
+    case 321: return dispatch_bk<32, 1>(pl);
+    case 322: return dispatch_bk<32, 2>(pl);
+    case 324: return dispatch_bk<32, 4>(pl);
+    case 641: return dispatch_bk<64, 1>(pl);
+    case 642: return dispatch_bk<64, 2>(pl);
+    case 644: return dispatch_bk<64, 4>(pl);
+    case 1281: return dispatch_bk<128, 1>(pl);
+    case 1282: return dispatch_bk<128, 2>(pl);
+    case 2561: return dispatch_bk<256, 1>(pl);
   }
-  return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "igemm: unsupported NT %d", pl->NT);
+  return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "igemm: unsupported tile NT=%d MS=%d", pl->NT, pl->MS);
 }
 
 CUtensorMapSwizzle swizzle_for(int bk) {
@@ -438,12 +540,11 @@ int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
   else return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "igemm needs in_c %% 16 == 0 (got %d); 3-channel inputs use the conv0 plans", d.in_c);
   pl->taps = d.kd * d.kh * d.kw;
   pl->Ktot = pl->taps * d.in_c;
-  // N tile: whole out_c when it fits one tile, else 256/128 wide tiles
+  // N tile: whole out_c when it fits one tile, else 256-wide tiles
   if (d.out_c <= 32) pl->NT = 32;
   else if (d.out_c <= 64) pl->NT = 64;
   else if (d.out_c <= 128) pl->NT = 128;
   else pl->NT = 256;
-  // keep (NT=256,BK=64) from exceeding shared memory: 4 stages of 48 KB fit
   pl->Kpad = ceil_div(d.out_c, pl->NT) * pl->NT;
   // M tiling: runs of tw output pixels along W; tw in {8..128} minimising padding, ties -> larger tw
   int best_tw = 8;
@@ -462,8 +563,16 @@ int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
   p.segs_per_row = ceil_div(pl->Wo, best_tw);
   p.total_rows = d.batch * pl->Do * pl->Ho;
   const long long total_segs = (long long)p.total_rows * p.segs_per_row;
-  p.m_tiles = (int)ceil_div_ll(total_segs, p.segs);
+  const int m_tiles = (int)ceil_div_ll(total_segs, p.segs);
+  // few M tiles (small spatial extents): split N so that more SMs stream the weights in parallel
+  while (pl->NT > 64 && (long long)m_tiles * (pl->Kpad / pl->NT) * 2 <= ctx->sm_count && d.out_c > pl->NT / 2) pl->NT /= 2;
   p.n_tiles = pl->Kpad / pl->NT;
+  // sub-tiles per CTA tile: fill one 256-column TMEM buffer, but keep at least two waves of CTA tiles
+  int ms = 256 / pl->NT;
+  if (ms > kMaxSub) ms = kMaxSub;
+  while (ms > 1 && (long long)ceil_div(m_tiles, ms) * p.n_tiles < 2LL * ctx->sm_count) ms /= 2;
+  pl->MS = ms;
+  p.m_super = ceil_div(m_tiles, ms);
   p.cblocks = d.in_c / pl->BK;
   p.num_kb = pl->taps * p.cblocks;
   p.taps_hw = d.kh * d.kw;
@@ -478,14 +587,13 @@ int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
   p.slope = d.slope;
   p.two_step = d.two_step;
   p.gerr = ctx->d_err;
-  const long long tiles = (long long)p.m_tiles * p.n_tiles;
+  const long long tiles = (long long)p.m_super * p.n_tiles;
   pl->grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   if (pl->grid < 1) pl->grid = 1;
   AIG_CUDA_OK(ctx, cudaMalloc(&pl->w_packed, (size_t)pl->Kpad * pl->Ktot * sizeof(__half)));
   AIG_CUDA_OK(ctx, cudaMemsetAsync(pl->w_packed, 0, (size_t)pl->Kpad * pl->Ktot * sizeof(__half), ctx->stream));
   AIG_CUDA_OK(ctx, cudaMalloc(&pl->scale, pl->Kpad * sizeof(float)));
   AIG_CUDA_OK(ctx, cudaMalloc(&pl->shift, pl->Kpad * sizeof(float)));
-  AIG_CUDA_OK(ctx, cudaMalloc(&pl->bias_h, pl->Kpad * sizeof(__half)));
   p.scale = pl->scale;
   p.shift = pl->shift;
   return encode_B(pl);
@@ -496,8 +604,8 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
   aig_ctx* ctx = pl->ctx;
   if (pl->d.two_step && g) return aig_fail(ctx, AIG_ERR_INVALID, "two_step plans reproduce conv+bias only; BatchNorm cannot be folded");
   if (g && !(b && m && v)) return aig_fail(ctx, AIG_ERR_INVALID, "BatchNorm needs gamma, beta, mean and var");
-  fold_affine_kernel<<<ceil_div(pl->Kpad, 128), 128, 0, ctx->stream>>>(pl->scale, pl->shift, pl->bias_h, (const __half*)bias,
-                                                                        g, b, m, v, eps, pl->d.out_c, pl->Kpad);
+  fold_affine_kernel<<<ceil_div(pl->Kpad, 128), 128, 0, ctx->stream>>>(pl->scale, pl->shift, (const __half*)bias, g, b, m, v, eps,
+                                                                        pl->d.out_c, pl->Kpad);
   AIG_LAUNCH_OK(ctx);
   pl->weights_set = true;
   return AIG_OK;
@@ -539,7 +647,6 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   cudaFree(pl->w_packed);
   cudaFree(pl->scale);
   cudaFree(pl->shift);
-  cudaFree(pl->bias_h);
   delete pl;
   return AIG_OK;
 }

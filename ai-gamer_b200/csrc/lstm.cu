@@ -148,7 +148,6 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tmapR, const __grid_co
         tc_fence_after();
         for (int kb = 0; kb < nkb; ++kb) {
           if (!mbar_wait_bounded(bar_a + 8 * kb, ph, s_abort, p.gerr, 404)) { ok = false; break; }
-          tc_fence_after();
 #pragma unroll
           for (int k = 0; k < kKB / 16; ++k) {
             const uint64_t adesc = umma_smem_desc(sA + kb * kRows * 128 + k * 32, 128);

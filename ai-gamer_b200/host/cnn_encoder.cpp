@@ -70,10 +70,19 @@ struct aig_cnn {
   uint8_t* frames_dev = nullptr;      // staging for the host-buffer entry point
   Arena params;
   aig_half* sa_w = nullptr;
+  aig_half *fcw = nullptr, *fcb = nullptr;  // head FC parameters as loaded ([in][out], [out])
+  bool fused_head = false;
   float sa_b = 0.f;
   bool loaded = false;
-  aig_graph* graph = nullptr;
-  const uint8_t* graph_in = nullptr;
+  static constexpr int kGraphs = 4;    // captured forwards, keyed by input pointer
+  aig_graph* graphs[kGraphs] = {nullptr, nullptr, nullptr, nullptr};
+  const uint8_t* graph_ins[kGraphs] = {nullptr, nullptr, nullptr, nullptr};
+  int graph_next = 0;
+  // pipelined host-buffer steps: private copy stream, two frame slots
+  cudaStream_t copy_stream = nullptr;
+  uint8_t* frames_slot[2] = {nullptr, nullptr};
+  cudaEvent_t ev_h2d[2] = {nullptr, nullptr}, ev_used[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr};
+  bool slot_used[2] = {false, false};
   int launches_per_forward = 0;
   // optional per-launch timing (eager forward only): one CUDA event between consecutive launches
   struct Site {
@@ -238,8 +247,14 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
       dev_alloc(m, &m->frames_dev, (size_t)c.batch * c.height * c.width * 4) != AIG_OK)
     return bail(AIG_ERR_CUDA);
   if ((rc = aig_fc_plan_create(ctx, c.batch, cl, c.n_out, AIG_ACT_NONE, 0.f, 1, &m->fc)) != AIG_OK) return bail(rc);
-  m->launches_per_forward += 2 /*mask, pool*/ + 1 /*fc*/ + 2 /*sigmoid, tanh*/ + 1 /*half->float*/;
-  {
+  // the head runs as one fused launch when a frame's last feature map fits shared memory
+  m->fused_head = ((size_t)h * w * cl * 2 + (size_t)(h * w + cl) * 4 <= 200 * 1024) && ((h * w * cl) % 8 == 0);
+  if (m->fused_head) {
+    m->launches_per_forward += 1;
+    const double fb = (double)c.batch * h * w * cl * 2;
+    m->sites.push_back({"head_mask_pool_fc", 2.0 * c.batch * cl * c.n_out, fb + (double)c.batch * (cl * 2 + c.n_out * 6)});
+  } else {
+    m->launches_per_forward += 2 /*mask, pool*/ + 1 /*fc*/ + 2 /*sigmoid, tanh*/ + 1 /*half->float*/;
     const double fb = (double)c.batch * h * w * cl * 2;
     m->sites.push_back({"mask_attention", 0.0, 2 * fb});
     m->sites.push_back({"global_avgpool", 0.0, fb + (double)c.batch * cl * 2});
@@ -255,7 +270,17 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
 int aig_cnn_destroy(aig_cnn* m) {
   if (!m) return AIG_OK;
   if (m->ctx) aig_ctx_sync(m->ctx);
-  aig_graph_destroy(m->graph);
+  for (aig_graph* g : m->graphs) aig_graph_destroy(g);
+  if (m->copy_stream) {
+    cudaStreamSynchronize(m->copy_stream);
+    cudaStreamDestroy(m->copy_stream);
+    for (int i = 0; i < 2; ++i) {
+      cudaFree(m->frames_slot[i]);
+      if (m->ev_h2d[i]) cudaEventDestroy(m->ev_h2d[i]);
+      if (m->ev_used[i]) cudaEventDestroy(m->ev_used[i]);
+      if (m->ev_done[i]) cudaEventDestroy(m->ev_done[i]);
+    }
+  }
   aig_conv0_plan_destroy(m->conv0);
   for (auto& b : m->blocks) {
     aig_conv_plan_destroy(b.c0);
@@ -319,6 +344,8 @@ int aig_cnn_load_memory(aig_cnn* m, const void* blob, size_t bytes) {
   ConvP fc;
   if (!read_conv(m, rd, fc, (size_t)cl * c.n_out, c.n_out, s)) return fail(m, AIG_ERR_IO, io);
   CNN_OK(m, aig_fc_plan_set_weights(m->fc, fc.w, fc.b, nullptr, nullptr, nullptr, nullptr, 0.f));
+  m->fcw = fc.w;
+  m->fcb = fc.b;
   if (rd.left != 0) return fail(m, AIG_ERR_IO, "trailing bytes in checkpoint");
   CNN_OK(m, aig_ctx_sync(m->ctx));  // the host blob may be freed by the caller after this returns
   m->loaded = true;
@@ -363,17 +390,24 @@ int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) {
   }
   const int cl = c.widths[c.n_blocks];
   const int h = c.n_blocks ? m->bh.back() : m->H0, w = c.n_blocks ? m->bw.back() : m->W0;
-  CNN_OK(m, aig_spatial_mask_forward(m->ctx, x, m->sa_w, m->sa_b, m->sa, c.batch, h * w, cl));
-  tick();
-  CNN_OK(m, aig_global_avgpool_nhwc(m->ctx, m->sa, m->feat, c.batch, h * w, cl));
-  tick();
-  CNN_OK(m, aig_conv_forward(m->fc, m->feat, nullptr, m->logits));
-  tick();
-  // Sigmoid is applied in place on the FC output, as in the reference (Sigmoid.cpp:8-12)
-  CNN_OK(m, aig_sigmoid_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));
-  if (c.n_sigmoid < c.n_out) CNN_OK(m, aig_tanh_tail_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));
-  CNN_OK(m, aig_half_to_float(m->ctx, m->logits, m->out_f32, (size_t)c.batch * c.n_out));
-  tick();
+  if (m->fused_head) {
+    // mask attention + pool + FC + sigmoid/tanh + half->float in one launch
+    CNN_OK(m, aig_cnn_head_forward(m->ctx, x, m->sa_w, m->sa_b, m->fcw, m->fcb, m->feat, m->logits, m->out_f32, c.batch, h * w, cl,
+                                   c.n_out, c.n_sigmoid));
+    tick();
+  } else {
+    CNN_OK(m, aig_spatial_mask_forward(m->ctx, x, m->sa_w, m->sa_b, m->sa, c.batch, h * w, cl));
+    tick();
+    CNN_OK(m, aig_global_avgpool_nhwc(m->ctx, m->sa, m->feat, c.batch, h * w, cl));
+    tick();
+    CNN_OK(m, aig_conv_forward(m->fc, m->feat, nullptr, m->logits));
+    tick();
+    // Sigmoid is applied in place on the FC output, as in the reference (Sigmoid.cpp:8-12)
+    CNN_OK(m, aig_sigmoid_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));
+    if (c.n_sigmoid < c.n_out) CNN_OK(m, aig_tanh_tail_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));
+    CNN_OK(m, aig_half_to_float(m->ctx, m->logits, m->out_f32, (size_t)c.batch * c.n_out));
+    tick();
+  }
   if (prof) ++m->prof_steps;
   return AIG_OK;
 }
@@ -419,10 +453,15 @@ double aig_cnn_site_bytes(aig_cnn* m, int i) { return (m && i >= 0 && i < (int)m
 // Same, replayed as one CUDA graph (captured on first use for this input pointer).
 int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
   if (!m || !bgra_dev) return AIG_ERR_INVALID;
-  if (!m->graph || m->graph_in != bgra_dev) {
-    if (m->graph) {
-      aig_graph_destroy(m->graph);
-      m->graph = nullptr;
+  int slot = -1;
+  for (int i = 0; i < aig_cnn::kGraphs; ++i)
+    if (m->graphs[i] && m->graph_ins[i] == bgra_dev) slot = i;
+  if (slot < 0) {
+    slot = m->graph_next;
+    m->graph_next = (m->graph_next + 1) % aig_cnn::kGraphs;
+    if (m->graphs[slot]) {
+      aig_graph_destroy(m->graphs[slot]);
+      m->graphs[slot] = nullptr;
     }
     // one eager pass first so that every plan has encoded its tensor maps before capture
     int rc = aig_cnn_forward(m, bgra_dev);
@@ -433,10 +472,49 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
     const int rc2 = aig_graph_end(m->ctx, &g);
     if (rc != AIG_OK) return rc;
     if (rc2 != AIG_OK) return fail(m, rc2, aig_last_error(m->ctx));
-    m->graph = g;
-    m->graph_in = bgra_dev;
+    m->graphs[slot] = g;
+    m->graph_ins[slot] = bgra_dev;
   }
-  CNN_OK(m, aig_graph_launch(m->ctx, m->graph));
+  CNN_OK(m, aig_graph_launch(m->ctx, m->graphs[slot]));
+  return AIG_OK;
+}
+
+// Pipelined frame steps with host buffers.  submit(slot) queues, without waiting, the host->device
+// copy of one batch on a private copy stream, the forward on the context stream once the copy has
+// landed, and the device->host copy of the outputs; wait(slot) blocks until that slot's outputs are
+// in the caller's buffer.  With the two slots used alternately the copy of step i+1 runs under the
+// forward of step i.  Host buffers should be pinned.
+int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host) {
+  if (!m || !bgra_host || !out_host || slot < 0 || slot > 1) return AIG_ERR_INVALID;
+  const aig_cnn_config& c = m->cfg;
+  const size_t fb = (size_t)c.batch * c.height * c.width * 4;
+  cudaStream_t s = (cudaStream_t)aig_ctx_stream(m->ctx);
+  if (!m->copy_stream) {
+    CNN_CUDA(m, cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      CNN_CUDA(m, cudaMalloc(reinterpret_cast<void**>(&m->frames_slot[i]), fb));
+      CNN_CUDA(m, cudaEventCreateWithFlags(&m->ev_h2d[i], cudaEventDisableTiming));
+      CNN_CUDA(m, cudaEventCreateWithFlags(&m->ev_used[i], cudaEventDisableTiming));
+      CNN_CUDA(m, cudaEventCreateWithFlags(&m->ev_done[i], cudaEventDisableTiming));
+    }
+  }
+  // the slot's frame buffer is free once the forward that last read it has run
+  if (m->slot_used[slot]) CNN_CUDA(m, cudaStreamWaitEvent(m->copy_stream, m->ev_used[slot], 0));
+  CNN_CUDA(m, cudaMemcpyAsync(m->frames_slot[slot], bgra_host, fb, cudaMemcpyHostToDevice, m->copy_stream));
+  CNN_CUDA(m, cudaEventRecord(m->ev_h2d[slot], m->copy_stream));
+  CNN_CUDA(m, cudaStreamWaitEvent(s, m->ev_h2d[slot], 0));
+  const int rc = aig_cnn_forward_graph(m, m->frames_slot[slot]);
+  if (rc != AIG_OK) return rc;
+  CNN_CUDA(m, cudaEventRecord(m->ev_used[slot], s));
+  m->slot_used[slot] = true;
+  CNN_CUDA(m, cudaMemcpyAsync(out_host, m->out_f32, (size_t)c.batch * c.n_out * sizeof(float), cudaMemcpyDeviceToHost, s));
+  CNN_CUDA(m, cudaEventRecord(m->ev_done[slot], s));
+  return AIG_OK;
+}
+
+int aig_cnn_wait(aig_cnn* m, int slot) {
+  if (!m || slot < 0 || slot > 1 || !m->slot_used[slot]) return AIG_ERR_INVALID;
+  CNN_CUDA(m, cudaEventSynchronize(m->ev_done[slot]));
   return AIG_OK;
 }
 

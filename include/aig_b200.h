@@ -124,6 +124,13 @@ int aig_spatial_mask_forward(aig_ctx* ctx, const aig_half* x_nhwc, const aig_hal
                              aig_half* y_nhwc, int batch, int hw, int c);
 /* Not in the reference: mean over hw of a channels-last tensor -> [batch][c]. */
 int aig_global_avgpool_nhwc(aig_ctx* ctx, const aig_half* x_nhwc, aig_half* y, int batch, int hw, int c);
+/* Not in the reference: the whole output head of the frame encoder in one launch -- mask attention,
+ * global average pool, FC (W [c][n_out], two roundings like FCLayer.cpp:50-51), sigmoid on the first
+ * n_sigmoid outputs and tanh on the rest (Sigmoid.cpp:8-12).  feat [batch][c]; out_half/out_f32
+ * [batch][n_out].  Same arithmetic as the separate calls. */
+int aig_cnn_head_forward(aig_ctx* ctx, const aig_half* x_nhwc, const aig_half* mask_w, float mask_b,
+                         const aig_half* fc_w, const aig_half* fc_b, aig_half* feat, aig_half* out_half,
+                         float* out_f32, int batch, int hw, int c, int n_out, int n_sigmoid);
 /* Not in the reference: adaptive average pool of channels-last [batch][d][h][w][c] over d and
  * ph x pw spatial cells -> [batch][c*ph*pw] in (c, ph, pw) order. */
 int aig_adaptive_avgpool3d_ndhwc(aig_ctx* ctx, const aig_half* x, aig_half* y, int batch, int d, int h,

@@ -47,6 +47,12 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev);
 /* One frame step with host buffers (Infer.cpp:103-112): host->device copy of the frames, forward,
  * half->float, device->host copy of [batch][n_out] floats, stream synchronise. */
 int aig_cnn_infer_host(aig_cnn* m, const uint8_t* bgra_host, float* out_host);
+/* The same frame step, pipelined: submit(slot) queues host->device copy (private copy stream), forward
+ * and device->host copy of [batch][n_out] floats and returns at once; wait(slot) blocks until that
+ * slot's outputs have arrived.  Alternating slots 0 and 1 lets the copy of step i+1 run under the
+ * forward of step i.  Host buffers should be pinned and must stay valid until wait() returns. */
+int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host);
+int aig_cnn_wait(aig_cnn* m, int slot);
 /* Device views of the last forward's results. */
 const aig_half* aig_cnn_outputs_half(aig_cnn* m);  /* [batch][n_out] after sigmoid/tanh */
 const float* aig_cnn_outputs_f32(aig_cnn* m);      /* the same as fp32 (ConvertHalfToFloat) */

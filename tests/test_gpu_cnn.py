@@ -67,6 +67,17 @@ def test_cnn_encoder_matches_oracle(env, trivial):
     pinned_out = torch.empty((B, 18), dtype=torch.float32).pin_memory()
     enc.infer_host(pinned_in, pinned_out)
     assert np.array_equal(pinned_out.numpy(), got)
+    # pipelined submit/wait over two slots: same bytes, any order of slots
+    outs = [torch.zeros((B, 18), dtype=torch.float32).pin_memory() for _ in range(2)]
+    for step in range(5):
+        if step >= 2:
+            enc.wait(step & 1)
+            assert np.array_equal(outs[step & 1].numpy(), got)
+            outs[step & 1].zero_()
+        enc.submit_host(step & 1, pinned_in, outs[step & 1])
+    for step in (3, 4):
+        enc.wait(step & 1)
+        assert np.array_equal(outs[step & 1].numpy(), got)
     enc.close()
 
 
