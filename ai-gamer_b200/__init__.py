@@ -152,14 +152,38 @@ SIGNATURES.update({
     "aig_agent_step_host": [P, P, P],
     "aig_agent_reset": [P],
     "aig_agent_outputs_f32": [P],
+    "aig_refnn_create": [P, c_int, c_int, ctypes.c_char_p, PP],
+    "aig_refnn_forward": [P, P, PP],
+    "aig_refnn_input_size": [P, PI, PI],
+    "aig_refnn_destroy": [P],
+    "aig_layers_last_error": [],
 })
-_RESTYPES = {"aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
+AIG_C3D_MAX_LAYERS = 6
+
+
+class C3dConfig(ctypes.Structure):
+    _fields_ = [("batch", c_int), ("depth", c_int), ("height", c_int), ("width", c_int), ("n_layers", c_int),
+                ("widths", c_int * (AIG_C3D_MAX_LAYERS + 1)), ("n_out", c_int), ("n_sigmoid", c_int), ("slope", c_float)]
+
+
+SIGNATURES.update({
+    "aig_c3d_create": [P, ctypes.POINTER(C3dConfig), PP],
+    "aig_c3d_destroy": [P],
+    "aig_c3d_last_error": [P],
+    "aig_c3d_param_bytes": [ctypes.POINTER(C3dConfig)],
+    "aig_c3d_load_memory": [P, P, c_size_t],
+    "aig_c3d_forward": [P, P],
+    "aig_c3d_outputs_f32": [P],
+    "aig_c3d_features": [P],
+})
+_RESTYPES = {"aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+             "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
              "aig_cnn_site_flops": ctypes.c_double, "aig_cnn_site_bytes": ctypes.c_double,
              "aig_lstm_weight_count": c_size_t, "aig_seq_last_error": ctypes.c_char_p, "aig_seq_param_bytes": c_size_t,
              "aig_seq_outputs_half": c_void_p, "aig_seq_outputs_f32": c_void_p, "aig_seq_lstm_output": c_void_p,
-             "aig_agent_last_error": ctypes.c_char_p, "aig_agent_param_bytes": c_size_t, "aig_agent_outputs_f32": c_void_p}
+             "aig_layers_last_error": ctypes.c_char_p, "aig_agent_last_error": ctypes.c_char_p, "aig_agent_param_bytes": c_size_t, "aig_agent_outputs_f32": c_void_p}
 
 _lib = None
 

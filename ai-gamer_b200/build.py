@@ -17,13 +17,13 @@ LIB = os.path.join(HERE, "libaig_b200.so")
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
-    "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-I" + HOST,
+    "-Xcompiler", "-fPIC", "-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-I" + HOST, "-I" + os.path.join(HOST, "layers"),
 ]
 
 
 def _newest_header():
     t = 0.0
-    for d in (CSRC, HOST, os.path.join(ROOT, "include")):
+    for d in (CSRC, HOST, os.path.join(HOST, "layers"), os.path.join(ROOT, "include")):
         if not os.path.isdir(d):
             continue
         for f in os.listdir(d):
@@ -34,7 +34,7 @@ def _newest_header():
 
 def sources():
     out = []
-    for d in (CSRC, HOST):
+    for d in (CSRC, HOST, os.path.join(HOST, "layers")):
         if os.path.isdir(d):
             out += [os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith((".cu", ".cpp"))]
     return out

@@ -1,0 +1,539 @@
+// Layers.cpp -- implementation of the reference-compatible layer classes (Layers.h) on the kernel ABI.
+// Errors are C++ exceptions (std::runtime_error), like the reference's checkCUDA/checkCUDNN macros
+// (common.h:15-34); the C hooks at the end of the file catch them.
+#include "Layers.h"
+
+#include <string.h>
+
+#include <iostream>
+
+namespace {
+
+aig_ctx* g_default_ctx = nullptr;
+
+void check(aig_ctx* ctx, int rc, const char* what) {
+  if (rc != AIG_OK) throw std::runtime_error(std::string(what) + ": " + aig_last_error(ctx));
+}
+void checkCuda(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+// common.h:82-86 (CUDAMallocZero)
+template <class T>
+void mallocZero(T** p, size_t count) {
+  checkCuda(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)), "cudaMalloc");
+  checkCuda(cudaMemset(*p, 0, count * sizeof(T)), "cudaMemset");
+}
+// file -> staging buffer -> device, the pattern of every LoadParameters in the reference (e.g. ConvLayer.cpp:96-107)
+void loadArray(std::ifstream& file, unsigned char* buffer, void* dst, size_t bytes) {
+  file.read(reinterpret_cast<char*>(buffer), (std::streamsize)bytes);
+  if ((size_t)file.gcount() != bytes) throw std::runtime_error("checkpoint truncated");
+  checkCuda(cudaMemcpy(dst, buffer, bytes, cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+}
+void saveArray(std::ofstream& file, unsigned char* buffer, const void* src, size_t bytes) {
+  checkCuda(cudaMemcpy(buffer, src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+  file.write(reinterpret_cast<const char*>(buffer), (std::streamsize)bytes);
+}
+aig_half* H(__half* p) { return reinterpret_cast<aig_half*>(p); }
+const aig_half* H(const __half* p) { return reinterpret_cast<const aig_half*>(p); }
+
+}  // namespace
+
+aig_ctx* aigDefaultContext() {
+  if (!g_default_ctx) throw std::runtime_error("no context yet: construct a layer that takes a handle first or call aigSetDefaultContext");
+  return g_default_ctx;
+}
+void aigSetDefaultContext(aig_ctx* ctx) { g_default_ctx = ctx; }
+
+// ------------------------------------------------------------------------------------------ ConvLayer
+ConvLayer::ConvLayer(cudnnHandle_t cudnnHandle, int batchSize, int inChannels, int outChannels, int filterSize, int stride,
+                     int padding, int* height, int* width, const char* layerName, bool train, float)
+    : batchSize_(batchSize), inC_(inChannels), outC_(outChannels), k_(filterSize), stride_(stride), pad_(padding), inH_(*height),
+      inW_(*width), ctx_(cudnnHandle) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  if (inC_ == 3) {
+    check(ctx_, aig_conv0_plan_create(ctx_, batchSize_, inH_, inW_, outC_, k_, stride_, pad_, AIG_ACT_NONE, 0.f, &plan0_), layerName);
+    aig_conv0_plan_out_dims(plan0_, nullptr, &outH_, &outW_);
+  } else {
+    aig_conv_desc d{};
+    d.batch = batchSize_; d.in_c = inC_; d.in_d = 1; d.in_h = inH_; d.in_w = inW_; d.out_c = outC_;
+    d.kd = 1; d.kh = d.kw = k_; d.sd = 1; d.sh = d.sw = stride_; d.pd = 0; d.ph = d.pw = pad_;
+    d.act = AIG_ACT_NONE; d.two_step = 1;  // conv -> half, + bias -> half (ConvLayer.cpp:76-77)
+    check(ctx_, aig_conv_plan_create(ctx_, &d, &plan_), layerName);
+    aig_conv_plan_out_dims(plan_, nullptr, &outH_, &outW_);
+    mallocZero(&nhwcIn_, (size_t)batchSize_ * inC_ * inH_ * inW_);
+  }
+  *height = outH_;  // ConvLayer.cpp:48-49
+  *width = outW_;
+  outNCHW_ = batchSize_ * outC_ * outH_ * outW_;
+  outDesc_ = {batchSize_, outC_, outH_, outW_};
+  weightCount_ = (size_t)outC_ * inC_ * k_ * k_;
+  mallocZero(&weights_, weightCount_);
+  mallocZero(&bias_, (size_t)outC_);
+  mallocZero(&outData_, (size_t)outNCHW_);
+  mallocZero(&nhwcOut_, (size_t)outNCHW_);
+  SyncWeights();
+}
+ConvLayer::~ConvLayer() {
+  aig_conv_plan_destroy(plan_);
+  aig_conv0_plan_destroy(plan0_);
+  cudaFree(weights_); cudaFree(bias_); cudaFree(outData_); cudaFree(nhwcIn_); cudaFree(nhwcOut_);
+}
+void ConvLayer::SyncWeights() {
+  if (plan0_) check(ctx_, aig_conv0_plan_set_weights(plan0_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
+  else check(ctx_, aig_conv_plan_set_weights(plan_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
+}
+__half* ConvLayer::Forward(__half* data) {
+  if (plan0_) {
+    check(ctx_, aig_conv0_forward_nchw(plan0_, H(data), H(nhwcOut_)), layerName_);
+  } else {
+    check(ctx_, aig_nchw_to_nhwc(ctx_, H(data), H(nhwcIn_), batchSize_, inC_, inH_ * inW_), layerName_);
+    check(ctx_, aig_conv_forward(plan_, H(nhwcIn_), nullptr, H(nhwcOut_)), layerName_);
+  }
+  check(ctx_, aig_nhwc_to_nchw(ctx_, H(nhwcOut_), H(outData_), batchSize_, outC_, outH_ * outW_), layerName_);
+  return outData_;
+}
+void ConvLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  loadArray(file, buffer, bias_, outC_ * sizeof(__half));
+  SyncWeights();
+}
+void ConvLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {
+  saveArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  saveArray(file, buffer, bias_, outC_ * sizeof(__half));
+}
+
+// ------------------------------------------------------------------------------------------ ConvLayer3D
+ConvLayer3D::ConvLayer3D(cudnnHandle_t cudnnHandle, int batchSize, int inChannels, int outChannels, int filterSizeD, int filterSizeHW,
+                         int strideD, int strideHW, int paddingD, int paddingHW, int* width, int* height, int* depth,
+                         const char* layerName, bool train, float)
+    : batchSize_(batchSize), inC_(inChannels), outC_(outChannels), inD_(*depth), inH_(*height), inW_(*width), ctx_(cudnnHandle) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  if (inC_ == 3) {
+    check(ctx_, aig_conv0_plan_create_3d(ctx_, batchSize_, inD_, inH_, inW_, outC_, filterSizeD, filterSizeHW, strideD, strideHW, paddingD,
+                                         paddingHW, AIG_ACT_NONE, 0.f, &plan0_), layerName);
+    aig_conv0_plan_out_dims(plan0_, &outD_, &outH_, &outW_);
+  } else {
+    aig_conv_desc d{};
+    d.batch = batchSize_; d.in_c = inC_; d.in_d = inD_; d.in_h = inH_; d.in_w = inW_; d.out_c = outC_;
+    d.kd = filterSizeD; d.kh = d.kw = filterSizeHW; d.sd = strideD; d.sh = d.sw = strideHW; d.pd = paddingD; d.ph = d.pw = paddingHW;
+    d.act = AIG_ACT_NONE; d.two_step = 1;
+    check(ctx_, aig_conv_plan_create(ctx_, &d, &plan_), layerName);
+    aig_conv_plan_out_dims(plan_, &outD_, &outH_, &outW_);
+    mallocZero(&nhwcIn_, (size_t)batchSize_ * inC_ * inD_ * inH_ * inW_);
+  }
+  *depth = outD_; *height = outH_; *width = outW_;
+  outNCHW_ = batchSize_ * outC_ * outD_ * outH_ * outW_;
+  outDesc_ = {batchSize_, outC_, outD_ * outH_, outW_};
+  weightCount_ = (size_t)outC_ * inC_ * filterSizeD * filterSizeHW * filterSizeHW;
+  mallocZero(&weights_, weightCount_);
+  mallocZero(&bias_, (size_t)outC_);
+  mallocZero(&outData_, (size_t)outNCHW_);
+  mallocZero(&nhwcOut_, (size_t)outNCHW_);
+  SyncWeights();
+}
+ConvLayer3D::~ConvLayer3D() {
+  aig_conv_plan_destroy(plan_);
+  aig_conv0_plan_destroy(plan0_);
+  cudaFree(weights_); cudaFree(bias_); cudaFree(outData_); cudaFree(nhwcIn_); cudaFree(nhwcOut_);
+}
+void ConvLayer3D::SyncWeights() {
+  if (plan0_) check(ctx_, aig_conv0_plan_set_weights(plan0_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
+  else check(ctx_, aig_conv_plan_set_weights(plan_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
+}
+__half* ConvLayer3D::Forward(__half* data) {
+  const int ohw = outD_ * outH_ * outW_;
+  if (plan0_) {
+    check(ctx_, aig_conv0_forward_nchw(plan0_, H(data), H(nhwcOut_)), layerName_);
+  } else {
+    check(ctx_, aig_nchw_to_nhwc(ctx_, H(data), H(nhwcIn_), batchSize_, inC_, inD_ * inH_ * inW_), layerName_);
+    check(ctx_, aig_conv_forward(plan_, H(nhwcIn_), nullptr, H(nhwcOut_)), layerName_);
+  }
+  check(ctx_, aig_nhwc_to_nchw(ctx_, H(nhwcOut_), H(outData_), batchSize_, outC_, ohw), layerName_);
+  return outData_;
+}
+void ConvLayer3D::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  loadArray(file, buffer, bias_, outC_ * sizeof(__half));
+  SyncWeights();
+}
+
+// ------------------------------------------------------------------------------------------ BatchNorm
+BatchNorm::BatchNorm(cudnnHandle_t cudnnHandle, cudnnBatchNormMode_t bnMode, int batchSize, int channels, int height, int width,
+                     const char* layerName, bool train, float)
+    : ctx_(cudnnHandle), mode_(bnMode), batch_(batchSize), c_(channels), hw_(height * width) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  outNCHW_ = batch_ * c_ * hw_;
+  outDesc_ = {batch_, c_, height, width};
+  paramCount_ = mode_ == CUDNN_BATCHNORM_SPATIAL ? (size_t)c_ : (size_t)c_ * hw_;
+  float** arrays[6] = {&bnScale_, &bnBias_, &bnRunningMean_, &bnRunningVar_, &bnSavedMean_, &bnSavedInvVariance_};
+  for (float** a : arrays) mallocZero(a, paramCount_);
+  std::vector<float> ones(paramCount_, 1.0f);  // scale = 1 as in BatchNorm.cpp:15-22
+  checkCuda(cudaMemcpy(bnScale_, ones.data(), paramCount_ * sizeof(float), cudaMemcpyHostToDevice), "bn scale init");
+  mallocZero(&outData_, (size_t)outNCHW_);
+}
+BatchNorm::~BatchNorm() {
+  float* arrays[6] = {bnScale_, bnBias_, bnRunningMean_, bnRunningVar_, bnSavedMean_, bnSavedInvVariance_};
+  for (float* a : arrays) cudaFree(a);
+  cudaFree(outData_);
+}
+__half* BatchNorm::Forward(__half* data) {
+  check(ctx_, aig_batchnorm_forward(ctx_, H(data), H(outData_), bnScale_, bnBias_, bnRunningMean_, bnRunningVar_, batch_, c_, hw_, 1e-6f,
+                                    mode_ == CUDNN_BATCHNORM_PER_ACTIVATION ? 1 : 0), layerName_);
+  return outData_;
+}
+void BatchNorm::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  float* arrays[6] = {bnScale_, bnBias_, bnRunningMean_, bnRunningVar_, bnSavedMean_, bnSavedInvVariance_};
+  for (float* a : arrays) loadArray(file, buffer, a, paramCount_ * sizeof(float));
+}
+void BatchNorm::SaveParameters(std::ofstream& file, unsigned char* buffer) {
+  float* arrays[6] = {bnScale_, bnBias_, bnRunningMean_, bnRunningVar_, bnSavedMean_, bnSavedInvVariance_};
+  for (float* a : arrays) saveArray(file, buffer, a, paramCount_ * sizeof(float));
+}
+
+// ------------------------------------------------------------------------------------------ activations
+Activate::Activate(cudnnHandle_t cudnnHandle, cudnnActivationMode_t mode, double, int batchSize, int channels, int height, int width,
+                   const char* layerName)
+    : ctx_(cudnnHandle) {
+  if (mode != CUDNN_ACTIVATION_RELU) throw std::runtime_error("Activate: only CUDNN_ACTIVATION_RELU is used by the reference");
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  outNCHW_ = batchSize * channels * height * width;
+  outDesc_ = {batchSize, channels, height, width};
+}
+__half* Activate::Forward(__half* data) {
+  check(ctx_, aig_relu_forward(ctx_, H(data), outNCHW_), layerName_);
+  return data;
+}
+Swish::Swish(int size, const char* layerName) {
+  layerName_ = layerName;
+  outNCHW_ = size;
+}
+__half* Swish::Forward(__half* data) {
+  check(aigDefaultContext(), aig_swish_forward(aigDefaultContext(), H(data), outNCHW_), layerName_);
+  return data;
+}
+LeakyReLU::LeakyReLU(int size, const char* layerName) {
+  layerName_ = layerName;
+  outNCHW_ = size;
+}
+__half* LeakyReLU::Forward(__half* data) {
+  check(aigDefaultContext(), aig_leaky_relu_forward(aigDefaultContext(), H(data), outNCHW_, slope_), layerName_);
+  return data;
+}
+Sigmoid::Sigmoid(int numSigmoidOutputs, int batchSize, int outC, const char* layerName) : numSigmoid_(numSigmoidOutputs), outC_(outC) {
+  layerName_ = layerName;
+  outNCHW_ = batchSize * outC;
+}
+__half* Sigmoid::Forward(__half* data) {
+  check(aigDefaultContext(), aig_sigmoid_forward(aigDefaultContext(), H(data), outC_, numSigmoid_, outNCHW_), layerName_);
+  return data;
+}
+
+// ------------------------------------------------------------------------------------------ FCLayer
+FCLayer::FCLayer(cudnnHandle_t cudnnHandle, cublasHandle_t, int batchSize, int inputSize, int outputSize, const char* layerName,
+                 bool train, float)
+    : batchSize_(batchSize), inC_(inputSize), outC_(outputSize), ctx_(cudnnHandle) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  outNCHW_ = batchSize_ * outC_;
+  outDesc_ = {batchSize_, outC_, 1, 1};
+  weightCount_ = (size_t)inC_ * outC_;
+  check(ctx_, aig_fc_plan_create(ctx_, batchSize_, inC_, outC_, AIG_ACT_NONE, 0.f, /*two_step*/ 1, &plan_), layerName);
+  mallocZero(&weights_, weightCount_);
+  mallocZero(&bias_, (size_t)outC_);
+  mallocZero(&outData_, (size_t)outNCHW_);
+  SyncWeights();
+}
+FCLayer::~FCLayer() {
+  aig_conv_plan_destroy(plan_);
+  cudaFree(weights_); cudaFree(bias_); cudaFree(outData_);
+}
+void FCLayer::SyncWeights() {
+  check(ctx_, aig_fc_plan_set_weights(plan_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
+}
+__half* FCLayer::Forward(__half* data) {
+  check(ctx_, aig_conv_forward(plan_, H(data), nullptr, H(outData_)), layerName_);
+  return outData_;
+}
+void FCLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  loadArray(file, buffer, bias_, outC_ * sizeof(__half));
+  SyncWeights();
+}
+void FCLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {
+  saveArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  saveArray(file, buffer, bias_, outC_ * sizeof(__half));
+}
+
+// ------------------------------------------------------------------------------------------ ResConvLayer
+ResConvLayer::ResConvLayer(cudnnHandle_t cudnnHandle, int batchSize, int inChannels, int outChannels, int* inHeight, int* inWidth,
+                           const char* layerName, bool train)
+    : ctx_(cudnnHandle), batchSize_(batchSize) {
+  layerName_ = layerName;
+  train_ = train;
+  constexpr float wd = 0.000001f;
+  int resH = *inHeight, resW = *inWidth;
+  // ResConvLayer.cpp:13-21
+  layers_.push_back(new ConvLayer(ctx_, batchSize_, inChannels, outChannels, 4, 2, 1, inHeight, inWidth, "Conv0", train, wd));
+  layers_.push_back(new BatchNorm(ctx_, CUDNN_BATCHNORM_SPATIAL, batchSize_, outChannels, *inHeight, *inWidth, "Conv0 BatchNorm", train, wd));
+  layers_.push_back(new Activate(ctx_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outChannels, *inHeight, *inWidth, "Conv0 ReLU"));
+  layers_.push_back(new ConvLayer(ctx_, batchSize_, outChannels, outChannels, 3, 1, 1, inHeight, inWidth, "Conv1", train, wd));
+  layers_.push_back(new BatchNorm(ctx_, CUDNN_BATCHNORM_SPATIAL, batchSize_, outChannels, *inHeight, *inWidth, "Conv1 BatchNorm", train, wd));
+  residue_ = new ConvLayer(ctx_, batchSize_, inChannels, outChannels, 2, 2, 0, &resH, &resW, "Residue", train, wd);
+  if (resH != *inHeight || resW != *inWidth) throw std::runtime_error("ResConvLayer: main and shortcut output sizes differ");
+  resAct_ = new Activate(ctx_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outChannels, *inHeight, *inWidth, "Residue ReLU");
+  outNCHW_ = batchSize_ * outChannels * *inHeight * *inWidth;
+  outDesc_ = {batchSize_, outChannels, *inHeight, *inWidth};
+}
+ResConvLayer::~ResConvLayer() {
+  for (Layer* l : layers_) delete l;
+  delete residue_;
+  delete resAct_;
+}
+__half* ResConvLayer::Forward(__half* data) {
+  // ResConvLayer.cpp:28-37
+  __half* residue = residue_->Forward(data);
+  for (Layer* l : layers_) data = l->Forward(data);
+  check(ctx_, aig_add_forward(ctx_, H(data), H(residue), outNCHW_), layerName_);
+  return resAct_->Forward(data);
+}
+void ResConvLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  for (Layer* l : layers_) l->LoadParameters(file, buffer);
+  residue_->LoadParameters(file, buffer);
+}
+void ResConvLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {
+  for (Layer* l : layers_) l->SaveParameters(file, buffer);
+  residue_->SaveParameters(file, buffer);
+}
+size_t ResConvLayer::GetParameterSize() {
+  size_t m = residue_->GetParameterSize();
+  for (Layer* l : layers_) m = std::max(m, l->GetParameterSize());
+  return m;
+}
+
+// ------------------------------------------------------------------------------------------ LayerNorm
+LayerNorm::LayerNorm(int batchSize, int channels, int height, int width, const char* layerName, float)
+    : n_(batchSize), c_(channels), hw_(height * width) {
+  layerName_ = layerName;
+  outNCHW_ = n_ * c_ * hw_;
+  outDesc_ = {n_, c_, height, width};
+  mallocZero(&gamma_, (size_t)c_);
+  mallocZero(&beta_, (size_t)c_);
+  mallocZero(&mean_, (size_t)c_);
+  mallocZero(&variance_, (size_t)c_);
+  mallocZero(&outData_, (size_t)outNCHW_);
+  std::vector<float> ones(c_, 1.0f);
+  checkCuda(cudaMemcpy(gamma_, ones.data(), c_ * sizeof(float), cudaMemcpyHostToDevice), "gamma init");
+}
+LayerNorm::~LayerNorm() { cudaFree(gamma_); cudaFree(beta_); cudaFree(mean_); cudaFree(variance_); cudaFree(outData_); }
+__half* LayerNorm::Forward(__half* data) {
+  check(aigDefaultContext(), aig_layernorm_forward(aigDefaultContext(), H(outData_), H(data), gamma_, beta_, mean_, variance_, n_, c_, hw_, 1e-7f),
+        layerName_);
+  return outData_;
+}
+void LayerNorm::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, gamma_, c_ * sizeof(float));
+  loadArray(file, buffer, beta_, c_ * sizeof(float));
+}
+
+// ------------------------------------------------------------------------------------------ SpatialAttentionLayer
+SpatialAttentionLayer::SpatialAttentionLayer(cudnnHandle_t cudnnHandle, int attentionChannels, int batchSize, int channels, int height,
+                                             int width, const char* layerName, bool train, float)
+    : ctx_(cudnnHandle), attC_(attentionChannels), batchSize_(batchSize), inC_(channels), inH_(height), inW_(width) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  outNCHW_ = batchSize_ * inC_ * inH_ * inW_;
+  outDesc_ = {batchSize_, inC_, inH_, inW_};
+  const size_t kq = std::max((size_t)inC_ * 9, (size_t)attC_ * inC_);
+  const size_t maps = std::max((size_t)outNCHW_, (size_t)batchSize_ * inH_ * inW_ * attC_);
+  mallocZero(&keyWeights_, kq);
+  mallocZero(&queryWeights_, kq);
+  mallocZero(&valueWeights_, (size_t)inC_ * attC_);
+  mallocZero(&keyMap_, maps);
+  mallocZero(&queryMap_, maps);
+  mallocZero(&valueMap_, maps);
+  mallocZero(&attentionScores_, (size_t)batchSize_ * attC_ * inH_ * inW_);
+  mallocZero(&outData_, maps);
+}
+SpatialAttentionLayer::~SpatialAttentionLayer() {
+  __half* bufs[] = {keyWeights_, queryWeights_, valueWeights_, keyMap_, queryMap_, valueMap_, attentionScores_, outData_};
+  for (__half* b : bufs) cudaFree(b);
+}
+__half* SpatialAttentionLayer::Forward(__half* data) {
+  check(ctx_, aig_spatial_attention_forward(ctx_, H(data), H(keyWeights_), H(queryWeights_), H(valueWeights_), H(keyMap_), H(queryMap_),
+                                            H(valueMap_), H(attentionScores_), H(outData_), batchSize_, inC_, attC_, inH_, inW_, group_),
+        layerName_);
+  return outData_;
+}
+void SpatialAttentionLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, keyWeights_, (size_t)inC_ * 9 * sizeof(__half));
+  loadArray(file, buffer, queryWeights_, (size_t)inC_ * 9 * sizeof(__half));
+  loadArray(file, buffer, valueWeights_, (size_t)inC_ * attC_ * sizeof(__half));
+}
+
+// ------------------------------------------------------------------------------------------ LSTMLayer
+LSTMLayer::LSTMLayer(cudnnHandle_t cudnnHandle, int seqLength, int numLayers, int hiddenSize, int batchSize, int inC, const char* layerName,
+                     bool train)
+    : ctx_(cudnnHandle), seq_(seqLength), layers_(numLayers), hidden_(hiddenSize), batch_(batchSize), inC_(inC) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  // LSTMLayer.cpp:14-15: cell clip +-5, two bias vectors (the library default); seq-major tensors
+  check(ctx_, aig_lstm_plan_create(ctx_, seq_, layers_, hidden_, batch_, inC_, 5.0f, 1, 0, &plan_), layerName);
+  weightCount_ = aig_lstm_weight_count(inC_, hidden_, layers_, 1);
+  mallocZero(&weights_, weightCount_);
+  mallocZero(&outData_, (size_t)seq_ * batch_ * hidden_);
+  outNCHW_ = batch_ * hidden_;
+  outDesc_ = {batch_, hidden_, 1, 1};
+  check(ctx_, aig_lstm_plan_set_weights(plan_, H(weights_)), layerName);
+}
+LSTMLayer::~LSTMLayer() {
+  aig_lstm_plan_destroy(plan_);
+  cudaFree(weights_); cudaFree(outData_);
+}
+__half* LSTMLayer::Forward(__half* data) {
+  check(ctx_, aig_lstm_forward(plan_, H(data), H(outData_), nullptr, nullptr, 0), layerName_);
+  return outData_ + (size_t)(seq_ - 1) * batch_ * hidden_;  // LSTMLayer.cpp:103: the last step's rows
+}
+void LSTMLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+}
+
+// ------------------------------------------------------------------------------------------ MultiHeadAttentionLayer
+MultiHeadAttentionLayer::MultiHeadAttentionLayer(cudnnHandle_t cudnnHandle, cublasHandle_t, int batchSize, int seqLength, int embedSize,
+                                                 int numHeads, const char* layerName, bool train, float)
+    : ctx_(cudnnHandle), batch_(batchSize), seq_(seqLength), embed_(embedSize), heads_(numHeads) {
+  g_default_ctx = ctx_;
+  layerName_ = layerName;
+  train_ = train;
+  check(ctx_, aig_mha_plan_create(ctx_, batch_, seq_, embed_, heads_, 0.f, 0, &plan_), layerName);
+  const size_t ee = (size_t)embed_ * embed_;
+  mallocZero(&wq_, ee); mallocZero(&wk_, ee); mallocZero(&wv_, ee); mallocZero(&wo_, ee);
+  mallocZero(&outData_, (size_t)batch_ * seq_ * embed_);
+  weightCount_ = 4 * ee;
+  outNCHW_ = batch_ * seq_ * embed_;
+  outDesc_ = {batch_, seq_, embed_, 1};
+  check(ctx_, aig_mha_plan_set_weights(plan_, H(wq_), H(wk_), H(wv_), H(wo_)), layerName);
+}
+MultiHeadAttentionLayer::~MultiHeadAttentionLayer() {
+  aig_mha_plan_destroy(plan_);
+  cudaFree(wq_); cudaFree(wk_); cudaFree(wv_); cudaFree(wo_); cudaFree(outData_);
+}
+__half* MultiHeadAttentionLayer::Forward(__half* data) {
+  check(ctx_, aig_mha_forward(plan_, H(data), H(outData_), 0), layerName_);
+  return outData_;
+}
+void MultiHeadAttentionLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
+  const size_t bytes = (size_t)embed_ * embed_ * sizeof(__half);
+  loadArray(file, buffer, wq_, bytes);
+  loadArray(file, buffer, wk_, bytes);
+  loadArray(file, buffer, wv_, bytes);
+  loadArray(file, buffer, wo_, bytes);
+  check(ctx_, aig_mha_plan_set_weights(plan_, H(wq_), H(wk_), H(wv_), H(wo_)), layerName_);
+}
+
+// ------------------------------------------------------------------------------------------ NN
+NN::NN(cudnnHandle_t cudnnHandle, cublasHandle_t cublasHandle, int w, int h, bool train, const std::string& ckptFileName)
+    : cudnn_(cudnnHandle), cublas_(cublasHandle), batchSize_(40), seqLength_(1), inWidth_(0), inHeight_(0), maxBufferSize_(0) {
+  if (!train) batchSize_ = 1;  // NN.cpp:12
+  std::ifstream ckptFile(ckptFileName, std::ios::binary);
+  const bool fileOpen = ckptFile.is_open();
+  int netWidth = w, netHeight = h;
+  if (fileOpen) {  // NN.cpp:17-20
+    ckptFile.read(reinterpret_cast<char*>(&netWidth), sizeof(int));
+    ckptFile.read(reinterpret_cast<char*>(&netHeight), sizeof(int));
+  }
+  inWidth_ = netWidth;
+  inHeight_ = netHeight;
+  constexpr float wd = 0.000001f;
+  int outC = 32;  // NN.cpp:33-61
+  layers_.push_back(new ConvLayer(cudnn_, batchSize_, 3, outC, 2, 2, 0, &netHeight, &netWidth, "Conv0", train, wd));
+  layers_.push_back(new BatchNorm(cudnn_, CUDNN_BATCHNORM_SPATIAL, batchSize_, outC, netHeight, netWidth, "Conv0 BatchNorm", train, wd));
+  layers_.push_back(new Activate(cudnn_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outC, netHeight, netWidth, "Conv0 ReLU"));
+  layers_.push_back(new ResConvLayer(cudnn_, batchSize_, 32, 64, &netHeight, &netWidth, "ResConv0", train));
+  layers_.push_back(new ResConvLayer(cudnn_, batchSize_, 64, 128, &netHeight, &netWidth, "ResConv1", train));
+  layers_.push_back(new ResConvLayer(cudnn_, batchSize_, 128, 256, &netHeight, &netWidth, "ResConv2", train));
+  outC = 1024;
+  layers_.push_back(new FCLayer(cudnn_, cublas_, batchSize_, 256 * netHeight * netWidth, outC, "FC0", train, wd));
+  layers_.push_back(new BatchNorm(cudnn_, CUDNN_BATCHNORM_PER_ACTIVATION, batchSize_, outC, 1, 1, "FC0 BatchNorm", train, wd));
+  layers_.push_back(new Activate(cudnn_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outC, 1, 1, "FC0 ReLU"));
+  outC = 512;
+  layers_.push_back(new FCLayer(cudnn_, cublas_, batchSize_, 1024, outC, "FC1", train, wd));
+  layers_.push_back(new BatchNorm(cudnn_, CUDNN_BATCHNORM_PER_ACTIVATION, batchSize_, outC, 1, 1, "FC1 BatchNorm", train, wd));
+  layers_.push_back(new Activate(cudnn_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outC, 1, 1, "FC1 ReLU"));
+  outC = 256;
+  layers_.push_back(new FCLayer(cudnn_, cublas_, batchSize_, 512, outC, "FC2", train, wd));
+  layers_.push_back(new BatchNorm(cudnn_, CUDNN_BATCHNORM_PER_ACTIVATION, batchSize_, outC, 1, 1, "FC2 BatchNorm", train, wd));
+  layers_.push_back(new Activate(cudnn_, CUDNN_ACTIVATION_RELU, 1.0, batchSize_, outC, 1, 1, "FC2 ReLU"));
+  outC = numCtrls_;
+  layers_.push_back(new FCLayer(cudnn_, cublas_, batchSize_, 256, outC, "FC Out", train, wd));
+  layers_.push_back(new Sigmoid(numButs_, batchSize_, outC, "Sigmoid"));
+  for (Layer* layer : layers_) maxBufferSize_ = std::max(maxBufferSize_, layer->GetParameterSize());
+  if (fileOpen) {  // NN.cpp:64-75
+    unsigned char* buffer = nullptr;
+    checkCuda(cudaMallocHost(reinterpret_cast<void**>(&buffer), maxBufferSize_), "cudaMallocHost");
+    try {
+      for (Layer* layer : layers_) layer->LoadParameters(ckptFile, buffer);
+    } catch (...) {
+      cudaFreeHost(buffer);
+      throw;
+    }
+    cudaFreeHost(buffer);
+  }
+}
+NN::~NN() {
+  for (Layer* l : layers_) delete l;
+}
+__half* NN::Forward(__half* data) {  // NN.cpp:93-100
+  for (Layer* layer : layers_) data = layer->Forward(data);
+  return data;
+}
+
+// ------------------------------------------------------------------------------------------ C hooks (tests, other languages)
+extern "C" {
+
+static thread_local std::string g_layers_error;
+const char* aig_layers_last_error() { return g_layers_error.c_str(); }
+
+// new NN(handle, handle, w, h, /*train*/false, ckpt_path): the reference's own network through the layer classes
+int aig_refnn_create(aig_ctx* ctx, int w, int h, const char* ckpt_path, void** out) {
+  if (!ctx || !ckpt_path || !out) return AIG_ERR_INVALID;
+  try {
+    *out = new NN(ctx, ctx, w, h, false, ckpt_path);
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_INVALID;
+  }
+}
+// NN::Forward on one planar fp16 frame [3][h][w]; *out_dev = the network's output buffer (numCtrls_ halves)
+int aig_refnn_forward(void* nn, aig_half* x_nchw_dev, const aig_half** out_dev) {
+  if (!nn || !x_nchw_dev || !out_dev) return AIG_ERR_INVALID;
+  try {
+    *out_dev = reinterpret_cast<const aig_half*>(static_cast<NN*>(nn)->Forward(reinterpret_cast<__half*>(x_nchw_dev)));
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_CUDA;
+  }
+}
+int aig_refnn_input_size(void* nn, int* w, int* h) {
+  if (!nn) return AIG_ERR_INVALID;
+  if (w) *w = static_cast<NN*>(nn)->inWidth_;
+  if (h) *h = static_cast<NN*>(nn)->inHeight_;
+  return AIG_OK;
+}
+int aig_refnn_destroy(void* nn) {
+  delete static_cast<NN*>(nn);
+  return AIG_OK;
+}
+
+}  // extern "C"

@@ -2,7 +2,7 @@
 (include/aig_host.h: aig_seq_*, aig_agent_*).  Thin: every method is one C call."""
 import ctypes
 
-from . import (AIG_CNN_MAX_BLOCKS, ACT_SWISH, AigError, CnnConfig, SeqConfig, c_int, c_void_p, lib, ptr)
+from . import (AIG_C3D_MAX_LAYERS, AIG_CNN_MAX_BLOCKS, ACT_SWISH, AigError, C3dConfig, CnnConfig, SeqConfig, c_int, c_void_p, lib, ptr)
 
 
 def _device_copy(ctx, addr, shape, dtype):
@@ -109,4 +109,47 @@ class Agent:
     def close(self):
         if self.handle:
             lib().aig_agent_destroy(self.handle)
+            self.handle = c_void_p()
+
+
+class ClipEncoder:
+    """Temporal clip encoder (aig_c3d_*): Conv3D+BN+LeakyReLU layers, 2x2 adaptive pool, FC head."""
+
+    def __init__(self, ctx, batch, depth, height, width, widths=(3, 32, 64, 128), n_out=18, n_sigmoid=16, slope=0.01):
+        self.ctx = ctx
+        w = (c_int * (AIG_C3D_MAX_LAYERS + 1))(*widths)
+        self.cfg = C3dConfig(batch, depth, height, width, len(widths) - 1, w, n_out, n_sigmoid, slope)
+        self.handle = c_void_p()
+        rc = lib().aig_c3d_create(ctx.handle, ctypes.byref(self.cfg), ctypes.byref(self.handle))
+        if rc != 0:
+            raise AigError(rc, lib().aig_last_error(ctx.handle).decode())
+
+    def check(self, rc):
+        if rc != 0:
+            raise AigError(rc, lib().aig_c3d_last_error(self.handle).decode())
+
+    def param_bytes(self):
+        return lib().aig_c3d_param_bytes(ctypes.byref(self.cfg))
+
+    def load_bytes(self, blob):
+        buf = (ctypes.c_char * len(blob)).from_buffer_copy(blob)
+        self.check(lib().aig_c3d_load_memory(self.handle, ctypes.cast(buf, c_void_p), len(blob)))
+
+    def forward(self, clips_dev):
+        self.check(lib().aig_c3d_forward(self.handle, ptr(clips_dev)))
+
+    def outputs_f32(self):
+        import torch
+
+        return _device_copy(self.ctx, lib().aig_c3d_outputs_f32(self.handle), (self.cfg.batch, self.cfg.n_out), torch.float32)
+
+    def features(self):
+        import torch
+
+        feat = self.cfg.widths[self.cfg.n_layers] * 4
+        return _device_copy(self.ctx, lib().aig_c3d_features(self.handle), (self.cfg.batch, feat), torch.float16)
+
+    def close(self):
+        if self.handle:
+            lib().aig_c3d_destroy(self.handle)
             self.handle = c_void_p()

@@ -167,6 +167,49 @@ def serialize_agent_params(p, width, height):
                      serialize_seq_params(p["seq"])])
 
 
+def make_refnn_params(seed, width, height):
+    """Parameters of the network the reference itself builds (NN.cpp:33-61) for a width x height input."""
+    rng = np.random.default_rng(seed)
+    p = dict(width=width, height=height)
+    p["c0w"] = he_normal(rng, (32, 3, 2, 2))
+    p["c0b"] = bias_params(rng, 32, False)
+    p["bn0"] = bn_params(rng, 32, False)
+    p["res"] = [make_resconv_params(rng, a, b, False) for a, b in ((32, 64), (64, 128), (128, 256))]
+    h, w = height // 2, width // 2
+    for _ in range(3):
+        h, w = (h + 2 - 4) // 2 + 1, (w + 2 - 4) // 2 + 1
+    p["fc"] = []
+    dims = [256 * h * w, 1024, 512, 256]
+    for i in range(3):
+        W = (rng.standard_normal((dims[i], dims[i + 1])) * math.sqrt(2.0 / dims[i])).astype(F16)
+        p["fc"].append(dict(W=W, b=bias_params(rng, dims[i + 1], False), bn=bn_params(rng, dims[i + 1], False)))
+    p["outW"] = (rng.standard_normal((256, 16)) * math.sqrt(2.0 / 256)).astype(F16)
+    p["outb"] = bias_params(rng, 16, False)
+    return p
+
+
+def serialize_refnn_checkpoint(p):
+    """The reference's checkpoint file (NN.cpp:113-128): int32 w, h, then each layer's payload."""
+    out = [np.array([p["width"], p["height"]], np.int32).tobytes(), p["c0w"].tobytes(), p["c0b"].tobytes(), _bn_bytes(p["bn0"])]
+    for blk in p["res"]:
+        out += [blk["c0w"].tobytes(), blk["c0b"].tobytes(), _bn_bytes(blk["bn0"]), blk["c1w"].tobytes(), blk["c1b"].tobytes(),
+                _bn_bytes(blk["bn1"]), blk["sw"].tobytes(), blk["sb"].tobytes()]
+    for L in p["fc"]:
+        out += [L["W"].tobytes(), L["b"].tobytes(), _bn_bytes(L["bn"])]
+    out += [p["outW"].tobytes(), p["outb"].tobytes()]
+    return b"".join(out)
+
+
 def make_embeddings(seed, T, B, d):
     rng = np.random.default_rng(seed + 3000003)
     return rng.standard_normal((T, B, d)).astype(F16)
+
+
+def serialize_conv3d_params(p):
+    """Clip-encoder blob: per layer the ConvLayer3D payload (w, b; ConvLayer3D.cpp:128-139) and the
+    BatchNorm payload, then the FC head (W [in][out], b)."""
+    out = []
+    for L in p["layers"]:
+        out += [L["w"].tobytes(), L["b"].tobytes(), _bn_bytes(L["bn"])]
+    out += [np.ascontiguousarray(p["fcW"], F16).tobytes(), np.ascontiguousarray(p["fcb"], F16).tobytes()]
+    return b"".join(out)

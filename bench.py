@@ -101,6 +101,7 @@ def cpu_oracle_rate(frames_per_sample, repeats):
     from oracle import pipelines as PL
 
     O.build()
+    O.set_threads(os.cpu_count() or 1)  # launchers export OMP_NUM_THREADS=1 for their ranks; this leg wants every core
     params = PL.make_cnn_params(0, widths=WIDTHS)
     frames = PL.make_frames(0, frames_per_sample, HEIGHT, WIDTH)
     PL.cnn_forward(params, frames[:1])  # warm

@@ -115,6 +115,42 @@ int aig_agent_step_host(aig_agent* a, const uint8_t* bgra_host, float* out_host)
 int aig_agent_reset(aig_agent* a);
 const float* aig_agent_outputs_f32(aig_agent* a);
 
+/* ---------------------------------------------------------------------------------------------
+ * Temporal clip encoder: n_layers of ConvLayer3D(k 3x3x3, stride 1x2x2, pad 1) -> BatchNorm -> LeakyReLU
+ * (ConvLayer3D.cpp:106-111) with channel widths[0]=3 .. widths[n_layers], adaptive average pool to 2x2
+ * cells (mean over depth), FC -> n_out, sigmoid on the first n_sigmoid outputs and tanh on the rest. */
+#define AIG_C3D_MAX_LAYERS 6
+typedef struct aig_c3d_config {
+  int batch, depth, height, width;
+  int n_layers;
+  int widths[AIG_C3D_MAX_LAYERS + 1];
+  int n_out, n_sigmoid;
+  float slope;
+} aig_c3d_config;
+typedef struct aig_c3d aig_c3d;
+int aig_c3d_create(aig_ctx* ctx, const aig_c3d_config* cfg, aig_c3d** out);
+int aig_c3d_destroy(aig_c3d* m);
+const char* aig_c3d_last_error(aig_c3d* m);
+size_t aig_c3d_param_bytes(const aig_c3d_config* cfg);
+/* Per layer: ConvLayer3D payload (half w[K][C][3][3][3], half b[K]; ConvLayer3D.cpp:128-139) then the
+ * BatchNorm payload (six float[K]; BatchNorm.cpp:90-117); then FC half W[in][out], half b[out]. */
+int aig_c3d_load_memory(aig_c3d* m, const void* blob, size_t bytes);
+/* clips: planar fp16 [batch][3][depth][height][width] (device).  Asynchronous on the context stream. */
+int aig_c3d_forward(aig_c3d* m, const aig_half* clips);
+const float* aig_c3d_outputs_f32(aig_c3d* m);   /* [batch][n_out] */
+const aig_half* aig_c3d_features(aig_c3d* m);   /* [batch][widths[n_layers]*4] pooled features */
+
+/* ---------------------------------------------------------------------------------------------
+ * The reference's own network through the C++ layer classes (ai-gamer_b200/host/layers/Layers.h, the
+ * reference-compatible `Layer` subclasses and `NN`): new NN(handle, handle, w, h, train=false) with the
+ * checkpoint path as an argument (NN.cpp:11-91), NN::Forward on one planar fp16 frame [3][h][w]
+ * (NN.cpp:93-100).  C hooks for tests and other languages; C++ callers use the classes directly. */
+int aig_refnn_create(aig_ctx* ctx, int w, int h, const char* ckpt_path, void** out);
+int aig_refnn_forward(void* nn, aig_half* x_nchw_dev, const aig_half** out_dev);
+int aig_refnn_input_size(void* nn, int* w, int* h);
+int aig_refnn_destroy(void* nn);
+const char* aig_layers_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,6 +14,8 @@
 // delegates to cuDNN/cuBLAS (convolution, BatchNorm, GEMM, LSTM, multi-head attention) is
 // "parity unpinned": the closed libraries' accumulation order, the cuDNN LSTM weight-blob layout
 // and the attention weight orientation are fixed here by definition (stated per function).
+#include <omp.h>
+
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -45,6 +47,14 @@ static inline float hround(float v) { return h2f(f2h(v)); }
 extern "C" {
 
 int orc_version() { return 1; }
+
+// Threads the OpenMP loops below use; returns the previous maximum.  The environment variable is read
+// once when the OpenMP runtime is loaded, which may be before the caller can set it.
+int orc_set_threads(int n) {
+  int prev = omp_get_max_threads();
+  if (n > 0) omp_set_num_threads(n);
+  return prev;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Preprocessing.  CudaStuff.cu:63-74 (cuARGBtoRGBplanar): pixel bytes are (B,G,R,A); plane 0 = R,

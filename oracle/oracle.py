@@ -44,6 +44,11 @@ def lib():
     return _LIB
 
 
+def set_threads(n):
+    """Threads used by the oracle's OpenMP loops; returns the previous maximum."""
+    return lib().orc_set_threads(int(n))
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(_vp)
 

@@ -88,3 +88,17 @@ def seq_forward(p, emb, rope_base=10000.0, window=0, n_sigmoid=16, pos0=0, h_sta
     logits = O.fc(n.reshape(B * T, -1), p["fcW"], p["fcb"])
     out = O.tanh_tail(O.sigmoid_head(logits, p["n_out"], n_sigmoid), p["n_out"], n_sigmoid)
     return y, a, logits.reshape(B, T, -1), out.reshape(B, T, -1)
+
+
+def refnn_forward(p, x_nchw):
+    """The network NN::NN builds (NN.cpp:33-61) on planar fp16 frames [B][3][H][W]: Conv k2 s2 + BN + ReLU,
+    three ResConv blocks (ReLU), three FC + per-activation BN + ReLU, FC(16), Sigmoid on the first 14."""
+    x = O.conv2d(x_nchw, p["c0w"], p["c0b"], 2, 0)
+    x = O.relu(O.batchnorm(x, *p["bn0"]))
+    for blk in p["res"]:
+        x = resconv_forward(x, blk, O.ACT_RELU)
+    x = x.reshape(x.shape[0], -1)
+    for L in p["fc"]:
+        x = O.relu(O.batchnorm(O.fc(x, L["W"], L["b"]), *L["bn"], per_activation=True))
+    y = O.fc(x, p["outW"], p["outb"])
+    return O.sigmoid_head(y, 16, 14)

@@ -90,3 +90,58 @@ def test_streaming_agent_matches_oracle(env):
         agent.step_host(torch.from_numpy(frames[t]).pin_memory(), out_h)
         assert np.array_equal(out_h.numpy(), got[:, t])
     agent.close()
+
+
+@gpu
+def test_clip_encoder_matches_oracle(env):
+    """Conv3D temporal encoder (three Conv3D+BN+LeakyReLU layers, 2x2 adaptive pool, FC head) on short
+    clips against the oracle composition, with non-trivial BatchNorm statistics and biases."""
+    U = env
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    B, D, H, W = 2, 4, 32, 64
+    p = PL.make_conv3d_params(7, trivial=False)
+    clips = PL.make_clips(7, B, D, H, W)
+    feat, logits, want = PL.conv3d_forward(p, clips)
+    enc = R.ClipEncoder(U.ctx(), B, D, H, W)
+    blob = PL.serialize_conv3d_params(p)
+    assert len(blob) == enc.param_bytes()
+    enc.load_bytes(blob)
+    enc.forward(U.dev(clips))
+    got_feat = U.host(enc.features()).astype(np.float32)
+    assert U.scaled_err(got_feat, feat.astype(np.float32)) < 1e-2
+    got = U.host(enc.outputs_f32())
+    assert U.rel_err(got, want.astype(np.float32), 0.05).max() < TOL
+    # a second call on the same buffers is deterministic
+    enc.forward(U.dev(clips))
+    assert np.array_equal(U.host(enc.outputs_f32()), got)
+    with pytest.raises(Exception, match="size"):
+        enc.load_bytes(blob[:-2])                            # a short blob is refused before anything is copied
+    enc.close()
+
+
+@gpu
+def test_fc_layernorm_swish_twin(env):
+    """The CPU-runnable configuration's GPU twin: FC 1024->1024, row LayerNorm (eps 1e-5), Swish on 32 rows."""
+    U = env
+    pk = U.pkg()
+    import torch
+
+    c = U.ctx()
+    rows, d = 32, 1024
+    p = PL.make_fc_ln_params(11, d, d)
+    x = np.random.default_rng(11).standard_normal((rows, d)).astype(np.float16)
+    want = PL.fc_ln_swish_forward(p, x)
+    plan = pk.FcPlan(c, rows, d, d, two_step=True)
+    dW, db, dg, dbeta, dx = (U.dev(a) for a in (p["W"], p["b"], p["gamma"], p["beta"], x))  # kept alive to the sync
+    plan.set_weights(dW, db)
+    y = torch.empty((rows, d), dtype=torch.float16, device="cuda")
+    plan.forward(dx, y)
+    z = torch.empty_like(y)
+    c.call("aig_layernorm_rows_forward", U.p(z), U.p(y), U.p(dg), U.p(dbeta), rows, d, 1e-5)
+    c.call("aig_swish_forward", U.p(z), rows * d)
+    c.sync()
+    got = U.host(z).astype(np.float32)
+    assert np.abs(got - want.astype(np.float32)).max() < 6e-3
+    assert U.rel_err(got, want.astype(np.float32), 0.05).max() < TOL
