@@ -83,7 +83,12 @@ __device__ __forceinline__ float act_apply(float v, int act, float slope) {
 __device__ __forceinline__ float act_apply_fast(float v, int act, float slope) {
   switch (act) {
     case AIG_ACT_RELU: return v > 0.f ? v : 0.f;
-    case AIG_ACT_SWISH: return v * __frcp_rn(1.0f + __expf(-v));
+    case AIG_ACT_SWISH: {
+      float e, r;
+      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
+      asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+      return v * r;
+    }
     case AIG_ACT_LEAKY: return v < 0.f ? v * slope : v;
     default: return v;
   }
@@ -186,6 +191,24 @@ __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same, with the descriptors given as their low words plus the one high word both share: for 128-byte
+// rows the high word (stride, version, swizzle) is a constant and the low word is linear in the
+// address, so an issue loop advances descriptors with one 32-bit add each.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ constexpr uint32_t umma_desc_hi(uint32_t row_bytes) {
+  return ((row_bytes * 8u) >> 4) | (1u << 14) | ((row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u)) << 29);
+}
+__device__ __forceinline__ void umma_f16_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // mbarrier arrives once all previously issued tcgen05.mma of this thread have completed.

@@ -17,6 +17,7 @@
 // warps 2..9 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
 // Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all
 // roles drain to the common exit where TMEM is freed.
+#include <cstdlib>
 #include <vector>
 
 #include "aig_common.cuh"
@@ -67,9 +68,70 @@ struct IgemmCfg {
 template <int ACT>
 __device__ __forceinline__ float act_ct(float v, float slope) {
   if (ACT == AIG_ACT_RELU) return fmaxf(v, 0.f);
-  if (ACT == AIG_ACT_SWISH) return v * __frcp_rn(1.0f + __expf(-v));
+  if (ACT == AIG_ACT_SWISH) {
+    // v * sigmoid(v) with the SFU's ex2 and rcp approximations (about 2 ulp of fp32 each, far below
+    // the fp16 rounding of the result); an IEEE reciprocal here costs several times the rest of the epilogue
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return v * r;
+  }
   if (ACT == AIG_ACT_LEAKY) return v < 0.f ? v * slope : v;
   return v;
+}
+
+// 32 accumulator columns of one TMEM lane (= one output pixel) per step: one TMEM load, the residual
+// row segment fetched as four 16-byte loads issued before the TMEM wait, 32 FMAs + activations, four
+// 16-byte stores.  Used whenever a warp's column range is a multiple of 32.
+template <int ACT, bool RES>
+__device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
+                                                 const float* __restrict__ sc, const float* __restrict__ sf,
+                                                 const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
+                                                 bool valid) {
+#pragma unroll 1
+  for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_addr + c0, r);
+    const int n0 = n_base + c0;
+    uint4 rv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) rv[i] = make_uint4(0, 0, 0, 0);
+    if (RES && valid) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (n0 + 8 * i < out_c) rv[i] = __ldg(reinterpret_cast<const uint4*>(rrow + n0 + 8 * i));
+    }
+    tmem_ld_wait();
+    if (valid) {
+#pragma unroll
+      for (int v8 = 0; v8 < 4; ++v8) {
+        if (n0 + v8 * 8 >= out_c) break;
+        const float4 s0 = reinterpret_cast<const float4*>(sc + c0)[2 * v8], s1 = reinterpret_cast<const float4*>(sc + c0)[2 * v8 + 1];
+        const float4 h0 = reinterpret_cast<const float4*>(sf + c0)[2 * v8], h1 = reinterpret_cast<const float4*>(sf + c0)[2 * v8 + 1];
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const __half2* rh = reinterpret_cast<const __half2*>(&rv[v8]);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int e2 = 0; e2 < 4; ++e2) {
+          const int e = v8 * 8 + e2 * 2;
+          float a0 = fmaf(__uint_as_float(r[e]), sv[e2 * 2], hv[e2 * 2]);
+          float a1 = fmaf(__uint_as_float(r[e + 1]), sv[e2 * 2 + 1], hv[e2 * 2 + 1]);
+          if (RES) {
+            // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
+            const float2 m = __half22float2(__floats2half2_rn(a0, a1));
+            const float2 rr = __half22float2(rh[e2]);
+            const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+            a0 = t.x;
+            a1 = t.y;
+          }
+          oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+        }
+        *reinterpret_cast<uint4*>(yrow + n0 + v8 * 8) = o;
+      }
+    }
+  }
 }
 
 template <int ACT, bool RES>
@@ -297,14 +359,14 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait_bounded(bar_full + 8 * stage, phase, s_abort, p.gerr, 202)) { ok = false; break; }
           const uint32_t a0 = sA + stage * Cfg::kABytes, b0 = sB + stage * Cfg::kBBytes;
+          const uint32_t a_lo = umma_desc_lo(a0), b_lo = umma_desc_lo(b0);
+          const uint32_t first = kb != 0 ? 1u : 0u;
 #pragma unroll
           for (int sub = 0; sub < MS; ++sub) {
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
-              const uint64_t adesc = umma_smem_desc(a0 + sub * Cfg::kSubBytes + k * 32, BK * 2);
-              const uint64_t bdesc = umma_smem_desc(b0 + k * 32, BK * 2);
-              umma_f16_ss(d_tmem + (uint32_t)(sub * NT), adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < BK / 16; ++k)
+              umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * Cfg::kSubBytes + k * 32) >> 4),
+                             b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(BK * 2), idesc, k == 0 ? first : 1u);
           }
           umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -346,7 +408,10 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q * 32) << 16);
         if (fast) {
 #define AIG_EPI(ACT)                                                                                                  \
-  if (rrow) epi_fused_cols<ACT, true>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid);      \
+  if (NT >= 64) {                                                                                                     \
+    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid);   \
+    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid);       \
+  } else if (rrow) epi_fused_cols<ACT, true>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid); \
   else epi_fused_cols<ACT, false>(t_addr, col_lo, col_hi, nb, p.out_c, sc, sf, rrow, yrow, p.slope, valid)
           switch (p.act) {
             case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
@@ -375,6 +440,311 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+
+// ==========================================================================================
+// Patch-resident convolution (stride 1, 2-D, in_c a multiple of 64).
+//
+// The streamed kernel above fetches one shifted copy of the activation tile per filter tap, so a
+// 3x3 layer moves 9x its input from L2 to shared memory, and L2->SM bandwidth (about 25 B/clk/SM)
+// is what bounds it.  Here the input patch of a tile is loaded once and every tap reads it in place.
+//
+// Flattened virtual pixel space: with padding p on every side, image row y of image n becomes virtual
+// row vr = n*RP + y + p (RP = H + p: the bottom padding rows of one image are the top padding rows
+// of the next), and pixel x sits at virtual column vc = x + p of a row of pitch P = W + p (the right
+// padding of one row is the left padding of the next).  With q = vr*P + vc, the input of output
+// position q for tap (fr, fs) is position q + fr*P + fs: one uniform shift per tap.  An M tile is M
+// consecutive positions q; its A operand for a tap is M consecutive 128-byte rows of the patch in
+// shared memory starting (fr*P + fs) rows further on, addressed by the UMMA descriptor alone.  Each
+// virtual row is one TMA box of P pixels x 64 channels starting at x = -p; padding and rows past the
+// batch are zero-filled by TMA.  Positions with vc >= Wo or vr % RP >= Ho are computed and dropped.
+// Weights stay resident in shared memory for the whole launch when they fit beside two patches,
+// otherwise they stream through a ring of (tap, 64-channel block) stages shared by the MS sub-tiles.
+struct OutSeg {
+  __half* y;                // destination, channels-last
+  const __half* residual;   // same layout as y, or null
+  int channels;             // channels of this destination (= leading dimension)
+  int c0;                   // first GEMM column of this segment
+  int act;
+  int s2d;                  // 1: store into the 2x2 space-to-depth layout read by the next stride-2 block
+  int Hb, Wb;               // block extents of that layout
+};
+
+struct PconvParams {
+  int P, RP, pad, kw, taps, cblocks;
+  int Ho, Wo, batch;
+  int m_tiles, n_tiles;
+  int patch_vrows, region_bytes, patch_bytes;
+  int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
+  int acc_bufs;            // TMEM accumulator buffers: 2, or 1 when MS*NT fills all 512 columns
+  int n_split;             // GEMM columns >= n_split go to seg[1]
+  int sparse_tile0;        // N tiles >= this one use the sparse shortcut K schedule (INT_MAX: none)
+  int sub_cblocks;         // 64-channel blocks per space-to-depth sub-position (sparse schedule)
+  float slope;
+  const float* scale;
+  const float* shift;
+  OutSeg seg[2];
+  int* gerr;
+  long long* ts;           // optional timeline of CTA 0 (8 stamps per tile, first 16 tiles), or null
+};
+
+// A operand descriptors here start on any 128-byte row of a 1024-byte swizzle atom, not only on its
+// first.  That needs nothing extra in the descriptor: TMA writes and the MMA reads the 128-byte
+// swizzle as a function of the absolute shared-memory address bits [7,10), so a tile that starts r
+// rows into an atom is read consistently (verified against the CPU oracle; setting the descriptor's
+// base-offset field to the row phase gives wrong results).
+
+// K schedule of one N tile as an iterator over (tap, 64-channel block) without divisions.  The dense
+// schedule walks every block of every tap; the sparse one (shortcut rows of a fused down-sampling
+// GEMM, 2x2 taps) only the blocks of the one space-to-depth sub-position that tap reads.
+struct PconvKIter {
+  int tap, fr, fs, l, cb, lim;
+  bool sparse;
+  __device__ __forceinline__ void start(const PconvParams& p, bool sp) {
+    sparse = sp;
+    tap = fr = fs = l = 0;
+    lim = sp ? p.sub_cblocks : p.cblocks;
+    cb = sp ? 3 * p.sub_cblocks : 0;
+  }
+  __device__ __forceinline__ void next(const PconvParams& p) {
+    ++l;
+    ++cb;
+    if (l == lim) {
+      l = 0;
+      ++tap;
+      if (++fs == p.kw) { fs = 0; ++fr; }
+      cb = sparse ? ((1 - fr) * 2 + (1 - fs)) * p.sub_cblocks : 0;
+    }
+  }
+};
+
+template <int NT, int MS, bool WRES>
+__global__ void __launch_bounds__(kNumThreads, 1)
+pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const PconvParams p) {
+  constexpr int kM = MS * kTileM;
+  constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  const uint32_t sPatch = base;
+  const uint32_t sW = base + 2 * p.patch_bytes;
+  const uint32_t tail = 2 * p.patch_bytes + p.w_stages * kWBlock;
+  float* s_scale = reinterpret_cast<float*>(sm + tail);
+  float* s_shift = s_scale + 256;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 2048);
+  const uint32_t bar_pfull = smem_u32(bars);          // [2]
+  const uint32_t bar_pempty = bar_pfull + 16;         // [2]
+  const uint32_t bar_tfull = bar_pfull + 32;          // [2]
+  const uint32_t bar_tempty = bar_pfull + 48;         // [2]
+  const uint32_t bar_wfull = bar_pfull + 64;          // [w_stages] (resident: [0] only)
+  const uint32_t bar_wempty = bar_wfull + 8 * 32;     // [w_stages]
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8 + 64);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (p.n_tiles == 1) {
+    for (int i = threadIdx.x; i < NT; i += kNumThreads) {
+      s_scale[i] = p.scale[i];
+      s_shift[i] = p.shift[i];
+    }
+  }
+  if (threadIdx.x == 0) {
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_pfull + 8 * a, 1);
+      mbar_init(bar_pempty + 8 * a, 1);
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 8);
+    }
+    const int nw = WRES ? 1 : p.w_stages;
+    for (int s = 0; s < nw; ++s) {
+      mbar_init(bar_wfull + 8 * s, 1);
+      mbar_init(bar_wempty + 8 * s, 1);
+    }
+    *s_abort = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmapA);
+    tma_prefetch_desc(&tmapB);
+  }
+  constexpr uint32_t kTmemCols = (2 * MS * NT > 512) ? 512u : (uint32_t)(2 * MS * NT);
+  if (warp == 1) {
+    tmem_alloc(smem_u32(s_tmem), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+  const int dense_kb = p.taps * p.cblocks, sparse_kb = p.taps * p.sub_cblocks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      if (WRES) {
+        mbar_expect_tx(bar_wfull, (uint32_t)(dense_kb * kWBlock));
+        for (int kb = 0; kb < dense_kb; ++kb) tma_load_2d(sW + kb * kWBlock, &tmapB, bar_wfull, kb * 64, 0);
+      }
+      auto load_patch = [&](int m_tile, int it) -> bool {
+        const int buf = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) return false;
+        mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.cblocks));
+        const long long q0 = (long long)m_tile * kM;
+        const int vr0 = (int)(q0 / p.P);
+        const uint32_t dst0 = sPatch + buf * p.patch_bytes;
+        for (int r = 0; r < p.patch_vrows; ++r) {
+          const int vr = vr0 + r;
+          const int n = vr / p.RP, yy = vr - n * p.RP;
+          for (int cb = 0; cb < p.cblocks; ++cb)
+            tma_load_5d(dst0 + cb * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, cb * 64, -p.pad, yy - p.pad, 0, n);
+        }
+        return true;
+      };
+      int it = 0;
+      int stage = 0;
+      uint32_t wphase = 0;
+      if ((int)blockIdx.x < p.m_tiles) ok = load_patch(blockIdx.x, 0);
+      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
+        const int next = m_tile + gridDim.x;
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
+        if (next < p.m_tiles) ok = load_patch(next, it + 1);  // under this tile's MMAs
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
+        if (!WRES) {
+          for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile) {
+            const bool sparse = n_tile >= p.sparse_tile0;
+            const int nkb = sparse ? sparse_kb : dense_kb;
+            PconvKIter ki;
+            ki.start(p, sparse);
+            for (int kb = 0; kb < nkb; ++kb, ki.next(p)) {
+              if (!mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)) { ok = false; break; }
+              mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
+              tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (ki.tap * p.cblocks + ki.cb) * 64, n_tile * NT);
+              if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
+            }
+          }
+        }
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 2] = clock64();
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
+      bool ok = true;
+      if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
+      int it = 0, cnt = 0, stage = 0;
+      uint32_t wphase = 0;
+      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(it >> 1) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 3] = clock64();
+        const long long q0 = (long long)m_tile * kM;
+        const int off0 = (int)(q0 - (q0 / p.P) * p.P);
+        const uint32_t patch = sPatch + buf * p.patch_bytes;
+        for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile, ++cnt) {
+          const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
+          const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
+          if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 503)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
+          const bool sparse = n_tile >= p.sparse_tile0;
+          const int nkb = sparse ? sparse_kb : dense_kb;
+          PconvKIter ki;
+          ki.start(p, sparse);
+          for (int kb = 0; kb < nkb; ++kb, ki.next(p)) {
+            uint32_t b0;
+            if (WRES) {
+              b0 = sW + kb * kWBlock;
+            } else {
+              if (!mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
+              b0 = sW + stage * kWBlock;
+            }
+            const uint32_t a0 = patch + ki.cb * p.region_bytes + (uint32_t)(off0 + ki.fr * p.P + ki.fs) * 128u;
+            const uint32_t a_lo = umma_desc_lo(a0), b_lo = umma_desc_lo(b0);
+            const uint32_t first = kb != 0 ? 1u : 0u;
+#pragma unroll
+            for (int sub = 0; sub < MS; ++sub) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
+                               b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+            }
+            if (!WRES) {
+              umma_commit(bar_wempty + 8 * stage);
+              if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
+            }
+          }
+          if (ok) umma_commit(bar_tfull + 8 * acc);
+        }
+        if (ok) umma_commit(bar_pempty + 8 * buf);  // the patch may be overwritten once these MMAs have read it
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 4] = clock64();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int q4 = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int col_lo = half * (NT / 2), col_hi = col_lo + NT / 2;
+    const int row_in_tile = q4 * 32 + lane;
+    int cnt = 0;
+    bool ok = true;
+    for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x) {
+      for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile, ++cnt) {
+        const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
+        const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
+        const int nb = n_tile * NT;
+        const float* sc = p.n_tiles == 1 ? s_scale : p.scale + nb;
+        const float* sf = p.n_tiles == 1 ? s_shift : p.shift + nb;
+        const OutSeg& sg = p.seg[(nb + col_lo) >= p.n_split ? 1 : 0];
+        if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
+        tc_fence_after();
+        if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 5] = clock64();
+#pragma unroll 1
+        for (int sub = 0; sub < MS; ++sub) {
+          const long long q = (long long)m_tile * kM + sub * kTileM + row_in_tile;
+          const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
+          const int n = vr / p.RP, yy = vr - n * p.RP;
+          const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
+          size_t pix;
+          if (sg.s2d) {
+            const int by = (yy + 1) >> 1, bx = (vc + 1) >> 1, sp = ((yy + 1) & 1) * 2 + ((vc + 1) & 1);
+            pix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
+          } else {
+            pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
+          }
+          __half* yrow = sg.y + pix * sg.channels;
+          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;
+          const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
+#define AIG_EPI(ACT)                                                                                                          \
+  if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
+  else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid)
+          switch (sg.act) {
+            case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
+            case AIG_ACT_SWISH: AIG_EPI(AIG_ACT_SWISH); break;
+            case AIG_ACT_LEAKY: AIG_EPI(AIG_ACT_LEAKY); break;
+            default: AIG_EPI(AIG_ACT_NONE); break;
+          }
+#undef AIG_EPI
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 6] = clock64();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      }
+    }
+  }
+
+  if (*s_abort) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -452,6 +822,14 @@ struct aig_conv_plan {
   CUtensorMap tmapA{}, tmapB{};
   const void* tmapA_ptr = nullptr;
   int grid = 1;
+  // patch-resident path (stride-1 2-D convolutions and fused down-sampling blocks)
+  bool use_pconv = false;
+  PconvParams pp{};
+  CUtensorMap tmapP{}, tmapBp{};
+  const void* tmapP_ptr = nullptr;
+  int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
+  bool pc_wres = false;
+  int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
 };
 
 namespace {
@@ -611,6 +989,170 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
   return AIG_OK;
 }
 
+
+// ---- patch-resident path: host side ------------------------------------------------------
+constexpr int kPconvTail = 2048 /*scale,shift*/ + 1024 /*barriers*/;
+constexpr int kPconvBudget = 227 * 1024 - 1024 /*align*/ - kPconvTail;
+
+template <int NT, int MS, bool WRES>
+int launch_pconv(aig_conv_plan* pl) {
+  static bool attr_set[64] = {};
+  aig_ctx* ctx = pl->ctx;
+  if (!attr_set[ctx->device & 63]) {
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(pconv_kernel<NT, MS, WRES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set[ctx->device & 63] = true;
+  }
+  pconv_kernel<NT, MS, WRES><<<pl->pc_grid, kNumThreads, pl->pc_smem, ctx->stream>>>(pl->tmapP, pl->tmapBp, pl->pp);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+template <int NT, int MS>
+int dispatch_pconv_w(aig_conv_plan* pl) {
+  return pl->pc_wres ? launch_pconv<NT, MS, true>(pl) : launch_pconv<NT, MS, false>(pl);
+}
+
+int dispatch_pconv(aig_conv_plan* pl) {
+  switch (pl->pc_NT * 10 + pl->pc_MS) {
+    case 641: return dispatch_pconv_w<64, 1>(pl);
+    case 642: return dispatch_pconv_w<64, 2>(pl);
+    case 644: return dispatch_pconv_w<64, 4>(pl);
+    case 1281: return dispatch_pconv_w<128, 1>(pl);
+    case 1282: return dispatch_pconv_w<128, 2>(pl);
+    case 1284: return dispatch_pconv_w<128, 4>(pl);
+    case 2561: return dispatch_pconv_w<256, 1>(pl);
+    case 2562: return dispatch_pconv_w<256, 2>(pl);
+  }
+  return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "pconv: unsupported tile NT=%d MS=%d", pl->pc_NT, pl->pc_MS);
+}
+
+// Chooses the tile (sub-tiles per CTA tile, resident or streamed weights) that moves the fewest
+// bytes per output position from L2 and fits shared memory.  Geometry (P, RP, pad, kw, taps, cblocks,
+// Ho, Wo, batch, n_tiles) must be filled in already.  Returns false when nothing fits.
+bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, int NT, int kh, int sparse_extra_kb) {
+  PconvParams& q = pl->pp;
+  const int wblock = NT * 128;
+  const int dense_kb = q.taps * q.cblocks;
+  const long long total_q = (long long)q.batch * q.RP * q.P;
+  double best = -1;
+  int best_ms = 0, best_bufs = 2, best_stages = 0;
+  bool best_res = false;
+  for (int ms = 4; ms >= 1; ms /= 2) {
+    if (ms * NT > 512) continue;
+    const int bufs = 2 * ms * NT <= 512 ? 2 : 1;
+    const int M = ms * kTileM;
+    const int vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
+    const int region = ((vrows * q.P * 128) + 1023) / 1024 * 1024;
+    const long long patch = (long long)region * q.cblocks;
+    const long long m_tiles = ceil_div_ll(total_q, M);
+    if (ms > 1 && m_tiles < ctx->sm_count) continue;  // keep every SM busy before growing the tile
+    const double wbytes = (double)(dense_kb * q.n_tiles + sparse_extra_kb) * wblock;
+    // resident weights (single N tile only)
+    if (q.n_tiles == 1 && 2 * patch + (long long)dense_kb * wblock <= kPconvBudget) {
+      const double cost = (double)patch / M;
+      if (best < 0 || cost < best) { best = cost; best_ms = ms; best_bufs = bufs; best_res = true; best_stages = dense_kb; }
+    }
+    long long stages = (kPconvBudget - 2 * patch) / wblock;
+    if (stages > 32) stages = 32;
+    if (stages >= 3) {
+      const double cost = ((double)patch + wbytes) / M * (bufs == 1 ? 1.1 : 1.0);  // single-buffered accumulators stall the MMAs during the epilogue
+      if (best < 0 || cost < best) { best = cost; best_ms = ms; best_bufs = bufs; best_res = false; best_stages = (int)stages; }
+    }
+  }
+  if (best < 0) return false;
+  const int M = best_ms * kTileM;
+  q.patch_vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
+  q.region_bytes = ((q.patch_vrows * q.P * 128) + 1023) / 1024 * 1024;
+  q.patch_bytes = q.region_bytes * q.cblocks;
+  q.w_stages = best_stages;
+  q.acc_bufs = best_bufs;
+  q.m_tiles = (int)ceil_div_ll(total_q, M);
+  pl->pc_NT = NT;
+  pl->pc_MS = best_ms;
+  pl->pc_wres = best_res;
+  pl->pc_smem = 1024 + 2 * q.patch_bytes + q.w_stages * wblock + kPconvTail;
+  pl->pc_grid = q.m_tiles < ctx->sm_count ? q.m_tiles : ctx->sm_count;
+  return true;
+}
+
+int encode_Bp(aig_conv_plan* pl) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {(cuuint64_t)pl->Ktot, (cuuint64_t)pl->Kpad};
+  cuuint64_t strides[1] = {(cuuint64_t)pl->Ktot * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)pl->pc_NT};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&pl->tmapBp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pl->w_packed, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(Bp) failed: %d", (int)r);
+  return AIG_OK;
+}
+
+int encode_P(aig_conv_plan* pl, const void* x) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t C = pl->pc_in_c, W = pl->pc_in_w, H = pl->pc_in_h, N = pl->d.batch;
+  cuuint64_t dims[5] = {C, W, H, 1, N};
+  cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, H * W * C * 2};
+  cuuint32_t box[5] = {64u, (cuuint32_t)pl->pp.P, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(&pl->tmapP, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(P) failed: %d", (int)r);
+  pl->tmapP_ptr = x;
+  return AIG_OK;
+}
+
+// Stride-1 2-D convolutions with in_c % 64 == 0 take the patch-resident kernel when a tile fits.
+int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
+  const aig_conv_desc& d = pl->d;
+  const char* off = getenv("AIG_PCONV_OFF");
+  if (off && atoi(off)) return AIG_OK;
+  if (pl->is_fc || d.kd != 1 || d.in_d != 1 || d.sd != 1 || d.sh != 1 || d.sw != 1 || d.ph != d.pw || d.pd != 0) return AIG_OK;
+  if (d.kh * d.kw < 2) return AIG_OK;  // 1x1: nothing to reuse, the streamed kernel is the same traffic
+  if (d.in_c % 64 != 0 || d.out_c % 8 != 0 || d.out_c <= 32 || d.two_step) return AIG_OK;
+  if (d.in_w + d.ph > 256 || d.kh - 1 > 2 * d.ph + d.in_h - 1) return AIG_OK;
+  PconvParams& q = pl->pp;
+  q = PconvParams{};
+  q.P = d.in_w + d.pw;
+  q.RP = d.in_h + d.ph;
+  q.pad = d.ph;
+  q.kw = d.kw;
+  q.taps = d.kh * d.kw;
+  q.cblocks = d.in_c / 64;
+  q.Ho = pl->Ho;
+  q.Wo = pl->Wo;
+  q.batch = d.batch;
+  const int NT = d.out_c <= 64 ? 64 : (d.out_c <= 128 ? 128 : 256);
+  q.n_tiles = pl->Kpad / NT;
+  q.n_split = 1 << 30;
+  q.sparse_tile0 = 1 << 30;
+  q.sub_cblocks = 1;
+  q.slope = d.slope;
+  q.scale = pl->scale;
+  q.shift = pl->shift;
+  q.gerr = ctx->d_err;
+  q.seg[0].channels = d.out_c;
+  q.seg[0].c0 = 0;
+  q.seg[0].act = d.act;
+  q.seg[0].s2d = 0;
+  q.seg[1] = q.seg[0];
+  if (!pconv_choose_tile(ctx, pl, NT, d.kh, 0)) return AIG_OK;
+  pl->pc_in_h = d.in_h;
+  pl->pc_in_w = d.in_w;
+  pl->pc_in_c = d.in_c;
+  const int rc = encode_Bp(pl);
+  if (rc != AIG_OK) return rc;
+  const char* ts = getenv("AIG_PCONV_TS");
+  if (ts && atoi(ts)) {
+    AIG_CUDA_OK(ctx, cudaMalloc(&q.ts, 128 * sizeof(long long)));
+    AIG_CUDA_OK(ctx, cudaMemset(q.ts, 0, 128 * sizeof(long long)));
+  }
+  pl->use_pconv = true;
+  return AIG_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -631,7 +1173,8 @@ int aig_conv_plan_create(aig_ctx* ctx, const aig_conv_desc* desc, aig_conv_plan*
   pl->Do = (d.in_d + 2 * d.pd - d.kd) / d.sd + 1;
   pl->Ho = (d.in_h + 2 * d.ph - d.kh) / d.sh + 1;
   pl->Wo = (d.in_w + 2 * d.pw - d.kw) / d.sw + 1;
-  const int rc = plan_finish(ctx, pl);
+  int rc = plan_finish(ctx, pl);
+  if (rc == AIG_OK) rc = pconv_try_plain(ctx, pl);
   if (rc != AIG_OK) {
     aig_conv_plan_destroy(pl);
     return rc;
@@ -648,6 +1191,16 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   cudaFree(pl->scale);
   cudaFree(pl->shift);
   delete pl;
+  return AIG_OK;
+}
+
+// Profiling aid (not part of the public interface): copies the timeline recorded by CTA 0 of the last
+// patch-resident launch (8 clock64 stamps per tile, 16 tiles) and the tile shape into out[0..131].
+int aig_conv_plan_debug_timeline(aig_conv_plan* pl, long long* out) {
+  if (!pl || !out || !pl->use_pconv || !pl->pp.ts) return AIG_ERR_INVALID;
+  cudaStreamSynchronize(pl->ctx->stream);
+  cudaMemcpy(out, pl->pp.ts, 128 * sizeof(long long), cudaMemcpyDeviceToHost);
+  out[128] = pl->pc_NT; out[129] = pl->pc_MS; out[130] = pl->pc_wres ? -1 : pl->pp.w_stages; out[131] = pl->pp.m_tiles;
   return AIG_OK;
 }
 
@@ -682,6 +1235,15 @@ int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* resid
   AIG_REQUIRE(ctx, pl->weights_set, "conv forward: weights not set");
   AIG_REQUIRE(ctx, ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)residual & 15) == 0,
               "conv forward: tensors must be 16-byte aligned");
+  if (pl->use_pconv && !pl->out_f32) {
+    if (pl->tmapP_ptr != x) {
+      const int rc = encode_P(pl, x);
+      if (rc != AIG_OK) return rc;
+    }
+    pl->pp.seg[0].y = (__half*)y;
+    pl->pp.seg[0].residual = (const __half*)residual;
+    return dispatch_pconv(pl);
+  }
   if (pl->tmapA_ptr != x) {
     const int rc = encode_A(pl, x);
     if (rc != AIG_OK) return rc;
