@@ -89,6 +89,14 @@ SIGNATURES = {
     "aig_conv0_plan_set_weights": [P, P, P, P, P, P, P, c_float],
     "aig_conv0_forward_bgra": [P, P, P],
     "aig_conv0_forward_nchw": [P, P, P],
+    "aig_s2d_elems": [c_int, c_int, c_int, c_int],
+    "aig_nhwc_to_s2d": [P, P, P, c_int, c_int, c_int, c_int],
+    "aig_s2d_to_nhwc": [P, P, P, c_int, c_int, c_int, c_int],
+    "aig_conv_plan_set_output_s2d": [P, c_int],
+    "aig_conv0_plan_set_output_s2d": [P, c_int],
+    "aig_resdown_plan_create": [P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, PP],
+    "aig_resdown_plan_set_weights": [P, P, P, P, P, P, P, c_float, P, P],
+    "aig_resdown_forward": [P, P, P, P],
     "aig_actions_from_outputs": [P, P, c_int, c_int, c_int],
 }
 AIG_CNN_MAX_BLOCKS = 7
@@ -176,7 +184,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
@@ -318,6 +326,25 @@ class ConvPlan(_Plan):
     def forward(self, x, y, residual=None):
         self.check(lib().aig_conv_forward(self.handle, ptr(x), ptr(residual), ptr(y)))
         return y
+
+
+class ResDownPlan(_Plan):
+    """aig_resdown_plan: main k4 s2 p1 conv (+BN+act) and k2 s2 p0 shortcut of a residual block as one launch
+    over the space-to-depth view of the input."""
+    _destroy = "aig_conv_plan_destroy"
+    _dims = "aig_conv_plan_out_dims"
+
+    def __init__(self, ctx, batch, in_c, in_h, in_w, out_c, act=ACT_NONE, slope=0.01):
+        super().__init__(ctx)
+        self.check(lib().aig_resdown_plan_create(ctx.handle, batch, in_c, in_h, in_w, out_c, act, slope, ctypes.byref(self.handle)))
+
+    def set_weights(self, w_main, b_main, bn, w_short, b_short, eps=1e-6):
+        g, b, m, v = bn if bn is not None else (None, None, None, None)
+        self.check(lib().aig_resdown_plan_set_weights(self.handle, ptr(w_main), ptr(b_main), ptr(g), ptr(b), ptr(m), ptr(v), eps,
+                                                      ptr(w_short), ptr(b_short)))
+
+    def forward(self, x_s2d, y_main, y_short):
+        self.check(lib().aig_resdown_forward(self.handle, ptr(x_s2d), ptr(y_main), ptr(y_short)))
 
 
 class FcPlan(_Plan):

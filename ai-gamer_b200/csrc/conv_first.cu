@@ -271,6 +271,16 @@ int aig_conv0_plan_set_weights(aig_conv0_plan* pl, const aig_half* w, const aig_
   return AIG_OK;
 }
 
+int aig_conv0_plan_set_output_s2d(aig_conv0_plan* pl, int enable) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  AIG_REQUIRE(ctx, !enable || (pl->tc && pl->p.D == 1 && pl->p.kd == 1), "conv0: space-to-depth output needs the 2-D tensor-core path");
+  if (!pl->tc) return AIG_OK;
+  // block extents of a following k4 s2 p1 / k2 s2 p0 pair: one more block than its output extent
+  const int Hb = (pl->p.Ho - 2) / 2 + 2, Wb = (pl->p.Wo - 2) / 2 + 2;
+  return conv_first_tc_set_s2d(pl->tc, enable, Hb, Wb);
+}
+
 int aig_conv0_forward_bgra(aig_conv0_plan* pl, const uint8_t* bgra, aig_half* y) {
   if (!pl) return AIG_ERR_INVALID;
   aig_ctx* ctx = pl->ctx;

@@ -25,6 +25,7 @@ struct TcParams {
   const float* scale;
   const float* shift;
   int* gerr;
+  int s2d, Hb, Wb;  // s2d: store into the 2x2 space-to-depth layout [n][Hb][Wb][4][K] read by a fused down-sampling block
 };
 
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
@@ -173,6 +174,13 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
       const long long px = (long long)tile * kRows + r;
       const bool valid = px < p.total_px;
       __half* yrow = y + (size_t)px * g.K;
+      if (p.s2d && valid) {
+        const int ow = (int)(px % g.Wo);
+        const long long t = px / g.Wo;
+        const int oh = (int)(t % g.Ho), n = (int)(t / g.Ho);
+        const int by = (oh + 1) >> 1, bx = (ow + 1) >> 1, sp = ((oh + 1) & 1) * 2 + ((ow + 1) & 1);
+        yrow = y + ((((size_t)n * p.Hb + by) * p.Wb + bx) * 4 + sp) * g.K;
+      }
       if (!mbar_wait_bounded(bar_tfull + 8 * st, ph, s_abort, p.gerr, 604)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t)(st * p.NT) + ((uint32_t)(q * 32) << 16);
@@ -305,6 +313,14 @@ int conv_first_tc_set_weights(ConvFirstTc* t, const __half* w) {
   const int taps = t->prm.g.kd * t->prm.g.k * t->prm.g.k;
   pack_wimg_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg, t->prm.g.K, t->prm.NT, taps);
   AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int conv_first_tc_set_s2d(ConvFirstTc* t, int enable, int Hb, int Wb) {
+  if (enable && t->prm.g.Do != 1) return aig_fail(t->ctx, AIG_ERR_UNSUPPORTED, "conv0: space-to-depth output is for 2-D layers");
+  t->prm.s2d = enable ? 1 : 0;
+  t->prm.Hb = Hb;
+  t->prm.Wb = Wb;
   return AIG_OK;
 }
 

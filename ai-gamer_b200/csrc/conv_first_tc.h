@@ -21,3 +21,5 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
 void conv_first_tc_destroy(ConvFirstTc* t);
 int conv_first_tc_set_weights(ConvFirstTc* t, const __half* w_kcx);
 int conv_first_tc_forward(ConvFirstTc* t, const void* x, bool bgra, __half* y);
+// Output layout switch: [n][Hb][Wb][4][K] blocks of 2x2 pixels (block (y+1)>>1, (x+1)>>1; sub-position ((y+1)&1)*2+((x+1)&1)).
+int conv_first_tc_set_s2d(ConvFirstTc* t, int enable, int Hb, int Wb);

@@ -479,6 +479,7 @@ struct PconvParams {
   int patch_vrows, region_bytes, patch_bytes;
   int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
   int acc_bufs;            // TMEM accumulator buffers: 2, or 1 when MS*NT fills all 512 columns
+  int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
   int n_split;             // GEMM columns >= n_split go to seg[1]
   int sparse_tile0;        // N tiles >= this one use the sparse shortcut K schedule (INT_MAX: none)
   int sub_cblocks;         // 64-channel blocks per space-to-depth sub-position (sparse schedule)
@@ -520,8 +521,11 @@ struct PconvKIter {
   }
 };
 
+constexpr int kPconvThreads = 352;  // patch producer, MMA issuer, 8 epilogue warps, weight producer
+constexpr int kWeightWarp = 10;
+
 template <int NT, int MS, bool WRES>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kPconvThreads, 1)
 pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const PconvParams p) {
   constexpr int kM = MS * kTileM;
   constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
@@ -530,8 +534,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw);
   const uint32_t sPatch = base;
-  const uint32_t sW = base + 2 * p.patch_bytes;
-  const uint32_t tail = 2 * p.patch_bytes + p.w_stages * kWBlock;
+  const uint32_t sW = base + p.patch_bufs * p.patch_bytes;
+  const uint32_t tail = p.patch_bufs * p.patch_bytes + p.w_stages * kWBlock;
   float* s_scale = reinterpret_cast<float*>(sm + tail);
   float* s_shift = s_scale + 256;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 2048);
@@ -546,7 +550,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (p.n_tiles == 1) {
-    for (int i = threadIdx.x; i < NT; i += kNumThreads) {
+    for (int i = threadIdx.x; i < NT; i += kPconvThreads) {
       s_scale[i] = p.scale[i];
       s_shift[i] = p.shift[i];
     }
@@ -580,39 +584,38 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   const int dense_kb = p.taps * p.cblocks, sparse_kb = p.taps * p.sub_cblocks;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ patch producer
     if (lane == 0) {
-      bool ok = true;
-      if (WRES) {
-        mbar_expect_tx(bar_wfull, (uint32_t)(dense_kb * kWBlock));
-        for (int kb = 0; kb < dense_kb; ++kb) tma_load_2d(sW + kb * kWBlock, &tmapB, bar_wfull, kb * 64, 0);
-      }
-      auto load_patch = [&](int m_tile, int it) -> bool {
-        const int buf = it & 1;
-        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
-        if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) return false;
+      int it = 0;
+      for (int m_tile = blockIdx.x; m_tile < p.m_tiles; m_tile += gridDim.x, ++it) {
+        const int buf = p.patch_bufs == 2 ? (it & 1) : 0;
+        const uint32_t ph = (uint32_t)(p.patch_bufs == 2 ? (it >> 1) : it) & 1u;
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
+        if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) break;
         mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.cblocks));
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
         const uint32_t dst0 = sPatch + buf * p.patch_bytes;
+        int n = vr0 / p.RP, yy = vr0 - n * p.RP;
         for (int r = 0; r < p.patch_vrows; ++r) {
-          const int vr = vr0 + r;
-          const int n = vr / p.RP, yy = vr - n * p.RP;
           for (int cb = 0; cb < p.cblocks; ++cb)
             tma_load_5d(dst0 + cb * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, cb * 64, -p.pad, yy - p.pad, 0, n);
+          if (++yy == p.RP) { yy = 0; ++n; }
         }
-        return true;
-      };
-      int it = 0;
-      int stage = 0;
-      uint32_t wphase = 0;
-      if ((int)blockIdx.x < p.m_tiles) ok = load_patch(blockIdx.x, 0);
-      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
-        const int next = m_tile + gridDim.x;
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
-        if (next < p.m_tiles) ok = load_patch(next, it + 1);  // under this tile's MMAs
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
-        if (!WRES) {
+      }
+    }
+  } else if (warp == kWeightWarp) {
+    // ------------------------------------------------------------------ weight producer
+    if (lane == 0) {
+      if (WRES) {
+        mbar_expect_tx(bar_wfull, (uint32_t)(dense_kb * kWBlock));
+        for (int kb = 0; kb < dense_kb; ++kb) tma_load_2d(sW + kb * kWBlock, &tmapB, bar_wfull, kb * 64, 0);
+      } else {
+        bool ok = true;
+        int stage = 0, it = 0;
+        uint32_t wphase = 0;
+        for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
           for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile) {
             const bool sparse = n_tile >= p.sparse_tile0;
             const int nkb = sparse ? sparse_kb : dense_kb;
@@ -625,8 +628,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
           }
+          if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 2] = clock64();
         }
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 2] = clock64();
       }
     }
   } else if (warp == 1) {
@@ -638,8 +641,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       int it = 0, cnt = 0, stage = 0;
       uint32_t wphase = 0;
       for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(it >> 1) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
+        const int buf = p.patch_bufs == 2 ? (it & 1) : 0;
+        if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(p.patch_bufs == 2 ? (it >> 1) : it) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 3] = clock64();
         const long long q0 = (long long)m_tile * kM;
         const int off0 = (int)(q0 - (q0 / p.P) * p.P);
@@ -683,7 +686,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 4] = clock64();
       }
     }
-  } else {
+  } else if (warp < kWeightWarp) {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int q4 = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -708,15 +711,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
           const int n = vr / p.RP, yy = vr - n * p.RP;
           const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
-          size_t pix;
+          const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
+          size_t opix = pix;
           if (sg.s2d) {
             const int by = (yy + 1) >> 1, bx = (vc + 1) >> 1, sp = ((yy + 1) & 1) * 2 + ((vc + 1) & 1);
-            pix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
-          } else {
-            pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
+            opix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
           }
-          __half* yrow = sg.y + pix * sg.channels;
-          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;
+          __half* yrow = sg.y + opix * sg.channels;
+          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
   if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
@@ -790,6 +792,46 @@ __global__ void add_bias_kernel(float* shift, const __half* bias2, int K) {
   if (k < K) shift[k] += __half2float(bias2[k]);
 }
 
+
+// Fused down-sampling weights.  With the input in 2x2 space-to-depth blocks (block (y+1)>>1, (x+1)>>1,
+// sub-position ((y+1)&1, (x+1)&1), channel index sub*C + c), the k4 s2 p1 convolution is a 2x2 stride-1
+// convolution over blocks: filter position (fy, fx) = (2*ty + dy, 2*tx + dx).  The k2 s2 p0 shortcut
+// reads, for block tap (ty, tx), only sub-position (1-ty, 1-tx) with filter position (ty, tx).
+// packed [2K][tap(4)][4C]: rows < K main, rows >= K shortcut.
+__global__ void repack_down_kernel(const __half* __restrict__ w_main, const __half* __restrict__ w_short,
+                                   __half* __restrict__ packed, int K, int C) {
+  const long long total = 2LL * K * 16 * C;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int col = (int)(i % (16 * C)), r = (int)(i / (16 * C));
+    const int tap = col / (4 * C), rem = col - tap * 4 * C;
+    const int sp = rem / C, c = rem - sp * C;
+    const int ty = tap >> 1, tx = tap & 1, dy = sp >> 1, dx = sp & 1;
+    __half v = __ushort_as_half((unsigned short)0);
+    if (r < K) {
+      v = w_main[(((size_t)r * C + c) * 4 + (2 * ty + dy)) * 4 + (2 * tx + dx)];
+    } else if (dy == 1 - ty && dx == 1 - tx) {
+      v = w_short[(((size_t)(r - K) * C + c) * 2 + ty) * 2 + tx];
+    }
+    packed[i] = v;
+  }
+}
+
+// channels-last [n][h][w][c] <-> space-to-depth blocks [n][hb][wb][4][c]; 8 channels per thread
+__global__ void s2d_convert_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int batch, int h, int w, int c8,
+                                   int hb, int wb, int to_s2d) {
+  const long long total = (long long)batch * h * w * c8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int cc = (int)(i % c8);
+    long long t = i / c8;
+    const int x = (int)(t % w);
+    t /= w;
+    const int y = (int)(t % h), n = (int)(t / h);
+    const size_t blk = ((((size_t)n * hb + ((y + 1) >> 1)) * wb + ((x + 1) >> 1)) * 4 + ((y + 1) & 1) * 2 + ((x + 1) & 1)) * c8 + cc;
+    if (to_s2d) dst[blk] = src[i];
+    else dst[i] = src[blk];
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -830,6 +872,7 @@ struct aig_conv_plan {
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
   bool pc_wres = false;
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
+  bool is_down = false;                        // fused down-sampling pair (main k4 s2 p1 + shortcut k2 s2 p0)
 };
 
 namespace {
@@ -1002,7 +1045,7 @@ int launch_pconv(aig_conv_plan* pl) {
     AIG_CUDA_OK(ctx, cudaFuncSetAttribute(pconv_kernel<NT, MS, WRES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[ctx->device & 63] = true;
   }
-  pconv_kernel<NT, MS, WRES><<<pl->pc_grid, kNumThreads, pl->pc_smem, ctx->stream>>>(pl->tmapP, pl->tmapBp, pl->pp);
+  pconv_kernel<NT, MS, WRES><<<pl->pc_grid, kPconvThreads, pl->pc_smem, ctx->stream>>>(pl->tmapP, pl->tmapBp, pl->pp);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }
@@ -1026,51 +1069,64 @@ int dispatch_pconv(aig_conv_plan* pl) {
   return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "pconv: unsupported tile NT=%d MS=%d", pl->pc_NT, pl->pc_MS);
 }
 
-// Chooses the tile (sub-tiles per CTA tile, resident or streamed weights) that moves the fewest
-// bytes per output position from L2 and fits shared memory.  Geometry (P, RP, pad, kw, taps, cblocks,
-// Ho, Wo, batch, n_tiles) must be filled in already.  Returns false when nothing fits.
-bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, int NT, int kh, int sparse_extra_kb) {
+// One way of tiling N: tile width, number of N tiles, weight blocks (NT x 64 channels) streamed per
+// M tile over all N tiles, and the first N tile that uses the sparse shortcut schedule.
+struct PconvNtOption {
+  int NT, n_tiles, w_kblocks, sparse_tile0;
+};
+
+// Chooses, among the N tilings offered, the tile (sub-tiles per CTA tile, resident or streamed weights,
+// one or two patch buffers) that moves the fewest bytes per output position from L2 and fits shared
+// memory and TMEM.  Geometry (P, RP, pad, kw, taps, cblocks, Ho, Wo, batch) must be filled in already.
+// Returns false when nothing fits.
+bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opts, int n_opts, int kh) {
   PconvParams& q = pl->pp;
-  const int wblock = NT * 128;
-  const int dense_kb = q.taps * q.cblocks;
   const long long total_q = (long long)q.batch * q.RP * q.P;
   double best = -1;
-  int best_ms = 0, best_bufs = 2, best_stages = 0;
+  int best_ms = 0, best_acc = 2, best_pb = 2, best_stages = 0, best_opt = 0;
   bool best_res = false;
-  for (int ms = 4; ms >= 1; ms /= 2) {
-    if (ms * NT > 512) continue;
-    const int bufs = 2 * ms * NT <= 512 ? 2 : 1;
-    const int M = ms * kTileM;
-    const int vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
-    const int region = ((vrows * q.P * 128) + 1023) / 1024 * 1024;
-    const long long patch = (long long)region * q.cblocks;
-    const long long m_tiles = ceil_div_ll(total_q, M);
-    if (ms > 1 && m_tiles < ctx->sm_count) continue;  // keep every SM busy before growing the tile
-    const double wbytes = (double)(dense_kb * q.n_tiles + sparse_extra_kb) * wblock;
-    // resident weights (single N tile only)
-    if (q.n_tiles == 1 && 2 * patch + (long long)dense_kb * wblock <= kPconvBudget) {
-      const double cost = (double)patch / M;
-      if (best < 0 || cost < best) { best = cost; best_ms = ms; best_bufs = bufs; best_res = true; best_stages = dense_kb; }
-    }
-    long long stages = (kPconvBudget - 2 * patch) / wblock;
-    if (stages > 32) stages = 32;
-    if (stages >= 3) {
-      const double cost = ((double)patch + wbytes) / M * (bufs == 1 ? 1.1 : 1.0);  // single-buffered accumulators stall the MMAs during the epilogue
-      if (best < 0 || cost < best) { best = cost; best_ms = ms; best_bufs = bufs; best_res = false; best_stages = (int)stages; }
+  for (int o = 0; o < n_opts; ++o) {
+    const int NT = opts[o].NT, wblock = NT * 128;
+    const int dense_kb = q.taps * q.cblocks;
+    for (int ms = 4; ms >= 1; ms /= 2) {
+      if (ms * NT > 512) continue;
+      const int acc = 2 * ms * NT <= 512 ? 2 : 1;
+      const int M = ms * kTileM;
+      const int vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
+      const long long patch = (long long)vrows * q.P * 128 * q.cblocks;
+      const long long m_tiles = ceil_div_ll(total_q, M);
+      if (ms > 1 && m_tiles < ctx->sm_count) continue;  // keep every SM busy before growing the tile
+      for (int pb = 2; pb >= 1; --pb) {
+        const double pen = (acc == 1 ? 1.15 : 1.0) * (pb == 1 ? 1.1 : 1.0);  // what the lost overlap costs, roughly
+        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget) {
+          const double cost = (double)patch / M * pen;
+          if (best < 0 || cost < best) { best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = true; best_stages = dense_kb; best_opt = o; }
+        }
+        long long stages = (kPconvBudget - pb * patch) / wblock;
+        if (stages > 32) stages = 32;
+        if (stages >= 2) {
+          const double cost = ((double)patch + (double)opts[o].w_kblocks * wblock) / M * pen * (stages == 2 ? 1.1 : 1.0);
+          if (best < 0 || cost < best) { best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = false; best_stages = (int)stages; best_opt = o; }
+        }
+      }
     }
   }
   if (best < 0) return false;
+  const int NT = opts[best_opt].NT;
   const int M = best_ms * kTileM;
+  q.n_tiles = opts[best_opt].n_tiles;
+  q.sparse_tile0 = opts[best_opt].sparse_tile0;
   q.patch_vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
-  q.region_bytes = ((q.patch_vrows * q.P * 128) + 1023) / 1024 * 1024;
+  q.region_bytes = q.patch_vrows * q.P * 128;
   q.patch_bytes = q.region_bytes * q.cblocks;
+  q.patch_bufs = best_pb;
   q.w_stages = best_stages;
-  q.acc_bufs = best_bufs;
+  q.acc_bufs = best_acc;
   q.m_tiles = (int)ceil_div_ll(total_q, M);
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
-  pl->pc_smem = 1024 + 2 * q.patch_bytes + q.w_stages * wblock + kPconvTail;
+  pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + kPconvTail;
   pl->pc_grid = q.m_tiles < ctx->sm_count ? q.m_tiles : ctx->sm_count;
   return true;
 }
@@ -1125,10 +1181,7 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.Ho = pl->Ho;
   q.Wo = pl->Wo;
   q.batch = d.batch;
-  const int NT = d.out_c <= 64 ? 64 : (d.out_c <= 128 ? 128 : 256);
-  q.n_tiles = pl->Kpad / NT;
   q.n_split = 1 << 30;
-  q.sparse_tile0 = 1 << 30;
   q.sub_cblocks = 1;
   q.slope = d.slope;
   q.scale = pl->scale;
@@ -1139,7 +1192,15 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.seg[0].act = d.act;
   q.seg[0].s2d = 0;
   q.seg[1] = q.seg[0];
-  if (!pconv_choose_tile(ctx, pl, NT, d.kh, 0)) return AIG_OK;
+  // N tilings: the natural tile width, and for wide layers also half of it (more sub-tiles per CTA tile
+  // then share every weight block); Kpad is a multiple of both
+  PconvNtOption opts[2];
+  int n_opts = 0;
+  const int NT0 = d.out_c <= 64 ? 64 : (d.out_c <= 128 ? 128 : 256);
+  const int dense = q.taps * q.cblocks;
+  opts[n_opts++] = PconvNtOption{NT0, pl->Kpad / NT0, dense * (pl->Kpad / NT0), 1 << 30};
+  if (NT0 == 256) opts[n_opts++] = PconvNtOption{128, pl->Kpad / 128, dense * (pl->Kpad / 128), 1 << 30};
+  if (!pconv_choose_tile(ctx, pl, opts, n_opts, d.kh)) return AIG_OK;
   pl->pc_in_h = d.in_h;
   pl->pc_in_w = d.in_w;
   pl->pc_in_c = d.in_c;
@@ -1190,6 +1251,7 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   cudaFree(pl->w_packed);
   cudaFree(pl->scale);
   cudaFree(pl->shift);
+  cudaFree(pl->pp.ts);
   delete pl;
   return AIG_OK;
 }
@@ -1232,6 +1294,7 @@ int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* resid
   aig_ctx* ctx = pl->ctx;
   DeviceGuard g(ctx->device);
   AIG_REQUIRE(ctx, x && y, "conv forward: null pointer");
+  AIG_REQUIRE(ctx, !pl->is_down, "conv forward: fused down-sampling plans run through aig_resdown_forward");
   AIG_REQUIRE(ctx, pl->weights_set, "conv forward: weights not set");
   AIG_REQUIRE(ctx, ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)residual & 15) == 0,
               "conv forward: tensors must be 16-byte aligned");
@@ -1316,6 +1379,148 @@ int aig_fc_plan_set_weights_out_in(aig_conv_plan* pl, const aig_half* w_out_in, 
   AIG_CUDA_OK(ctx, cudaMemcpyAsync(pl->w_packed, w_out_in, (size_t)pl->d.out_c * pl->d.in_c * sizeof(__half),
                                    cudaMemcpyDeviceToDevice, ctx->stream));
   return set_affine(pl, bias, nullptr, nullptr, nullptr, nullptr, 0.f);
+}
+
+// ---- fused down-sampling pair and space-to-depth plumbing ---------------------------------
+static inline int s2d_extent(int v) { return (v - 2) / 2 + 2; }  // blocks along an axis of v pixels
+
+size_t aig_s2d_elems(int batch, int h, int w, int c) { return (size_t)batch * s2d_extent(h) * s2d_extent(w) * 4 * c; }
+
+int aig_nhwc_to_s2d(aig_ctx* ctx, const aig_half* x, aig_half* s2d, int batch, int h, int w, int c) {
+  if (!ctx) return AIG_ERR_INVALID;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, x && s2d && c % 8 == 0 && h >= 2 && w >= 2, "nhwc_to_s2d: bad arguments");
+  const long long total = (long long)batch * h * w * (c / 8);
+  long long blocks = ceil_div_ll(total, 256);
+  if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  s2d_convert_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const uint4*)x, (uint4*)s2d, batch, h, w, c / 8, s2d_extent(h), s2d_extent(w), 1);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int aig_s2d_to_nhwc(aig_ctx* ctx, const aig_half* s2d, aig_half* y, int batch, int h, int w, int c) {
+  if (!ctx) return AIG_ERR_INVALID;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, y && s2d && c % 8 == 0 && h >= 2 && w >= 2, "s2d_to_nhwc: bad arguments");
+  const long long total = (long long)batch * h * w * (c / 8);
+  long long blocks = ceil_div_ll(total, 256);
+  if (blocks > ctx->sm_count * 16) blocks = ctx->sm_count * 16;
+  s2d_convert_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const uint4*)s2d, (uint4*)y, batch, h, w, c / 8, s2d_extent(h), s2d_extent(w), 0);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int aig_conv_plan_set_output_s2d(aig_conv_plan* pl, int enable) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  if (enable && !(pl->use_pconv && !pl->is_down)) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "space-to-depth output needs the patch-resident convolution path");
+  if (!pl->use_pconv) return AIG_OK;
+  AIG_REQUIRE(ctx, !enable || (pl->Ho >= 2 && pl->Wo >= 2), "space-to-depth output: image too small");
+  pl->pp.seg[0].s2d = enable ? 1 : 0;
+  pl->pp.seg[0].Hb = s2d_extent(pl->Ho);
+  pl->pp.seg[0].Wb = s2d_extent(pl->Wo);
+  return AIG_OK;
+}
+
+int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_w, int out_c, int act, float slope, aig_conv_plan** out) {
+  if (!ctx || !out) return AIG_ERR_INVALID;
+  *out = nullptr;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, batch > 0 && in_c > 0 && in_h >= 2 && in_w >= 2 && out_c > 0, "resdown plan: bad extents");
+  if (in_c % 16 != 0 || out_c % 64 != 0)
+    return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: needs in_c %% 16 == 0 and out_c %% 64 == 0 (got %d -> %d)", in_c, out_c);
+  aig_conv_plan* pl = new aig_conv_plan();
+  pl->ctx = ctx;
+  pl->is_down = true;
+  aig_conv_desc& d = pl->d;
+  d.batch = batch; d.in_c = in_c; d.in_d = 1; d.in_h = in_h; d.in_w = in_w; d.out_c = out_c;
+  d.kd = 1; d.kh = d.kw = 4; d.sd = 1; d.sh = d.sw = 2; d.pd = 0; d.ph = d.pw = 1; d.act = act; d.slope = slope;
+  pl->Do = 1;
+  pl->Ho = (in_h + 2 - 4) / 2 + 1;
+  pl->Wo = (in_w + 2 - 4) / 2 + 1;
+  const int Hb = pl->Ho + 1, Wb = pl->Wo + 1, C4 = 4 * in_c, N2 = 2 * out_c;
+  pl->Kpad = N2;
+  pl->taps = 4;
+  pl->Ktot = 4 * C4;
+  auto bail = [&](int rc) {
+    aig_conv_plan_destroy(pl);
+    return rc;
+  };
+  if (Wb > 256) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: rows of more than 255 output pixels are not supported"));
+  if (cudaMalloc(&pl->w_packed, (size_t)N2 * pl->Ktot * sizeof(__half)) != cudaSuccess || cudaMalloc(&pl->scale, N2 * sizeof(float)) != cudaSuccess ||
+      cudaMalloc(&pl->shift, N2 * sizeof(float)) != cudaSuccess)
+    return bail(aig_fail(ctx, AIG_ERR_CUDA, "resdown plan: allocation failed"));
+  PconvParams& q = pl->pp;
+  q = PconvParams{};
+  q.P = Wb; q.RP = Hb; q.pad = 0; q.kw = 2; q.taps = 4; q.cblocks = C4 / 64;
+  q.Ho = pl->Ho; q.Wo = pl->Wo; q.batch = batch;
+  q.n_split = out_c;
+  q.sub_cblocks = in_c % 64 == 0 ? in_c / 64 : 1;
+  q.slope = slope;
+  q.scale = pl->scale; q.shift = pl->shift;
+  q.gerr = ctx->d_err;
+  q.seg[0].channels = out_c; q.seg[0].c0 = 0; q.seg[0].act = act;
+  q.seg[1].channels = out_c; q.seg[1].c0 = out_c; q.seg[1].act = AIG_ACT_NONE;
+  // N tilings: main and shortcut columns in one tile (shortcut rows dense, mostly zero), or tiles of
+  // their own, where the shortcut tiles walk only the channel blocks they read (needs in_c % 64 == 0)
+  PconvNtOption opts[2];
+  int n_opts = 0;
+  const int dense = q.taps * q.cblocks, sparse = q.taps * q.sub_cblocks;
+  for (int NT = 256; NT >= 128; NT /= 2) {
+    if (N2 % NT != 0 || out_c % (NT / 2) != 0) continue;
+    const int nt = N2 / NT;
+    if (nt > 1 && out_c % NT == 0 && in_c % 64 == 0) {
+      opts[n_opts++] = PconvNtOption{NT, nt, (out_c / NT) * dense + (out_c / NT) * sparse, out_c / NT};
+    } else {
+      opts[n_opts++] = PconvNtOption{NT, nt, nt * dense, 1 << 30};
+    }
+  }
+  if (n_opts == 0 || !pconv_choose_tile(ctx, pl, opts, n_opts, 2)) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: no tile fits shared memory"));
+  pl->pc_in_h = Hb; pl->pc_in_w = Wb; pl->pc_in_c = C4;
+  const int rc = encode_Bp(pl);
+  if (rc != AIG_OK) return bail(rc);
+  pl->use_pconv = true;
+  *out = pl;
+  return AIG_OK;
+}
+
+int aig_resdown_plan_set_weights(aig_conv_plan* pl, const aig_half* w_main, const aig_half* b_main, const float* bn_gamma,
+                                 const float* bn_beta, const float* bn_mean, const float* bn_var, float bn_eps,
+                                 const aig_half* w_short, const aig_half* b_short) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, pl->is_down && w_main && w_short, "resdown set_weights: bad arguments");
+  AIG_REQUIRE(ctx, !bn_gamma || (bn_beta && bn_mean && bn_var), "BatchNorm needs gamma, beta, mean and var");
+  const int K = pl->d.out_c, C = pl->d.in_c;
+  const long long total = 2LL * K * 16 * C;
+  long long blocks = ceil_div_ll(total, 256);
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  repack_down_kernel<<<(int)blocks, 256, 0, ctx->stream>>>((const __half*)w_main, (const __half*)w_short, pl->w_packed, K, C);
+  AIG_LAUNCH_OK(ctx);
+  fold_affine_kernel<<<ceil_div(K, 128), 128, 0, ctx->stream>>>(pl->scale, pl->shift, (const __half*)b_main, bn_gamma, bn_beta, bn_mean, bn_var, bn_eps, K, K);
+  AIG_LAUNCH_OK(ctx);
+  fold_affine_kernel<<<ceil_div(K, 128), 128, 0, ctx->stream>>>(pl->scale + K, pl->shift + K, (const __half*)b_short, nullptr, nullptr, nullptr, nullptr, 0.f, K, K);
+  AIG_LAUNCH_OK(ctx);
+  pl->weights_set = true;
+  return AIG_OK;
+}
+
+int aig_resdown_forward(aig_conv_plan* pl, const aig_half* x_s2d, aig_half* y_main, aig_half* y_short) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, pl->is_down && x_s2d && y_main && y_short && pl->weights_set, "resdown forward: bad arguments or weights not set");
+  AIG_REQUIRE(ctx, ((uintptr_t)x_s2d & 15) == 0 && ((uintptr_t)y_main & 15) == 0 && ((uintptr_t)y_short & 15) == 0, "resdown forward: tensors must be 16-byte aligned");
+  if (pl->tmapP_ptr != x_s2d) {
+    const int rc = encode_P(pl, x_s2d);
+    if (rc != AIG_OK) return rc;
+  }
+  pl->pp.seg[0].y = (__half*)y_main;
+  pl->pp.seg[0].residual = nullptr;
+  pl->pp.seg[1].y = (__half*)y_short;
+  pl->pp.seg[1].residual = nullptr;
+  return dispatch_pconv(pl);
 }
 
 }  // extern "C"

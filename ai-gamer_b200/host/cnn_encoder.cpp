@@ -18,6 +18,7 @@
 //   FC: half W[in][out], half b[out]                        (FCLayer.cpp:70-81)
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <fstream>
@@ -61,8 +62,13 @@ struct aig_cnn {
   aig_conv0_plan* conv0 = nullptr;
   struct Block {
     aig_conv_plan *c0 = nullptr, *c1 = nullptr, *sc = nullptr;
+    aig_conv_plan* down = nullptr;  // main k4 s2 + shortcut k2 s2 as one launch over the space-to-depth input (replaces c0 and sc)
     aig_half *t = nullptr, *r = nullptr, *y = nullptr;
+    bool y_s2d = false;             // y is written in the space-to-depth layout the next block's fused launch reads
   };
+  bool act0_s2d = false;
+  aig_half* stage_scratch = nullptr;  // channels-last copy of a space-to-depth stage, made on request
+  size_t stage_scratch_elems = 0;
   std::vector<Block> blocks;
   aig_conv_plan* fc = nullptr;
   aig_half *act0 = nullptr, *sa = nullptr, *feat = nullptr, *logits = nullptr;
@@ -195,7 +201,6 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
   rc = aig_conv0_plan_create(ctx, c.batch, c.height, c.width, c.widths[0], c.k0, 2, c.k0 / 2, c.act, c.slope, &m->conv0);
   if (rc != AIG_OK) return bail(rc);
   aig_conv0_plan_out_dims(m->conv0, nullptr, &m->H0, &m->W0);
-  if (dev_alloc(m, &m->act0, (size_t)c.batch * m->H0 * m->W0 * c.widths[0]) != AIG_OK) return bail(AIG_ERR_CUDA);
   int h = m->H0, w = m->W0;
   m->launches_per_forward = 1;
   {
@@ -203,6 +208,8 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
     m->sites.push_back({"conv0_bgra", 2.0 * px * c.widths[0] * 3 * c.k0 * c.k0,
                         (double)c.batch * c.height * c.width * 4 + px * c.widths[0] * 2});
   }
+  const char* no_fused = getenv("AIG_CNN_NO_FUSED_DOWN");
+  const bool allow_fused = !(no_fused && atoi(no_fused));
   for (int i = 0; i < c.n_blocks; ++i) {
     aig_cnn::Block b;
     const int ci = c.widths[i], co = c.widths[i + 1];
@@ -210,23 +217,40 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
     d.batch = c.batch; d.in_c = ci; d.in_d = 1; d.in_h = h; d.in_w = w; d.out_c = co;
     d.kd = 1; d.kh = d.kw = 4; d.sd = 1; d.sh = d.sw = 2; d.pd = 0; d.ph = d.pw = 1;
     d.act = c.act; d.slope = c.slope; d.two_step = 0;
-    if ((rc = aig_conv_plan_create(ctx, &d, &b.c0)) != AIG_OK) return bail(rc);
-    int oh, ow;
-    aig_conv_plan_out_dims(b.c0, nullptr, &oh, &ow);
-    aig_conv_desc s = d;
-    s.kh = s.kw = 2; s.ph = s.pw = 0; s.act = AIG_ACT_NONE;
-    if ((rc = aig_conv_plan_create(ctx, &s, &b.sc)) != AIG_OK) return bail(rc);
-    int sh_, sw_;
-    aig_conv_plan_out_dims(b.sc, nullptr, &sh_, &sw_);
-    if (sh_ != oh || sw_ != ow) {
-      aig_cnn_destroy(m);
-      return AIG_ERR_INVALID;  // main and shortcut paths disagree on odd extents (ResConvLayer.cpp:13-20)
+    int oh = 0, ow = 0;
+    // fused down-sampling launch when the plan fits and the producer of this block's input can write
+    // the space-to-depth layout it reads; otherwise the two separate stride-2 convolutions
+    if (allow_fused && h >= 2 && w >= 2 && aig_resdown_plan_create(ctx, c.batch, ci, h, w, co, c.act, c.slope, &b.down) == AIG_OK) {
+      const int prc = i == 0 ? aig_conv0_plan_set_output_s2d(m->conv0, 1) : aig_conv_plan_set_output_s2d(m->blocks[i - 1].c1, 1);
+      if (prc != AIG_OK) {
+        aig_conv_plan_destroy(b.down);
+        b.down = nullptr;
+      } else if (i == 0) {
+        m->act0_s2d = true;
+      } else {
+        m->blocks[i - 1].y_s2d = true;
+      }
+    }
+    if (b.down) {
+      aig_conv_plan_out_dims(b.down, nullptr, &oh, &ow);
+    } else {
+      if ((rc = aig_conv_plan_create(ctx, &d, &b.c0)) != AIG_OK) return bail(rc);
+      aig_conv_plan_out_dims(b.c0, nullptr, &oh, &ow);
+      aig_conv_desc s = d;
+      s.kh = s.kw = 2; s.ph = s.pw = 0; s.act = AIG_ACT_NONE;
+      if ((rc = aig_conv_plan_create(ctx, &s, &b.sc)) != AIG_OK) return bail(rc);
+      int sh_, sw_;
+      aig_conv_plan_out_dims(b.sc, nullptr, &sh_, &sw_);
+      if (sh_ != oh || sw_ != ow) {
+        aig_cnn_destroy(m);
+        return AIG_ERR_INVALID;  // main and shortcut paths disagree on odd extents (ResConvLayer.cpp:13-20)
+      }
     }
     aig_conv_desc e = d;
     e.in_c = co; e.in_h = oh; e.in_w = ow; e.kh = e.kw = 3; e.sh = e.sw = 1; e.ph = e.pw = 1;
     if ((rc = aig_conv_plan_create(ctx, &e, &b.c1)) != AIG_OK) return bail(rc);
     const size_t n = (size_t)c.batch * oh * ow * co;
-    if (dev_alloc(m, &b.t, n) != AIG_OK || dev_alloc(m, &b.r, n) != AIG_OK || dev_alloc(m, &b.y, n) != AIG_OK) return bail(AIG_ERR_CUDA);
+    if (dev_alloc(m, &b.t, n) != AIG_OK || dev_alloc(m, &b.r, n) != AIG_OK) return bail(AIG_ERR_CUDA);
     m->blocks.push_back(b);
     m->bh.push_back(oh);
     m->bw.push_back(ow);
@@ -234,12 +258,28 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
       const double px = (double)c.batch * oh * ow;
       const double in_b = (double)c.batch * h * w * ci * 2, out_b = px * co * 2;
       const std::string nm = "res" + std::to_string(i);
-      m->sites.push_back({nm + ".shortcut_k2s2", 2.0 * px * co * ci * 4, in_b + out_b + (double)co * ci * 4 * 2});
-      m->sites.push_back({nm + ".conv0_k4s2", 2.0 * px * co * ci * 16, in_b + out_b + (double)co * ci * 16 * 2});
+      if (b.down) {
+        m->sites.push_back({nm + ".down_k4s2+shortcut_k2s2", 2.0 * px * co * ci * 20, in_b + 2 * out_b + (double)co * ci * 20 * 2});
+      } else {
+        m->sites.push_back({nm + ".shortcut_k2s2", 2.0 * px * co * ci * 4, in_b + out_b + (double)co * ci * 4 * 2});
+        m->sites.push_back({nm + ".conv0_k4s2", 2.0 * px * co * ci * 16, in_b + out_b + (double)co * ci * 16 * 2});
+      }
       m->sites.push_back({nm + ".conv1_k3s1", 2.0 * px * co * co * 9, 3 * out_b + (double)co * co * 9 * 2});
     }
     h = oh; w = ow;
-    m->launches_per_forward += 3;
+    m->launches_per_forward += b.down ? 2 : 3;
+  }
+  // stage outputs: channels-last, or space-to-depth blocks (zero-filled once: border sub-positions are
+  // never written and stand for the padding) where the consumer is a fused down-sampling launch
+  {
+    const size_t n0 = m->act0_s2d ? aig_s2d_elems(c.batch, m->H0, m->W0, c.widths[0]) : (size_t)c.batch * m->H0 * m->W0 * c.widths[0];
+    if (dev_alloc(m, &m->act0, n0) != AIG_OK) return bail(AIG_ERR_CUDA);
+    for (int i = 0; i < c.n_blocks; ++i) {
+      aig_cnn::Block& b = m->blocks[i];
+      const int co = c.widths[i + 1];
+      const size_t n = b.y_s2d ? aig_s2d_elems(c.batch, m->bh[i], m->bw[i], co) : (size_t)c.batch * m->bh[i] * m->bw[i] * co;
+      if (dev_alloc(m, &b.y, n) != AIG_OK) return bail(AIG_ERR_CUDA);
+    }
   }
   const int cl = c.widths[c.n_blocks];
   if (dev_alloc(m, &m->sa, (size_t)c.batch * h * w * cl) != AIG_OK || dev_alloc(m, &m->feat, (size_t)c.batch * cl) != AIG_OK ||
@@ -286,12 +326,14 @@ int aig_cnn_destroy(aig_cnn* m) {
     aig_conv_plan_destroy(b.c0);
     aig_conv_plan_destroy(b.c1);
     aig_conv_plan_destroy(b.sc);
+    aig_conv_plan_destroy(b.down);
     cudaFree(b.t);
     cudaFree(b.r);
     cudaFree(b.y);
   }
   aig_conv_plan_destroy(m->fc);
   cudaFree(m->act0);
+  cudaFree(m->stage_scratch);
   cudaFree(m->sa);
   cudaFree(m->feat);
   cudaFree(m->logits);
@@ -334,9 +376,13 @@ int aig_cnn_load_memory(aig_cnn* m, const void* blob, size_t bytes) {
         !read_conv(m, rd, c1, (size_t)co * co * 9, co, s) || !read_bn(m, rd, b1, co, s) ||
         !read_conv(m, rd, sc, (size_t)co * ci * 4, co, s))
       return fail(m, AIG_ERR_IO, io);
-    CNN_OK(m, aig_conv_plan_set_weights(m->blocks[i].c0, c0.w, c0.b, b0.a[0], b0.a[1], b0.a[2], b0.a[3], eps));
+    if (m->blocks[i].down) {
+      CNN_OK(m, aig_resdown_plan_set_weights(m->blocks[i].down, c0.w, c0.b, b0.a[0], b0.a[1], b0.a[2], b0.a[3], eps, sc.w, sc.b));
+    } else {
+      CNN_OK(m, aig_conv_plan_set_weights(m->blocks[i].c0, c0.w, c0.b, b0.a[0], b0.a[1], b0.a[2], b0.a[3], eps));
+      CNN_OK(m, aig_conv_plan_set_weights(m->blocks[i].sc, sc.w, sc.b, nullptr, nullptr, nullptr, nullptr, 0.f));
+    }
     CNN_OK(m, aig_conv_plan_set_weights(m->blocks[i].c1, c1.w, c1.b, b1.a[0], b1.a[1], b1.a[2], b1.a[3], eps));
-    CNN_OK(m, aig_conv_plan_set_weights(m->blocks[i].sc, sc.w, sc.b, nullptr, nullptr, nullptr, nullptr, 0.f));
   }
   const int cl = c.widths[c.n_blocks];
   m->sa_w = (aig_half*)m->params.take((size_t)cl * 2);
@@ -380,10 +426,15 @@ int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) {
   tick();
   const aig_half* x = m->act0;
   for (auto& b : m->blocks) {
-    CNN_OK(m, aig_conv_forward(b.sc, x, nullptr, b.r));
-    tick();
-    CNN_OK(m, aig_conv_forward(b.c0, x, nullptr, b.t));
-    tick();
+    if (b.down) {
+      CNN_OK(m, aig_resdown_forward(b.down, x, b.t, b.r));
+      tick();
+    } else {
+      CNN_OK(m, aig_conv_forward(b.sc, x, nullptr, b.r));
+      tick();
+      CNN_OK(m, aig_conv_forward(b.c0, x, nullptr, b.t));
+      tick();
+    }
     CNN_OK(m, aig_conv_forward(b.c1, b.t, b.r, b.y));
     tick();
     x = b.y;
@@ -538,16 +589,25 @@ const aig_half* aig_cnn_features(aig_cnn* m) { return m ? m->feat : nullptr; }
 int aig_cnn_kernel_launches(aig_cnn* m) { return m ? m->launches_per_forward : 0; }
 const aig_half* aig_cnn_stage_output(aig_cnn* m, int stage, int* h, int* w, int* ch) {
   if (!m || stage < 0 || stage > (int)m->blocks.size()) return nullptr;
-  if (stage == 0) {
-    if (h) *h = m->H0;
-    if (w) *w = m->W0;
-    if (ch) *ch = m->cfg.widths[0];
-    return m->act0;
+  const int sh = stage == 0 ? m->H0 : m->bh[stage - 1], sw = stage == 0 ? m->W0 : m->bw[stage - 1], sc = m->cfg.widths[stage];
+  if (h) *h = sh;
+  if (w) *w = sw;
+  if (ch) *ch = sc;
+  const aig_half* buf = stage == 0 ? m->act0 : m->blocks[stage - 1].y;
+  const bool s2d = stage == 0 ? m->act0_s2d : m->blocks[stage - 1].y_s2d;
+  if (!s2d) return buf;
+  // the stage lives in space-to-depth blocks: hand out a channels-last copy
+  const size_t n = (size_t)m->cfg.batch * sh * sw * sc;
+  if (m->stage_scratch_elems < n) {
+    aig_ctx_sync(m->ctx);
+    cudaFree(m->stage_scratch);
+    m->stage_scratch = nullptr;
+    m->stage_scratch_elems = 0;
+    if (cudaMalloc(reinterpret_cast<void**>(&m->stage_scratch), n * sizeof(aig_half)) != cudaSuccess) return nullptr;
+    m->stage_scratch_elems = n;
   }
-  if (h) *h = m->bh[stage - 1];
-  if (w) *w = m->bw[stage - 1];
-  if (ch) *ch = m->cfg.widths[stage];
-  return m->blocks[stage - 1].y;
+  if (aig_s2d_to_nhwc(m->ctx, buf, m->stage_scratch, m->cfg.batch, sh, sw, sc) != AIG_OK) return nullptr;
+  return m->stage_scratch;
 }
 
 }  // extern "C"

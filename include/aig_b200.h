@@ -216,6 +216,33 @@ int aig_conv0_forward_bgra(aig_conv0_plan* plan, const uint8_t* bgra, aig_half* 
 int aig_conv0_forward_nchw(aig_conv0_plan* plan, const aig_half* x_nchw, aig_half* y_nhwc);
 
 /* ---------------------------------------------------------------------------------------------
+ * Fused down-sampling pair of a residual block.  ResConvLayer (ResConvLayer.cpp:13-21) opens with two
+ * stride-2 convolutions of the same input: the main ConvLayer(k4, s2, p1) + BatchNorm + activation and
+ * the shortcut ConvLayer(k2, s2, p0) (Forward: ResConvLayer.cpp:28-31).  Over the 2x2 space-to-depth
+ * view of the input both are one stride-1 GEMM; this plan runs them as ONE launch that reads the input
+ * once and writes both results (channels-last, [batch][Ho][Wo][out_c] each).
+ *
+ * Space-to-depth layout of an [h][w][c] image: [hb][wb][4][c] with hb = (h-2)/2+2, wb = (w-2)/2+2;
+ * pixel (y, x) lives in block ((y+1)>>1, (x+1)>>1) at sub-position ((y+1)&1)*2 + ((x+1)&1).  Buffers in
+ * this layout must be zero-filled once before first use (border sub-positions are never written and
+ * stand for the padding).  Producers write it directly: aig_conv0_plan_set_output_s2d and
+ * aig_conv_plan_set_output_s2d switch a plan's output to this layout. */
+size_t aig_s2d_elems(int batch, int h, int w, int c);
+int aig_nhwc_to_s2d(aig_ctx* ctx, const aig_half* x, aig_half* s2d, int batch, int h, int w, int c);
+int aig_s2d_to_nhwc(aig_ctx* ctx, const aig_half* s2d, aig_half* y, int batch, int h, int w, int c);
+int aig_conv_plan_set_output_s2d(aig_conv_plan* plan, int enable);
+int aig_conv0_plan_set_output_s2d(aig_conv0_plan* plan, int enable);
+/* in_c % 16 == 0; out_c 64, 128 or a multiple of 128 whose double is a multiple of 256. */
+int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_w, int out_c, int act, float slope,
+                            aig_conv_plan** out);
+/* w_main fp16 [out_c][in_c][4][4], w_short fp16 [out_c][in_c][2][2] (ConvLayer::LoadParameters layout,
+ * ConvLayer.cpp:96-107), biases fp16 [out_c]; bn_* = the BatchNorm after the main convolution or null. */
+int aig_resdown_plan_set_weights(aig_conv_plan* plan, const aig_half* w_main, const aig_half* b_main,
+                                 const float* bn_gamma, const float* bn_beta, const float* bn_mean,
+                                 const float* bn_var, float bn_eps, const aig_half* w_short, const aig_half* b_short);
+int aig_resdown_forward(aig_conv_plan* plan, const aig_half* x_s2d, aig_half* y_main, aig_half* y_short);
+
+/* ---------------------------------------------------------------------------------------------
  * LSTM.  Replaces LSTMLayer (LSTMLayer.cpp:4-40 constructor, :75-104 Forward: cudnnRNNForwardInference,
  * seq-major x [T][B][in] -> y [T][B][hidden], cell clip +-5, two bias vectors) and the cuDNN-8 variant
  * (LSTMLayerv8.cpp:8-39,78-82: batch-major [B][T][.], single bias, no clip).

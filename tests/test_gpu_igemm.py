@@ -207,3 +207,111 @@ def test_first_layer_convs(env):
     got = U.nchw(U.host(dy).reshape(B, *want.shape[2:], K))
     assert U.scaled_err(got, want) < 4e-3
     plan.close()
+
+
+def _s2d_host(x_nhwc):
+    """numpy restatement of the space-to-depth block layout: [B][H][W][C] -> [B][hb][wb][4][C]."""
+    B, H, W, C = x_nhwc.shape
+    hb, wb = (H - 2) // 2 + 2, (W - 2) // 2 + 2
+    out = np.zeros((B, hb, wb, 4, C), x_nhwc.dtype)
+    for y in range(H):
+        for x in range(W):
+            out[:, (y + 1) >> 1, (x + 1) >> 1, ((y + 1) & 1) * 2 + ((x + 1) & 1)] = x_nhwc[:, y, x]
+    return out
+
+
+RESDOWN = [
+    # B, C, H, W, K
+    (2, 32, 24, 32, 64),     # N = 128 in one tile, 32-channel sub-positions
+    (3, 64, 18, 32, 128),    # N = 256 in one tile
+    (2, 128, 9, 16, 256),    # two N tiles, sparse shortcut schedule, odd height
+    (5, 32, 72, 128, 64),    # several M tiles per CTA, resident weights
+]
+
+
+@gpu
+@pytest.mark.parametrize("B,C,H,W,K", RESDOWN)
+def test_fused_downsampling_pair(env, B, C, H, W, K):
+    """Main k4 s2 p1 conv + BatchNorm + Swish and the k2 s2 p0 shortcut of a residual block in one launch
+    over the space-to-depth input, against the two oracle convolutions."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    pk = U.pkg()
+    x = h(RNG.standard_normal((B, C, H, W)))
+    w0 = PL.he_normal(RNG, (K, C, 4, 4))
+    b0 = h(RNG.uniform(-0.2, 0.2, K))
+    bn = PL.bn_params(RNG, K, trivial=False)
+    ws = PL.he_normal(RNG, (K, C, 2, 2))
+    bs = h(RNG.uniform(-0.2, 0.2, K))
+    want_main = O.activate(O.batchnorm(O.conv2d(x, w0, b0, 2, 1), *bn), 2, 0.01)
+    want_short = O.conv2d(x, ws, bs, 2, 0)
+    Ho, Wo = want_main.shape[2:]
+    assert want_short.shape == want_main.shape
+    plan = pk.ResDownPlan(c, B, C, H, W, K, act=pk.ACT_SWISH)
+    assert plan.out_dims() == (1, Ho, Wo)
+    keep = [U.dev(a) for a in (w0, b0, ws, bs)] + [U.dev(q) for q in bn]
+    plan.set_weights(keep[0], keep[1], keep[4:], keep[2], keep[3], eps=1e-6)
+    # space-to-depth input made on the device from the channels-last tensor, checked against the numpy layout
+    dx = U.dev(U.nhwc(x))
+    n_s2d = pk.lib().aig_s2d_elems(B, H, W, C)
+    ds = torch.zeros(n_s2d, dtype=torch.float16, device="cuda")
+    c.call("aig_nhwc_to_s2d", U.p(dx), U.p(ds), B, H, W, C)
+    c.sync()
+    assert np.array_equal(U.host(ds).reshape(-1), _s2d_host(U.nhwc(x)).reshape(-1))
+    dm = torch.zeros(want_main.size, dtype=torch.float16, device="cuda")
+    dsh = torch.zeros(want_main.size, dtype=torch.float16, device="cuda")
+    plan.forward(ds, dm, dsh)
+    c.sync()
+    got_main = U.nchw(U.host(dm).reshape(B, Ho, Wo, K))
+    got_short = U.nchw(U.host(dsh).reshape(B, Ho, Wo, K))
+    assert U.scaled_err(got_main, want_main) < 6e-3
+    assert U.scaled_err(got_short, want_short) < 3e-3
+    # round trip of the layout conversion
+    back = torch.zeros_like(dx)
+    c.call("aig_s2d_to_nhwc", U.p(ds), U.p(back), B, H, W, C)
+    c.sync()
+    assert torch.equal(back, dx)
+    plan.close()
+
+
+@gpu
+def test_conv_output_in_space_to_depth_layout(env):
+    """A stride-1 convolution writing straight into the space-to-depth layout gives the same values as
+    its channels-last output rearranged."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    pk = U.pkg()
+    for (B, C, H, W, K) in [(2, 64, 12, 16, 64), (3, 128, 9, 16, 128)]:
+        x = h(RNG.standard_normal((B, C, H, W)))
+        w = PL.he_normal(RNG, (K, C, 3, 3))
+        b = h(RNG.uniform(-0.2, 0.2, K))
+        res = h(RNG.standard_normal((B, K, H, W)))
+        plan = pk.ConvPlan(c, B, C, H, W, K, 3, 1, 1, act=pk.ACT_SWISH)
+        dw, db, dx, dr = U.dev(w), U.dev(b), U.dev(U.nhwc(x)), U.dev(U.nhwc(res))
+        plan.set_weights(dw, db)
+        plain = torch.zeros(B * H * W * K, dtype=torch.float16, device="cuda")
+        plan.forward(dx, plain, residual=dr)
+        c.sync()
+        c.check(pk.lib().aig_conv_plan_set_output_s2d(plan.handle, 1))
+        blocks = torch.zeros(pk.lib().aig_s2d_elems(B, H, W, K), dtype=torch.float16, device="cuda")
+        plan.forward(dx, blocks, residual=dr)
+        c.sync()
+        want = _s2d_host(U.host(plain).reshape(B, H, W, K))
+        assert np.array_equal(U.host(blocks).reshape(-1), want.reshape(-1))
+        plan.close()
+
+
+@gpu
+def test_fused_downsampling_refuses_what_does_not_fit(env):
+    """1024 space-to-depth channels need a patch larger than shared memory: the plan is refused with a
+    clear status (callers then use the two separate convolutions)."""
+    U = env
+    pk = U.pkg()
+    with pytest.raises(pk.AigError, match="no tile fits"):
+        pk.ResDownPlan(U.ctx(), 1, 256, 10, 12, 256)
+    with pytest.raises(pk.AigError, match="in_c"):
+        pk.ResDownPlan(U.ctx(), 1, 24, 10, 12, 64)
