@@ -17,6 +17,8 @@
 // warps 2..9 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
 // Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all
 // roles drain to the common exit where TMEM is freed.
+#include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <vector>
 
@@ -702,6 +704,25 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const float* sc = p.n_tiles == 1 ? s_scale : p.scale + nb;
         const float* sf = p.n_tiles == 1 ? s_shift : p.shift + nb;
         const OutSeg& sg = p.seg[(nb + col_lo) >= p.n_split ? 1 : 0];
+        if (sg.residual) {
+          // pull the residual rows of this CTA's next tile (and of its first tile) towards L2 now, so that
+          // the loads in the epilogue steps below find them there instead of waiting on HBM
+          for (int which = (m_tile == (int)blockIdx.x ? 0 : 1); which < 2; ++which) {
+            const int mt = m_tile + which * (int)gridDim.x;
+            if (mt >= p.m_tiles) break;
+#pragma unroll 1
+            for (int sub = 0; sub < MS; ++sub) {
+              const long long q = (long long)mt * kM + sub * kTileM + row_in_tile;
+              const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
+              const int n = vr / p.RP, yy = vr - n * p.RP;
+              if (n < p.batch && yy < p.Ho && vc < p.Wo) {
+                const __half* rr = sg.residual + (((size_t)n * p.Ho + yy) * p.Wo + vc) * sg.channels + (nb - sg.c0 + col_lo);
+                for (int b = 0; b < NT; b += 128)  // NT/2 halfs = NT bytes per row segment
+                  asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(rr) + b));
+              }
+            }
+          }
+        }
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
         tc_fence_after();
         if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 5] = clock64();
@@ -1085,28 +1106,55 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   double best = -1;
   int best_ms = 0, best_acc = 2, best_pb = 2, best_stages = 0, best_opt = 0;
   bool best_res = false;
+  int f_nt = 0, f_ms = 0, f_pb = 0;  // tuning aid: AIG_PCONV_FORCE="NT,MS,patch buffers" restricts the search
+  if (const char* f = getenv("AIG_PCONV_FORCE")) sscanf(f, "%d,%d,%d", &f_nt, &f_ms, &f_pb);
   for (int o = 0; o < n_opts; ++o) {
     const int NT = opts[o].NT, wblock = NT * 128;
     const int dense_kb = q.taps * q.cblocks;
+    if (f_nt && NT != f_nt) continue;
     for (int ms = 4; ms >= 1; ms /= 2) {
       if (ms * NT > 512) continue;
+      if (f_ms && ms != f_ms) continue;
       const int acc = 2 * ms * NT <= 512 ? 2 : 1;
       const int M = ms * kTileM;
       const int vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
       const long long patch = (long long)vrows * q.P * 128 * q.cblocks;
       const long long m_tiles = ceil_div_ll(total_q, M);
-      if (ms > 1 && m_tiles < ctx->sm_count) continue;  // keep every SM busy before growing the tile
+      if (ms > 1 && m_tiles < ctx->sm_count && !f_ms) continue;  // keep every SM busy before growing the tile
+      // Time model of one CTA tile, in SM clocks, from measurements on B200 at 256 frames:
+      //  - operands stream from L2 at most ~34 B/clk/SM, and only with enough bytes in flight: a weight
+      //    ring of R bytes sustains about R / 4000 B/clk (TMA round trip under load ~4000 clk)
+      //  - tcgen05.mma M128 x N x K16 takes 49 / 64 / 128 clk for N = 64 / 128 / 256
+      //  - the epilogue (8 warps) costs ~0.45 clk per output element
+      // The busiest CTA runs ceil(tiles / SMs) tiles.
+      const double kCap = 34.0, kLat = 4000.0;
+      const double rounds = (double)ceil_div_ll(m_tiles, ctx->sm_count);
+      const double mma_clk = NT == 64 ? 49.0 : (NT == 128 ? 64.0 : 128.0);
+      const double t_patch = (double)patch / kCap;
+      const double t_epi = 0.45 * M * NT * opts[o].n_tiles;
       for (int pb = 2; pb >= 1; --pb) {
-        const double pen = (acc == 1 ? 1.15 : 1.0) * (pb == 1 ? 1.1 : 1.0);  // what the lost overlap costs, roughly
-        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget) {
-          const double cost = (double)patch / M * pen;
-          if (best < 0 || cost < best) { best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = true; best_stages = dense_kb; best_opt = o; }
-        }
-        long long stages = (kPconvBudget - pb * patch) / wblock;
-        if (stages > 32) stages = 32;
-        if (stages >= 2) {
-          const double cost = ((double)patch + (double)opts[o].w_kblocks * wblock) / M * pen * (stages == 2 ? 1.1 : 1.0);
-          if (best < 0 || cost < best) { best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = false; best_stages = (int)stages; best_opt = o; }
+        if (f_pb && pb != f_pb) continue;
+        for (int res = 1; res >= 0; --res) {
+          double t_w = 0, t_mma;
+          long long stages;
+          if (res) {
+            if (opts[o].n_tiles != 1 || pb * patch + (long long)dense_kb * wblock > kPconvBudget) continue;
+            stages = dense_kb;
+            t_mma = (double)dense_kb * ms * 4 * mma_clk;
+          } else {
+            stages = (kPconvBudget - pb * patch) / wblock;
+            if (stages > 32) stages = 32;
+            if (stages < 2) continue;
+            const double rate = std::min(kCap, (double)stages * wblock / kLat);
+            t_w = (double)opts[o].w_kblocks * wblock / rate;
+            t_mma = (double)opts[o].w_kblocks * ms * 4 * mma_clk;
+          }
+          const double core = pb == 2 ? std::max(t_mma, t_w + t_patch) : std::max(t_mma, t_w) + t_patch;
+          const double t_tile = acc == 2 ? std::max(core, t_epi) : core + t_epi;
+          const double cost = rounds * t_tile;
+          if (best < 0 || cost < best) {
+            best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = res != 0; best_stages = (int)stages; best_opt = o;
+          }
         }
       }
     }
