@@ -482,6 +482,7 @@ struct PconvParams {
   int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
   int acc_bufs;            // TMEM accumulator buffers: 2, or 1 when MS*NT fills all 512 columns
   int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
+  int G, groups;           // 64-channel blocks per patch unit, units per pass over the channels (G * groups == cblocks)
   int n_split;             // GEMM columns >= n_split go to seg[1]
   int sparse_tile0;        // N tiles >= this one use the sparse shortcut K schedule (INT_MAX: none)
   int sub_cblocks;         // 64-channel blocks per space-to-depth sub-position (sparse schedule)
@@ -490,6 +491,9 @@ struct PconvParams {
   const float* shift;
   OutSeg seg[2];
   int* gerr;
+  const uint32_t* tab;     // K schedule tables (see PconvTab)
+  int tab_words;
+  int dbg;                 // tuning aid: 1 = no stores, 2 = no residual loads, 4 = TMEM loads only
   long long* ts;           // optional timeline of CTA 0 (8 stamps per tile, first 16 tiles), or null
 };
 
@@ -499,29 +503,20 @@ struct PconvParams {
 // rows into an atom is read consistently (verified against the CPU oracle; setting the descriptor's
 // base-offset field to the row phase gives wrong results).
 
-// K schedule of one N tile as an iterator over (tap, 64-channel block) without divisions.  The dense
-// schedule walks every block of every tap; the sparse one (shortcut rows of a fused down-sampling
-// GEMM, 2x2 taps) only the blocks of the one space-to-depth sub-position that tap reads.
-struct PconvKIter {
-  int tap, fr, fs, l, cb, lim;
-  bool sparse;
-  __device__ __forceinline__ void start(const PconvParams& p, bool sp) {
-    sparse = sp;
-    tap = fr = fs = l = 0;
-    lim = sp ? p.sub_cblocks : p.cblocks;
-    cb = sp ? 3 * p.sub_cblocks : 0;
-  }
-  __device__ __forceinline__ void next(const PconvParams& p) {
-    ++l;
-    ++cb;
-    if (l == lim) {
-      l = 0;
-      ++tap;
-      if (++fs == p.kw) { fs = 0; ++fr; }
-      cb = sparse ? ((1 - fr) * 2 + (1 - fs)) * p.sub_cblocks : 0;
-    }
-  }
-};
+// K schedule.  The 64-channel blocks of the input are split into `groups` groups of G blocks; a patch
+// unit in shared memory holds one group (all of them when groups == 1).  For one N tile the K loop runs
+// group-major: for every group, every tap, the blocks of that group the tap needs.  A dense tile needs
+// all G blocks; a sparse tile (shortcut rows of a fused down-sampling GEMM, 2x2 taps) only the blocks
+// of the space-to-depth sub-position the tap reads, (1-fr, 1-fs): global blocks [sp*sub, (sp+1)*sub).
+// The host writes both schedules as tables, the kernel copies them to shared memory once, and the
+// issue loops walk them with one load per step:
+//   words [0, 17)  dense:  first entry of group g (word 16 = one past the last)
+//   words [17, 34) sparse: the same
+//   then the dense entries, then the sparse ones; an entry is
+//     low 16 bits:  row offset of the A operand inside the patch unit (block l of the group, tap shift)
+//     high 16 bits: weight block index tap*cblocks + cb (K coordinate / 64, and slot of resident weights)
+constexpr int kTabHead = 34;
+constexpr int kTabMaxWords = kTabHead + 2 * 256;
 
 constexpr int kPconvThreads = 352;  // patch producer, MMA issuer, 8 epilogue warps, weight producer
 constexpr int kWeightWarp = 10;
@@ -549,8 +544,10 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   const uint32_t bar_wempty = bar_wfull + 8 * 32;     // [w_stages]
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  uint32_t* s_tab = s_tmem + 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < p.tab_words; i += kPconvThreads) s_tab[i] = p.tab[i];
   if (p.n_tiles == 1) {
     for (int i = threadIdx.x; i < NT; i += kPconvThreads) {
       s_scale[i] = p.scale[i];
@@ -583,28 +580,46 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
-  const int dense_kb = p.taps * p.cblocks, sparse_kb = p.taps * p.sub_cblocks;
+  const int dense_kb = p.taps * p.cblocks;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ patch producer
+    // one unit = the patch rows of one channel-block group; with a single group the unit serves all N
+    // tiles of the M tile, otherwise the groups are streamed again for every N tile
     if (lane == 0) {
-      int it = 0;
-      for (int m_tile = blockIdx.x; m_tile < p.m_tiles; m_tile += gridDim.x, ++it) {
-        const int buf = p.patch_bufs == 2 ? (it & 1) : 0;
-        const uint32_t ph = (uint32_t)(p.patch_bufs == 2 ? (it >> 1) : it) & 1u;
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
-        if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) break;
-        mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.cblocks));
+      int it = 0, uc = 0;
+      bool ok = true;
+      const int units = p.groups == 1 ? 1 : p.n_tiles * p.groups;
+      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
-        const uint32_t dst0 = sPatch + buf * p.patch_bytes;
-        int n = vr0 / p.RP, yy = vr0 - n * p.RP;
-        for (int r = 0; r < p.patch_vrows; ++r) {
-          for (int cb = 0; cb < p.cblocks; ++cb)
-            tma_load_5d(dst0 + cb * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, cb * 64, -p.pad, yy - p.pad, 0, n);
-          if (++yy == p.RP) { yy = 0; ++n; }
+        const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
+        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
+        for (int u = 0; u < units && ok; ++u, ++uc) {
+          const int g = p.groups == 1 ? 0 : u % p.groups;
+          const int buf = p.patch_bufs == 2 ? (uc & 1) : 0;
+          const uint32_t ph = (uint32_t)(p.patch_bufs == 2 ? (uc >> 1) : uc) & 1u;
+          if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
+          mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
+          const uint32_t dst0 = sPatch + buf * p.patch_bytes;
+          int n = n0, yy = yy0;
+          for (int r = 0; r < p.patch_vrows; ++r) {
+            for (int l = 0; l < p.G; ++l)
+              tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
+            if (++yy == p.RP) { yy = 0; ++n; }
+          }
         }
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
+        // the patch two tiles ahead: towards L2 now, so that its load later is an L2 hit
+        const int ahead = m_tile + 2 * (int)gridDim.x;
+        if (ahead < p.m_tiles && !(p.dbg & 8)) {
+          const int avr0 = (int)(((long long)ahead * kM) / p.P);
+          int an = avr0 / p.RP, ayy = avr0 - an * p.RP;
+          for (int r = 0; r < p.patch_vrows; ++r) {
+            for (int cb = 0; cb < p.cblocks; ++cb) tma_prefetch_5d(&tmapA, cb * 64, -p.pad, ayy - p.pad, 0, an);
+            if (++ayy == p.RP) { ayy = 0; ++an; }
+          }
+        }
       }
     }
   } else if (warp == kWeightWarp) {
@@ -620,13 +635,12 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
           for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile) {
             const bool sparse = n_tile >= p.sparse_tile0;
-            const int nkb = sparse ? sparse_kb : dense_kb;
-            PconvKIter ki;
-            ki.start(p, sparse);
-            for (int kb = 0; kb < nkb; ++kb, ki.next(p)) {
+            const uint32_t* gs = s_tab + (sparse ? 17 : 0);
+            const uint32_t* ent = s_tab + kTabHead;
+            for (uint32_t e = gs[0]; e < gs[p.groups]; ++e) {
               if (!mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)) { ok = false; break; }
               mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
-              tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (ki.tap * p.cblocks + ki.cb) * 64, n_tile * NT);
+              tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
           }
@@ -640,15 +654,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
       bool ok = true;
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
-      int it = 0, cnt = 0, stage = 0;
+      int it = 0, cnt = 0, stage = 0, uc = 0;
       uint32_t wphase = 0;
       for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
-        const int buf = p.patch_bufs == 2 ? (it & 1) : 0;
-        if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(p.patch_bufs == 2 ? (it >> 1) : it) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 3] = clock64();
         const long long q0 = (long long)m_tile * kM;
         const int off0 = (int)(q0 - (q0 / p.P) * p.P);
-        const uint32_t patch = sPatch + buf * p.patch_bytes;
         for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile, ++cnt) {
           const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
           const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
@@ -656,35 +666,50 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
           const bool sparse = n_tile >= p.sparse_tile0;
-          const int nkb = sparse ? sparse_kb : dense_kb;
-          PconvKIter ki;
-          ki.start(p, sparse);
-          for (int kb = 0; kb < nkb; ++kb, ki.next(p)) {
-            uint32_t b0;
-            if (WRES) {
-              b0 = sW + kb * kWBlock;
-            } else {
-              if (!mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
-              b0 = sW + stage * kWBlock;
+          uint32_t first = 0;  // 0 until the first MMA of this accumulator has been issued
+          const uint32_t* gs = s_tab + (sparse ? 17 : 0);
+          const uint32_t* ent = s_tab + kTabHead;
+          for (int g = 0; g < p.groups && ok; ++g) {
+            // the patch unit of this group: a new one per (N tile, group), or the M tile's only one
+            const bool fresh = p.groups > 1 || n_tile == 0;
+            const int buf = p.patch_bufs == 2 ? (uc & 1) : 0;
+            if (fresh) {
+              if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(p.patch_bufs == 2 ? (uc >> 1) : uc) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
+              if (p.ts && blockIdx.x == 0 && it < 16 && n_tile == 0 && g == 0) p.ts[it * 8 + 3] = clock64();
             }
-            const uint32_t a0 = patch + ki.cb * p.region_bytes + (uint32_t)(off0 + ki.fr * p.P + ki.fs) * 128u;
-            const uint32_t a_lo = umma_desc_lo(a0), b_lo = umma_desc_lo(b0);
-            const uint32_t first = kb != 0 ? 1u : 0u;
+            const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
+            const uint32_t e1 = gs[g + 1];
+            for (uint32_t e = gs[g]; e < e1; ++e) {
+              const uint32_t en = ent[e];
+              uint32_t b0;
+              if (WRES) {
+                b0 = sW + (en >> 16) * kWBlock;
+              } else {
+                if (!mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
+                b0 = sW + stage * kWBlock;
+              }
+              const uint32_t a_lo = umma_desc_lo(patch + (en & 0xFFFFu) * 128u), b_lo = umma_desc_lo(b0);
 #pragma unroll
-            for (int sub = 0; sub < MS; ++sub) {
+              for (int sub = 0; sub < MS; ++sub) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k)
-                umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
-                               b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+                for (int k = 0; k < 4; ++k)
+                  umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
+                                 b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+              }
+              first = 1u;
+              if (!WRES) {
+                umma_commit(bar_wempty + 8 * stage);
+                if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
+              }
             }
-            if (!WRES) {
-              umma_commit(bar_wempty + 8 * stage);
-              if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
+            // the unit may be overwritten once these MMAs have read it
+            if (ok && (p.groups > 1 || n_tile == p.n_tiles - 1)) {
+              umma_commit(bar_pempty + 8 * buf);
+              ++uc;
             }
           }
           if (ok) umma_commit(bar_tfull + 8 * acc);
         }
-        if (ok) umma_commit(bar_pempty + 8 * buf);  // the patch may be overwritten once these MMAs have read it
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 4] = clock64();
       }
     }
@@ -731,7 +756,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const long long q = (long long)m_tile * kM + sub * kTileM + row_in_tile;
           const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
           const int n = vr / p.RP, yy = vr - n * p.RP;
-          const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
+          const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo && !(p.dbg & 4);
           const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
           size_t opix = pix;
           if (sg.s2d) {
@@ -739,7 +764,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             opix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
           }
           __half* yrow = sg.y + opix * sg.channels;
-          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
+          const __half* rrow = (sg.residual && !(p.dbg & 2)) ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
+          if (p.dbg & 1) yrow = sg.y + (size_t)(threadIdx.x & 31) * sg.channels;  // tuning aid: every tile stores to the same 32 rows
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
   if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
@@ -888,6 +914,7 @@ struct aig_conv_plan {
   // patch-resident path (stride-1 2-D convolutions and fused down-sampling blocks)
   bool use_pconv = false;
   PconvParams pp{};
+  uint32_t* pc_tab = nullptr;
   CUtensorMap tmapP{}, tmapBp{};
   const void* tmapP_ptr = nullptr;
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
@@ -1055,7 +1082,7 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
 
 
 // ---- patch-resident path: host side ------------------------------------------------------
-constexpr int kPconvTail = 2048 /*scale,shift*/ + 1024 /*barriers*/;
+constexpr int kPconvTail = 2048 /*scale,shift*/ + 1024 /*barriers*/ + 2560 /*K schedule tables*/;
 constexpr int kPconvBudget = 227 * 1024 - 1024 /*align*/ - kPconvTail;
 
 template <int NT, int MS, bool WRES>
@@ -1096,66 +1123,65 @@ struct PconvNtOption {
   int NT, n_tiles, w_kblocks, sparse_tile0;
 };
 
-// Chooses, among the N tilings offered, the tile (sub-tiles per CTA tile, resident or streamed weights,
-// one or two patch buffers) that moves the fewest bytes per output position from L2 and fits shared
-// memory and TMEM.  Geometry (P, RP, pad, kw, taps, cblocks, Ho, Wo, batch) must be filled in already.
-// Returns false when nothing fits.
+// Chooses the tile: N tiling, sub-tiles per CTA tile, resident or streamed weights, patch buffers and
+// channel-block group size.  Geometry (P, RP, pad, kw, taps, cblocks, Ho, Wo, batch) must be filled in
+// already.  Returns false when nothing fits.
+//
+// The rules below are what a sweep over all combinations on the encoder's layers (256 frames, B200)
+// showed; measured facts behind them:
+//  - operands stream from L2 to an SM at 35-40 B/clk at best, and only with enough bytes in flight:
+//    two to four weight stages of 32 KB saturate it, a TMA round trip under load is 2000-4000 clk;
+//  - tcgen05.mma M128 x N x K16 takes 49 / 64 / 128 clk for N = 64 / 128 / 256, so the widest N tile that
+//    exists wins, and sub-tiles are added until the accumulators fill 256 TMEM columns (the other 256 are
+//    the second buffer the epilogue drains); single-buffered accumulators lose more than they save;
+//  - two patch buffers beat one even when that means smaller channel-block groups, but every extra
+//    patch unit costs ~1300 clk of hand-over, so the largest group that still leaves two weight stages;
+//  - resident weights win whenever they fit beside two patches;
+//  - the busiest CTA runs ceil(tiles / SMs) tiles, so sub-tiles are dropped while tiles < SMs.
 bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opts, int n_opts, int kh) {
   PconvParams& q = pl->pp;
   const long long total_q = (long long)q.batch * q.RP * q.P;
   double best = -1;
-  int best_ms = 0, best_acc = 2, best_pb = 2, best_stages = 0, best_opt = 0;
+  int best_ms = 0, best_acc = 2, best_pb = 2, best_stages = 0, best_opt = 0, best_G = 0;
   bool best_res = false;
-  int f_nt = 0, f_ms = 0, f_pb = 0;  // tuning aid: AIG_PCONV_FORCE="NT,MS,patch buffers" restricts the search
-  if (const char* f = getenv("AIG_PCONV_FORCE")) sscanf(f, "%d,%d,%d", &f_nt, &f_ms, &f_pb);
-  for (int o = 0; o < n_opts; ++o) {
+  int f_nt = 0, f_ms = 0, f_pb = 0, f_g = 0;  // tuning aid: AIG_PCONV_FORCE="NT,MS,patch buffers,G" restricts the search
+  if (const char* f = getenv("AIG_PCONV_FORCE")) sscanf(f, "%d,%d,%d,%d", &f_nt, &f_ms, &f_pb, &f_g);
+  auto vrows_of = [&](int M) { return (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1; };
+  auto take = [&](int o, int ms, int pb, int G, bool res, long long stages) {
+    best = 1; best_opt = o; best_ms = ms; best_pb = pb; best_G = G; best_res = res; best_stages = (int)stages;
+    best_acc = 2 * ms * opts[o].NT <= 512 ? 2 : 1;
+  };
+  for (int o = 0; o < n_opts && best < 0; ++o) {
     const int NT = opts[o].NT, wblock = NT * 128;
     const int dense_kb = q.taps * q.cblocks;
     if (f_nt && NT != f_nt) continue;
-    for (int ms = 4; ms >= 1; ms /= 2) {
-      if (ms * NT > 512) continue;
-      if (f_ms && ms != f_ms) continue;
-      const int acc = 2 * ms * NT <= 512 ? 2 : 1;
-      const int M = ms * kTileM;
-      const int vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
-      const long long patch = (long long)vrows * q.P * 128 * q.cblocks;
-      const long long m_tiles = ceil_div_ll(total_q, M);
-      if (ms > 1 && m_tiles < ctx->sm_count && !f_ms) continue;  // keep every SM busy before growing the tile
-      // Time model of one CTA tile, in SM clocks, from measurements on B200 at 256 frames:
-      //  - operands stream from L2 at most ~34 B/clk/SM, and only with enough bytes in flight: a weight
-      //    ring of R bytes sustains about R / 4000 B/clk (TMA round trip under load ~4000 clk)
-      //  - tcgen05.mma M128 x N x K16 takes 49 / 64 / 128 clk for N = 64 / 128 / 256
-      //  - the epilogue (8 warps) costs ~0.45 clk per output element
-      // The busiest CTA runs ceil(tiles / SMs) tiles.
-      const double kCap = 34.0, kLat = 4000.0;
-      const double rounds = (double)ceil_div_ll(m_tiles, ctx->sm_count);
-      const double mma_clk = NT == 64 ? 49.0 : (NT == 128 ? 64.0 : 128.0);
-      const double t_patch = (double)patch / kCap;
-      const double t_epi = 0.45 * M * NT * opts[o].n_tiles;
-      for (int pb = 2; pb >= 1; --pb) {
-        if (f_pb && pb != f_pb) continue;
-        for (int res = 1; res >= 0; --res) {
-          double t_w = 0, t_mma;
-          long long stages;
-          if (res) {
-            if (opts[o].n_tiles != 1 || pb * patch + (long long)dense_kb * wblock > kPconvBudget) continue;
-            stages = dense_kb;
-            t_mma = (double)dense_kb * ms * 4 * mma_clk;
-          } else {
-            stages = (kPconvBudget - pb * patch) / wblock;
-            if (stages > 32) stages = 32;
-            if (stages < 2) continue;
-            const double rate = std::min(kCap, (double)stages * wblock / kLat);
-            t_w = (double)opts[o].w_kblocks * wblock / rate;
-            t_mma = (double)opts[o].w_kblocks * ms * 4 * mma_clk;
-          }
-          const double core = pb == 2 ? std::max(t_mma, t_w + t_patch) : std::max(t_mma, t_w) + t_patch;
-          const double t_tile = acc == 2 ? std::max(core, t_epi) : core + t_epi;
-          const double cost = rounds * t_tile;
-          if (best < 0 || cost < best) {
-            best = cost; best_ms = ms; best_acc = acc; best_pb = pb; best_res = res != 0; best_stages = (int)stages; best_opt = o;
-          }
+    int ms_top = 256 / NT < 1 ? 1 : 256 / NT;
+    if (f_ms) ms_top = f_ms;
+    if (ms_top * NT > 512) continue;
+    while (!f_ms && ms_top > 1 && ceil_div_ll(total_q, ms_top * kTileM) < ctx->sm_count) ms_top /= 2;
+    // resident weights beside two whole patches (then one), largest tile first
+    for (int pb = 2; pb >= 1 && best < 0; --pb) {
+      if (f_pb && pb != f_pb) continue;
+      if (f_g && f_g != q.cblocks) continue;
+      for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
+        const long long patch = (long long)vrows_of(ms * kTileM) * q.P * 128 * q.cblocks;
+        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget && pb == 2) take(o, ms, pb, q.cblocks, true, dense_kb);
+        if (ms == 1) break;
+      }
+    }
+    // streamed weights: two patch units of the largest channel-block group that leaves two stages
+    for (int pb = 2; pb >= 1 && best < 0; --pb) {
+      if (f_pb && pb != f_pb) continue;
+      for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
+        const long long region = (long long)vrows_of(ms * kTileM) * q.P * 128;
+        for (int G = q.cblocks; G >= 1 && best < 0; G /= 2) {
+          if (q.cblocks % G != 0) break;
+          if (f_g && G != f_g) continue;
+          long long stages = (kPconvBudget - pb * region * G) / wblock;
+          if (stages > 32) stages = 32;
+          if (stages >= 2) take(o, ms, pb, G, false, stages);
         }
+        if (ms == 1) break;
       }
     }
   }
@@ -1166,7 +1192,9 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   q.sparse_tile0 = opts[best_opt].sparse_tile0;
   q.patch_vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
   q.region_bytes = q.patch_vrows * q.P * 128;
-  q.patch_bytes = q.region_bytes * q.cblocks;
+  q.G = best_G;
+  q.groups = q.cblocks / best_G;
+  q.patch_bytes = q.region_bytes * q.G;
   q.patch_bufs = best_pb;
   q.w_stages = best_stages;
   q.acc_bufs = best_acc;
@@ -1177,6 +1205,47 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + kPconvTail;
   pl->pc_grid = q.m_tiles < ctx->sm_count ? q.m_tiles : ctx->sm_count;
   return true;
+}
+
+// Writes the K schedule tables of a plan whose tile has been chosen (layout: see kTabHead).
+int pconv_build_tables(aig_ctx* ctx, aig_conv_plan* pl) {
+  PconvParams& q = pl->pp;
+  std::vector<uint32_t> tab(kTabHead, 0u), entries[2];
+  const int region_rows = q.region_bytes / 128;
+  for (int sched = 0; sched < 2; ++sched) {
+    for (int g = 0; g < q.groups; ++g) {
+      tab[sched * 17 + g] = (uint32_t)entries[sched].size();
+      for (int tap = 0; tap < q.taps; ++tap) {
+        const int fr = tap / q.kw, fs = tap % q.kw;
+        int l0 = 0, l1 = q.G;
+        if (sched == 1) {
+          const int lo = ((1 - fr) * 2 + (1 - fs)) * q.sub_cblocks, hi = lo + q.sub_cblocks, g0 = g * q.G;
+          l0 = std::max(lo, g0) - g0;
+          l1 = std::min(hi, g0 + q.G) - g0;
+        }
+        for (int l = l0; l < l1; ++l) {
+          const uint32_t row = (uint32_t)(l * region_rows + fr * q.P + fs);
+          const uint32_t wblk = (uint32_t)(tap * q.cblocks + g * q.G + l);
+          if (row > 0xFFFFu || wblk > 0xFFFFu) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "pconv: K schedule entry out of range");
+          entries[sched].push_back(row | (wblk << 16));
+        }
+      }
+    }
+    for (int g = q.groups; g <= 16; ++g) tab[sched * 17 + g] = (uint32_t)entries[sched].size();
+    if (sched == 1 && q.kw != 2) entries[1].clear();  // the sparse schedule exists for 2x2 taps only
+  }
+  // sparse entries follow the dense ones: shift their group starts
+  for (int g = 0; g <= 16; ++g) tab[17 + g] += (uint32_t)entries[0].size();
+  tab.insert(tab.end(), entries[0].begin(), entries[0].end());
+  tab.insert(tab.end(), entries[1].begin(), entries[1].end());
+  if ((int)tab.size() > kTabMaxWords || q.groups > 16) return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "pconv: K schedule too long");
+  cudaFree(pl->pc_tab);
+  pl->pc_tab = nullptr;
+  AIG_CUDA_OK(ctx, cudaMalloc(&pl->pc_tab, tab.size() * sizeof(uint32_t)));
+  AIG_CUDA_OK(ctx, cudaMemcpy(pl->pc_tab, tab.data(), tab.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  q.tab = pl->pc_tab;
+  q.tab_words = (int)tab.size();
+  return AIG_OK;
 }
 
 int encode_Bp(aig_conv_plan* pl) {
@@ -1252,8 +1321,10 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   pl->pc_in_h = d.in_h;
   pl->pc_in_w = d.in_w;
   pl->pc_in_c = d.in_c;
-  const int rc = encode_Bp(pl);
+  int rc = pconv_build_tables(ctx, pl);
+  if (rc == AIG_OK) rc = encode_Bp(pl);
   if (rc != AIG_OK) return rc;
+  if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
   const char* ts = getenv("AIG_PCONV_TS");
   if (ts && atoi(ts)) {
     AIG_CUDA_OK(ctx, cudaMalloc(&q.ts, 128 * sizeof(long long)));
@@ -1300,17 +1371,19 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   cudaFree(pl->scale);
   cudaFree(pl->shift);
   cudaFree(pl->pp.ts);
+  cudaFree(pl->pc_tab);
   delete pl;
   return AIG_OK;
 }
 
 // Profiling aid (not part of the public interface): copies the timeline recorded by CTA 0 of the last
-// patch-resident launch (8 clock64 stamps per tile, 16 tiles) and the tile shape into out[0..131].
+// patch-resident launch (8 clock64 stamps per tile, 16 tiles) and the tile shape into out[0..135].
 int aig_conv_plan_debug_timeline(aig_conv_plan* pl, long long* out) {
   if (!pl || !out || !pl->use_pconv || !pl->pp.ts) return AIG_ERR_INVALID;
   cudaStreamSynchronize(pl->ctx->stream);
   cudaMemcpy(out, pl->pp.ts, 128 * sizeof(long long), cudaMemcpyDeviceToHost);
   out[128] = pl->pc_NT; out[129] = pl->pc_MS; out[130] = pl->pc_wres ? -1 : pl->pp.w_stages; out[131] = pl->pp.m_tiles;
+  out[132] = pl->pp.patch_bufs; out[133] = pl->pp.G; out[134] = pl->pp.acc_bufs; out[135] = 0;
   return AIG_OK;
 }
 
@@ -1524,8 +1597,13 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
     }
   }
   if (n_opts == 0 || !pconv_choose_tile(ctx, pl, opts, n_opts, 2)) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: no tile fits shared memory"));
+  if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
+  if (const char* ts = getenv("AIG_PCONV_TS")) {
+    if (atoi(ts) && cudaMalloc(&q.ts, 128 * sizeof(long long)) == cudaSuccess) cudaMemset(q.ts, 0, 128 * sizeof(long long));
+  }
   pl->pc_in_h = Hb; pl->pc_in_w = Wb; pl->pc_in_c = C4;
-  const int rc = encode_Bp(pl);
+  int rc = pconv_build_tables(ctx, pl);
+  if (rc == AIG_OK) rc = encode_Bp(pl);
   if (rc != AIG_OK) return bail(rc);
   pl->use_pconv = true;
   *out = pl;

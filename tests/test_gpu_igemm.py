@@ -226,6 +226,8 @@ RESDOWN = [
     (3, 64, 18, 32, 128),    # N = 256 in one tile
     (2, 128, 9, 16, 256),    # two N tiles, sparse shortcut schedule, odd height
     (5, 32, 72, 128, 64),    # several M tiles per CTA, resident weights
+    (1, 256, 10, 12, 256),   # 1024 space-to-depth channels: the patch streams in channel-block groups
+    (4, 256, 9, 16, 256),    # the same with odd height and several M tiles
 ]
 
 
@@ -306,12 +308,12 @@ def test_conv_output_in_space_to_depth_layout(env):
 
 
 @gpu
-def test_fused_downsampling_refuses_what_does_not_fit(env):
-    """1024 space-to-depth channels need a patch larger than shared memory: the plan is refused with a
-    clear status (callers then use the two separate convolutions)."""
+def test_fused_downsampling_refuses_unsupported_channel_counts(env):
+    """Channel counts the space-to-depth GEMM cannot tile are refused with a clear status (callers then
+    use the two separate convolutions)."""
     U = env
     pk = U.pkg()
-    with pytest.raises(pk.AigError, match="no tile fits"):
-        pk.ResDownPlan(U.ctx(), 1, 256, 10, 12, 256)
     with pytest.raises(pk.AigError, match="in_c"):
         pk.ResDownPlan(U.ctx(), 1, 24, 10, 12, 64)
+    with pytest.raises(pk.AigError, match="out_c"):
+        pk.ResDownPlan(U.ctx(), 1, 32, 10, 12, 48)
