@@ -188,6 +188,91 @@ __device__ __forceinline__ void epi_fused_cols(uint32_t t_addr, int col_lo, int 
   }
 }
 
+// The same step with coalesced global accesses.  A TMEM lane is an output pixel, so a thread owns one
+// row and its plain 16-byte stores hit 32 different lines per instruction; here the 32 rows x 64 bytes
+// of a step pass through a 2 KB per-warp staging tile in shared memory (16-byte chunks XOR-swizzled so
+// that both directions are conflict free) and leave as 8 rows x 64 contiguous bytes per instruction;
+// the residual arrives the same way.  Lane t serves row 8j + t/4, chunk t%4 on the global side.
+template <int ACT, bool RES>
+__device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
+                                                   const float* __restrict__ sc, const float* __restrict__ sf,
+                                                   const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
+                                                   bool valid, uint8_t* st, int lane) {
+  const int gr = lane >> 2, gc = lane & 3;
+  const int own = lane * 64, swz = (lane >> 1) & 3;
+  // row pointers and validity of the four rows this lane serves on the global side
+  __half* yp[4];
+  const __half* rp[4];
+  bool vj[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int row = 8 * j + gr;
+    yp[j] = reinterpret_cast<__half*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(yrow), row));
+    rp[j] = RES ? reinterpret_cast<const __half*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(rrow), row)) : nullptr;
+    vj[j] = __shfl_sync(0xffffffffu, valid ? 1 : 0, row) != 0;
+  }
+#pragma unroll 1
+  for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_addr + c0, r);
+    const int n0 = n_base + c0;
+    const bool cok = n0 + gc * 8 < out_c;
+    uint4 rv[4];
+    if (RES) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        rv[j] = (vj[j] && cok) ? __ldg(reinterpret_cast<const uint4*>(rp[j] + n0 + gc * 8)) : make_uint4(0, 0, 0, 0);
+    }
+    tmem_ld_wait();
+    uint4 rown[4];
+    if (RES) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = 8 * j + gr;
+        *reinterpret_cast<uint4*>(st + row * 64 + ((gc ^ ((row >> 1) & 3)) << 4)) = rv[j];
+      }
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) rown[c] = *reinterpret_cast<const uint4*>(st + own + ((c ^ swz) << 4));
+      __syncwarp();
+    }
+#pragma unroll
+    for (int v8 = 0; v8 < 4; ++v8) {
+      const float4 s0 = reinterpret_cast<const float4*>(sc + c0)[2 * v8], s1 = reinterpret_cast<const float4*>(sc + c0)[2 * v8 + 1];
+      const float4 h0 = reinterpret_cast<const float4*>(sf + c0)[2 * v8], h1 = reinterpret_cast<const float4*>(sf + c0)[2 * v8 + 1];
+      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+      const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+      const __half2* rh = reinterpret_cast<const __half2*>(&rown[v8]);
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2) {
+        const int e = v8 * 8 + e2 * 2;
+        float a0 = fmaf(__uint_as_float(r[e]), sv[e2 * 2], hv[e2 * 2]);
+        float a1 = fmaf(__uint_as_float(r[e + 1]), sv[e2 * 2 + 1], hv[e2 * 2 + 1]);
+        if (RES) {
+          // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
+          const float2 m = __half22float2(__floats2half2_rn(a0, a1));
+          const float2 rr = __half22float2(rh[e2]);
+          const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+          a0 = t.x;
+          a1 = t.y;
+        }
+        oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+      }
+      *reinterpret_cast<uint4*>(st + own + ((v8 ^ swz) << 4)) = o;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = 8 * j + gr;
+      const uint4 o = *reinterpret_cast<const uint4*>(st + row * 64 + ((gc ^ ((row >> 1) & 3)) << 4));
+      if (vj[j] && cok) *reinterpret_cast<uint4*>(yp[j] + n0 + gc * 8) = o;
+    }
+    __syncwarp();
+  }
+}
+
 // Generic epilogue: the reference's two-step rounding, fp32 output, or channel counts that are not a
 // multiple of 8 (scalar stores).  Rare paths; run-time checks are acceptable here.
 __device__ __forceinline__ void epi_generic_cols(uint32_t t_addr, int col_lo, int col_hi, int n_base, const IgemmParams& p,
@@ -493,6 +578,7 @@ struct PconvParams {
   int* gerr;
   const uint32_t* tab;     // K schedule tables (see PconvTab)
   int tab_words;
+  int direct_store;        // epilogue stores straight from the row-owning lanes instead of through the staging tile
   int dbg;                 // tuning aid: 1 = no stores, 2 = no residual loads, 4 = TMEM loads only
   long long* ts;           // optional timeline of CTA 0 (8 stamps per tile, first 16 tiles), or null
 };
@@ -536,15 +622,16 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   float* s_scale = reinterpret_cast<float*>(sm + tail);
   float* s_shift = s_scale + 256;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 2048);
-  const uint32_t bar_pfull = smem_u32(bars);          // [2]
-  const uint32_t bar_pempty = bar_pfull + 16;         // [2]
-  const uint32_t bar_tfull = bar_pfull + 32;          // [2]
-  const uint32_t bar_tempty = bar_pfull + 48;         // [2]
-  const uint32_t bar_wfull = bar_pfull + 64;          // [w_stages] (resident: [0] only)
+  const uint32_t bar_pfull = smem_u32(bars);          // [4]
+  const uint32_t bar_pempty = bar_pfull + 32;         // [4]
+  const uint32_t bar_tfull = bar_pfull + 64;          // [2]
+  const uint32_t bar_tempty = bar_pfull + 80;         // [2]
+  const uint32_t bar_wfull = bar_pfull + 96;          // [w_stages] (resident: [0] only)
   const uint32_t bar_wempty = bar_wfull + 8 * 32;     // [w_stages]
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8 + 64);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 12 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint32_t* s_tab = s_tmem + 4;
+  uint8_t* s_stage = sm + tail + 5120 + (threadIdx.x >> 5) * 2048;  // per-warp staging tile of the epilogue (warps 2..9 use it)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < p.tab_words; i += kPconvThreads) s_tab[i] = p.tab[i];
@@ -555,9 +642,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
   }
   if (threadIdx.x == 0) {
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       mbar_init(bar_pfull + 8 * a, 1);
       mbar_init(bar_pempty + 8 * a, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 8);
     }
@@ -587,7 +676,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     // one unit = the patch rows of one channel-block group; with a single group the unit serves all N
     // tiles of the M tile, otherwise the groups are streamed again for every N tile
     if (lane == 0) {
-      int it = 0, uc = 0;
+      int it = 0, buf = 0;
+      uint32_t ph = 0;
       bool ok = true;
       const int units = p.groups == 1 ? 1 : p.n_tiles * p.groups;
       for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
@@ -595,10 +685,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const int vr0 = (int)(q0 / p.P);
         const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
-        for (int u = 0; u < units && ok; ++u, ++uc) {
+        for (int u = 0; u < units && ok; ++u) {
           const int g = p.groups == 1 ? 0 : u % p.groups;
-          const int buf = p.patch_bufs == 2 ? (uc & 1) : 0;
-          const uint32_t ph = (uint32_t)(p.patch_bufs == 2 ? (uc >> 1) : uc) & 1u;
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
           mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
@@ -608,6 +696,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
             if (++yy == p.RP) { yy = 0; ++n; }
           }
+          if (++buf == p.patch_bufs) { buf = 0; ph ^= 1u; }
         }
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
         // the patch two tiles ahead: towards L2 now, so that its load later is an L2 hit
@@ -654,8 +743,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
       bool ok = true;
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
-      int it = 0, cnt = 0, stage = 0, uc = 0;
-      uint32_t wphase = 0;
+      int it = 0, cnt = 0, stage = 0, buf = 0;
+      uint32_t wphase = 0, pph = 0;
       for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
         const long long q0 = (long long)m_tile * kM;
         const int off0 = (int)(q0 - (q0 / p.P) * p.P);
@@ -672,9 +761,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           for (int g = 0; g < p.groups && ok; ++g) {
             // the patch unit of this group: a new one per (N tile, group), or the M tile's only one
             const bool fresh = p.groups > 1 || n_tile == 0;
-            const int buf = p.patch_bufs == 2 ? (uc & 1) : 0;
             if (fresh) {
-              if (!mbar_wait_bounded(bar_pfull + 8 * buf, (uint32_t)(p.patch_bufs == 2 ? (uc >> 1) : uc) & 1u, s_abort, p.gerr, 502)) { ok = false; break; }
+              if (!mbar_wait_bounded(bar_pfull + 8 * buf, pph, s_abort, p.gerr, 502)) { ok = false; break; }
               if (p.ts && blockIdx.x == 0 && it < 16 && n_tile == 0 && g == 0) p.ts[it * 8 + 3] = clock64();
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
@@ -705,7 +793,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             // the unit may be overwritten once these MMAs have read it
             if (ok && (p.groups > 1 || n_tile == p.n_tiles - 1)) {
               umma_commit(bar_pempty + 8 * buf);
-              ++uc;
+              if (++buf == p.patch_bufs) { buf = 0; pph ^= 1u; }
             }
           }
           if (ok) umma_commit(bar_tfull + 8 * acc);
@@ -768,8 +856,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           if (p.dbg & 1) yrow = sg.y + (size_t)(threadIdx.x & 31) * sg.channels;  // tuning aid: every tile stores to the same 32 rows
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
-  if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
-  else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid)
+  if (p.direct_store) {                                                                                                        \
+    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
+    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);      \
+  } else if (rrow) epi_fused_cols32_t<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane);  \
+  else epi_fused_cols32_t<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane)
           switch (sg.act) {
             case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
             case AIG_ACT_SWISH: AIG_EPI(AIG_ACT_SWISH); break;
@@ -1082,7 +1173,7 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
 
 
 // ---- patch-resident path: host side ------------------------------------------------------
-constexpr int kPconvTail = 2048 /*scale,shift*/ + 1024 /*barriers*/ + 2560 /*K schedule tables*/;
+constexpr int kPconvTail = 5120 /*scale,shift, barriers, K schedule tables*/ + 12 * 2048 /*epilogue staging, one tile per warp slot*/;
 constexpr int kPconvBudget = 227 * 1024 - 1024 /*align*/ - kPconvTail;
 
 template <int NT, int MS, bool WRES>
@@ -1160,17 +1251,17 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
     if (ms_top * NT > 512) continue;
     while (!f_ms && ms_top > 1 && ceil_div_ll(total_q, ms_top * kTileM) < ctx->sm_count) ms_top /= 2;
     // resident weights beside two whole patches (then one), largest tile first
-    for (int pb = 2; pb >= 1 && best < 0; --pb) {
+    for (int pb = (f_pb ? f_pb : 2); pb >= 2 && best < 0; --pb) {
       if (f_pb && pb != f_pb) continue;
       if (f_g && f_g != q.cblocks) continue;
       for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
         const long long patch = (long long)vrows_of(ms * kTileM) * q.P * 128 * q.cblocks;
-        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget && pb == 2) take(o, ms, pb, q.cblocks, true, dense_kb);
+        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget) take(o, ms, pb, q.cblocks, true, dense_kb);
         if (ms == 1) break;
       }
     }
     // streamed weights: two patch units of the largest channel-block group that leaves two stages
-    for (int pb = 2; pb >= 1 && best < 0; --pb) {
+    for (int pb = (f_pb > 2 ? f_pb : 2); pb >= 1 && best < 0; --pb) {
       if (f_pb && pb != f_pb) continue;
       for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
         const long long region = (long long)vrows_of(ms * kTileM) * q.P * 128;
@@ -1199,6 +1290,9 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   q.w_stages = best_stages;
   q.acc_bufs = best_acc;
   q.m_tiles = (int)ceil_div_ll(total_q, M);
+  // N = 64 tiles saturate shared-memory bandwidth with operand reads (6 KB per 49-clk MMA); the staging
+  // tile of the coalescing epilogue costs more there than the scattered stores it saves
+  q.direct_store = NT == 64 ? 1 : 0;
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
@@ -1325,6 +1419,8 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   if (rc == AIG_OK) rc = encode_Bp(pl);
   if (rc != AIG_OK) return rc;
   if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
+  if (q.dbg & 32) q.acc_bufs = 1;
+  if (q.dbg & 64) q.direct_store = 1;
   const char* ts = getenv("AIG_PCONV_TS");
   if (ts && atoi(ts)) {
     AIG_CUDA_OK(ctx, cudaMalloc(&q.ts, 128 * sizeof(long long)));
@@ -1598,6 +1694,7 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
   }
   if (n_opts == 0 || !pconv_choose_tile(ctx, pl, opts, n_opts, 2)) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: no tile fits shared memory"));
   if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
+  if (q.dbg & 64) q.direct_store = 1;
   if (const char* ts = getenv("AIG_PCONV_TS")) {
     if (atoi(ts) && cudaMalloc(&q.ts, 128 * sizeof(long long)) == cudaSuccess) cudaMemset(q.ts, 0, 128 * sizeof(long long));
   }
