@@ -243,6 +243,231 @@ __global__ void pack_wimg_kernel(const __half* __restrict__ w, __half* __restric
   }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// 2-D BGRA frames: the same GEMM with the gather done through a shared-memory patch.  A tile is a
+// block of 8 x 16 output pixels; its input patch ((8-1)*s + k rows, (16-1)*s + k columns) is read
+// once with coalesced 4-byte loads, each pixel converted once to four halfs (R, G, B, 0), and every
+// producer thread then assembles its im2col row from 8-byte shared-memory reads -- no per-tap
+// conversion, bounds check or address arithmetic on global memory.  K index = tap*4 + channel (the
+// fourth channel's weights are zero), 100 for 5x5, still two 64-element K blocks.
+constexpr int kBH = 8, kBW = 16;
+constexpr int kPatchMax = 19 * 35;  // pixels: 5x5 taps at stride 2
+
+template <int KHW>
+__global__ void __launch_bounds__(kThreads, 2)
+conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y, const uint4* __restrict__ wimg, const TcParams p) {
+  constexpr int TAPS = KHW * KHW;
+  constexpr int KTOT = 4 * TAPS;
+  constexpr int NCH = (KTOT + 7) / 8;
+  constexpr int KSTEPS = (KTOT + 15) / 16;
+  static_assert(KTOT <= 128, "filter too large for the single-tile K");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  uint8_t* sA = sm;
+  uint8_t* sB = sA + 2 * kABytes;
+  float* s_scale = reinterpret_cast<float*>(sB + 2 * p.NT * 128);
+  float* s_shift = s_scale + 256;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_shift + 256);
+  const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 16, bar_tfull = bar_afull + 32, bar_tempty = bar_afull + 48;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  uint2* s_patch = reinterpret_cast<uint2*>(bars + 16);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const ConvFirstGeom& g = p.g;
+  const int blocks_x = (g.Wo + kBW - 1) / kBW, blocks_y = (g.Ho + kBH - 1) / kBH;
+  const int tiles = g.batch * blocks_y * blocks_x;
+  const int PH = (kBH - 1) * g.s + KHW, PW = (kBW - 1) * g.s + KHW;
+
+  for (int i = threadIdx.x; i < 2 * kABytes / 16; i += kThreads) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < 2 * p.NT * 128 / 16; i += kThreads) reinterpret_cast<uint4*>(sB)[i] = wimg[i];
+  for (int i = threadIdx.x; i < p.NT; i += kThreads) {
+    s_scale[i] = p.scale[i];
+    s_shift[i] = p.shift[i];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_afull + 8 * s, kRows);
+      mbar_init(bar_aempty + 8 * s, 1);
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);
+    }
+    *s_abort = 0;
+    fence_mbar_init();
+  }
+  const uint32_t tmem_cols = 2 * p.NT <= 32 ? 32 : (2 * p.NT <= 64 ? 64 : (2 * p.NT <= 128 ? 128 : (2 * p.NT <= 256 ? 256 : 512)));
+  if (warp == 8) {
+    tmem_alloc(smem_u32(s_tmem), tmem_cols);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ producers
+    const int r = threadIdx.x;
+    const int oy = r / kBW, ox = r - oy * kBW;
+    const int pbase = oy * g.s * PW + ox * g.s;
+    int it = 0;
+    bool ok = true;
+    constexpr int kPix = (kPatchMax + kRows - 1) / kRows;  // patch pixels per producer thread
+    uint32_t nxt[kPix];
+    // the pixels of a tile's patch this thread converts, loaded one tile ahead so that their latency
+    // hides behind the row assembly of the current tile
+    auto load_patch = [&](int tile) {
+      const int bx = tile % blocks_x, t2 = tile / blocks_x;
+      const int by = t2 % blocks_y, n = t2 / blocks_y;
+      const int ih0 = by * kBH * g.s - g.pad, iw0 = bx * kBW * g.s - g.pad;
+      const uint32_t* img = xin + (size_t)n * g.H * g.W;
+#pragma unroll
+      for (int k = 0; k < kPix; ++k) {
+        const int i = r + k * kRows;
+        const int py = i / PW, px = i - py * PW;
+        const int ih = ih0 + py, iw = iw0 + px;
+        nxt[k] = (i < PH * PW && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? __ldg(img + (size_t)ih * g.W + iw) : 0u;
+      }
+    };
+    if ((int)blockIdx.x < tiles) load_patch(blockIdx.x);
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+      // every producer is done reading the previous tile's patch
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+      for (int k = 0; k < kPix; ++k) {
+        const int i = r + k * kRows;
+        if (i < PH * PW) {
+          // bytes B,G,R,A; channels of the network are R,G,B; half(float(u8)/255) == half(float(u8)*(1/255)) for all bytes
+          const float k255 = 1.0f / 255.0f;
+          const uint32_t pxl = nxt[k];
+          const __half2 rg = __floats2half2_rn((float)((pxl >> 16) & 0xFFu) * k255, (float)((pxl >> 8) & 0xFFu) * k255);
+          const __half2 b0 = __floats2half2_rn((float)(pxl & 0xFFu) * k255, 0.f);
+          s_patch[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&rg), *reinterpret_cast<const uint32_t*>(&b0));
+        }
+      }
+      if (tile + (int)gridDim.x < tiles) load_patch(tile + gridDim.x);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!ok) continue;  // keep arriving at the producers' barrier; the other roles have drained
+      if (!mbar_wait_bounded(bar_aempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 611)) { ok = false; continue; }
+      uint8_t* a = sA + st * kABytes;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int t0 = 2 * j, t1 = 2 * j + 1;
+        const uint2 lo = s_patch[pbase + (t0 / KHW) * PW + (t0 % KHW)];
+        uint2 hi = make_uint2(0u, 0u);
+        if (t1 < TAPS) hi = s_patch[pbase + (t1 / KHW) * PW + (t1 % KHW)];
+        *reinterpret_cast<uint4*>(a + (j >> 3) * (kRows * 128) + swz(r, j & 7)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_afull + 8 * st);
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(kRows, p.NT);
+      int it = 0;
+      for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait_bounded(bar_tempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 612)) break;
+        if (!mbar_wait_bounded(bar_afull + 8 * st, ph, s_abort, p.gerr, 613)) break;
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(sA) + st * kABytes, b0 = smem_u32(sB);
+#pragma unroll
+        for (int i = 0; i < KSTEPS; ++i) {
+          const int kb = i >> 2, k = i & 3;
+          umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
+                      umma_smem_desc(b0 + kb * (p.NT * 128) + k * 32, 128), idesc, i != 0 ? 1u : 0u);
+        }
+        umma_commit(bar_aempty + 8 * st);
+        umma_commit(bar_tfull + 8 * st);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 4..7)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int oy = r / kBW, ox = r - oy * kBW;
+    const bool vec_ok = (g.K & 7) == 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+      const int bx = tile % blocks_x, t2 = tile / blocks_x;
+      const int by = t2 % blocks_y, n = t2 / blocks_y;
+      const int oh = by * kBH + oy, ow = bx * kBW + ox;
+      const bool valid = oh < g.Ho && ow < g.Wo;
+      size_t pix = ((size_t)n * g.Ho + oh) * g.Wo + ow;
+      if (p.s2d) {
+        const int sby = (oh + 1) >> 1, sbx = (ow + 1) >> 1, sp = ((oh + 1) & 1) * 2 + ((ow + 1) & 1);
+        pix = (((size_t)n * p.Hb + sby) * p.Wb + sbx) * 4 + sp;
+      }
+      __half* yrow = y + pix * g.K;
+      if (!mbar_wait_bounded(bar_tfull + 8 * st, ph, s_abort, p.gerr, 614)) break;
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (uint32_t)(st * p.NT) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < p.NT; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld_32x16(t_addr + c0, v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int v8 = 0; v8 < 2; ++v8) {
+            const int n0 = c0 + v8 * 8;
+            if (n0 >= g.K) break;
+            if (vec_ok) {
+              uint4 o;
+              __half* oh8 = reinterpret_cast<__half*>(&o);
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                oh8[e] = __float2half(act_apply_fast(__uint_as_float(v[v8 * 8 + e]) * s_scale[n0 + e] + s_shift[n0 + e], g.act, g.slope));
+              *reinterpret_cast<uint4*>(yrow + n0) = o;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (n0 + e < g.K)
+                  yrow[n0 + e] = __float2half(act_apply_fast(__uint_as_float(v[v8 * 8 + e]) * s_scale[n0 + e] + s_shift[n0 + e], g.act, g.slope));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * st);
+    }
+  }
+
+  if (*s_abort) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// w [K][3][taps] fp16 -> the same shared-memory image with K index = tap*4 + c (c = 3: zero)
+__global__ void pack_wimg4_kernel(const __half* __restrict__ w, __half* __restrict__ img, int K, int NT, int taps) {
+  const int total = 2 * NT * 64;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int kk = i % 128, n = i / 128;
+    const int kb = kk >> 6, kl = kk & 63;
+    __half v = __ushort_as_half((unsigned short)0);
+    const int tap = kk >> 2, c = kk & 3;
+    if (n < K && tap < taps && c < 3) v = w[((size_t)n * 3 + c) * taps + tap];
+    const size_t off = (size_t)kb * NT * 128 + (size_t)n * 128 + (((kl >> 3) ^ (n & 7)) << 4) + (kl & 7) * 2;
+    *reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(img) + off) = v;
+  }
+}
+
 template <int KD, int KHW>
 int launch_tc(ConvFirstTc* t, const void* x, bool bgra, __half* y);
 
@@ -252,9 +477,25 @@ struct ConvFirstTc {
   aig_ctx* ctx = nullptr;
   TcParams prm{};
   __half* wimg = nullptr;
-  size_t smem = 0;
-  int grid = 1;
+  __half* wimg4 = nullptr;   // weight image in the tap*4 + channel K layout of the patch kernel
+  bool patch_ok = false;     // 2-D, stride <= 2, k in {2, 3, 5}: BGRA frames go through the patch kernel
+  size_t smem = 0, smem_patch = 0;
+  int grid = 1, grid_patch = 1;
 };
+
+namespace {
+
+template <int KHW>
+int launch_patch(ConvFirstTc* t, const void* x, __half* y) {
+  aig_ctx* ctx = t->ctx;
+  AIG_CUDA_OK(ctx, cudaFuncSetAttribute(conv_first_patch_kernel<KHW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)t->smem_patch));
+  conv_first_patch_kernel<KHW><<<t->grid_patch, kThreads, t->smem_patch, ctx->stream>>>(reinterpret_cast<const uint32_t*>(x), y,
+                                                                                        reinterpret_cast<const uint4*>(t->wimg4), t->prm);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+}  // namespace
 
 namespace {
 
@@ -294,9 +535,16 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
   t->smem = (size_t)2 * kABytes + (size_t)2 * p.NT * 128 + 2048 + 256 + 1024;
   // two CTAs per SM: the gather of one hides behind the conversion / epilogue work of the other
   t->grid = p.tiles < 2 * ctx->sm_count ? p.tiles : 2 * ctx->sm_count;
-  if (cudaMalloc(&t->wimg, (size_t)2 * p.NT * 128) != cudaSuccess) {
+  if (cudaMalloc(&t->wimg, (size_t)2 * p.NT * 128) != cudaSuccess || cudaMalloc(&t->wimg4, (size_t)2 * p.NT * 128) != cudaSuccess) {
+    cudaFree(t->wimg);
     delete t;
     return aig_fail(ctx, AIG_ERR_CUDA, "conv0: weight image allocation failed");
+  }
+  t->patch_ok = g.kd == 1 && g.D == 1 && g.s <= 2 && (g.k == 2 || g.k == 3 || g.k == 5);
+  if (t->patch_ok) {
+    const long long tiles = (long long)g.batch * ceil_div(g.Ho, kBH) * ceil_div(g.Wo, kBW);
+    t->grid_patch = (int)(tiles < 2 * ctx->sm_count ? tiles : 2 * ctx->sm_count);
+    t->smem_patch = t->smem + (size_t)kPatchMax * 8;
   }
   *out = t;
   return AIG_OK;
@@ -305,6 +553,7 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
 void conv_first_tc_destroy(ConvFirstTc* t) {
   if (!t) return;
   cudaFree(t->wimg);
+  cudaFree(t->wimg4);
   delete t;
 }
 
@@ -313,6 +562,10 @@ int conv_first_tc_set_weights(ConvFirstTc* t, const __half* w) {
   const int taps = t->prm.g.kd * t->prm.g.k * t->prm.g.k;
   pack_wimg_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg, t->prm.g.K, t->prm.NT, taps);
   AIG_LAUNCH_OK(ctx);
+  if (t->patch_ok) {
+    pack_wimg4_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg4, t->prm.g.K, t->prm.NT, taps);
+    AIG_LAUNCH_OK(ctx);
+  }
   return AIG_OK;
 }
 
@@ -326,6 +579,11 @@ int conv_first_tc_set_s2d(ConvFirstTc* t, int enable, int Hb, int Wb) {
 
 int conv_first_tc_forward(ConvFirstTc* t, const void* x, bool bgra, __half* y) {
   const ConvFirstGeom& g = t->prm.g;
+  if (bgra && t->patch_ok) {
+    if (g.k == 5) return launch_patch<5>(t, x, y);
+    if (g.k == 3) return launch_patch<3>(t, x, y);
+    return launch_patch<2>(t, x, y);
+  }
   if (g.kd == 1 && g.k == 5) return launch_tc<1, 5>(t, x, bgra, y);
   if (g.kd == 1 && g.k == 3) return launch_tc<1, 3>(t, x, bgra, y);
   if (g.kd == 1 && g.k == 2) return launch_tc<1, 2>(t, x, bgra, y);

@@ -191,7 +191,9 @@ def test_first_layer_convs(env):
         plan.forward_nchw(U.dev(x), dy)
         c.sync()
         got2 = U.nchw(U.host(dy).reshape(B, want.shape[2], want.shape[3], K))
-        assert np.array_equal(got, got2)
+        assert U.scaled_err(got2, want) < 4e-3
+        # the two entry points order the K dimension differently (different kernels): equal up to fp32 summation order
+        assert np.abs(got.astype(np.float32) - got2.astype(np.float32)).max() <= 2 * np.abs(want).max() * 2.0 ** -10
         plan.close()
     # 3-D first layer
     B, D, H, W, K = 1, 4, 12, 20, 32
