@@ -579,7 +579,6 @@ struct PconvParams {
   const uint32_t* tab;     // K schedule tables (see PconvTab)
   int tab_words;
   int direct_store;        // epilogue stores straight from the row-owning lanes instead of through the staging tile
-  int dbg;                 // tuning aid: 1 = no stores, 2 = no residual loads, 4 = TMEM loads only
   long long* ts;           // optional timeline of CTA 0 (8 stamps per tile, first 16 tiles), or null
 };
 
@@ -701,7 +700,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
         // the patch two tiles ahead: towards L2 now, so that its load later is an L2 hit
         const int ahead = m_tile + 2 * (int)gridDim.x;
-        if (ahead < p.m_tiles && !(p.dbg & 8)) {
+        if (ahead < p.m_tiles) {
           const int avr0 = (int)(((long long)ahead * kM) / p.P);
           int an = avr0 / p.RP, ayy = avr0 - an * p.RP;
           for (int r = 0; r < p.patch_vrows; ++r) {
@@ -844,7 +843,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const long long q = (long long)m_tile * kM + sub * kTileM + row_in_tile;
           const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
           const int n = vr / p.RP, yy = vr - n * p.RP;
-          const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo && !(p.dbg & 4);
+          const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
           const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
           size_t opix = pix;
           if (sg.s2d) {
@@ -852,8 +851,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             opix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
           }
           __half* yrow = sg.y + opix * sg.channels;
-          const __half* rrow = (sg.residual && !(p.dbg & 2)) ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
-          if (p.dbg & 1) yrow = sg.y + (size_t)(threadIdx.x & 31) * sg.channels;  // tuning aid: every tile stores to the same 32 rows
+          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
   if (p.direct_store) {                                                                                                        \
@@ -1418,9 +1416,6 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   int rc = pconv_build_tables(ctx, pl);
   if (rc == AIG_OK) rc = encode_Bp(pl);
   if (rc != AIG_OK) return rc;
-  if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
-  if (q.dbg & 32) q.acc_bufs = 1;
-  if (q.dbg & 64) q.direct_store = 1;
   const char* ts = getenv("AIG_PCONV_TS");
   if (ts && atoi(ts)) {
     AIG_CUDA_OK(ctx, cudaMalloc(&q.ts, 128 * sizeof(long long)));
@@ -1693,8 +1688,6 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
     }
   }
   if (n_opts == 0 || !pconv_choose_tile(ctx, pl, opts, n_opts, 2)) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: no tile fits shared memory"));
-  if (const char* dbg = getenv("AIG_PCONV_DBG")) q.dbg = atoi(dbg);
-  if (q.dbg & 64) q.direct_store = 1;
   if (const char* ts = getenv("AIG_PCONV_TS")) {
     if (atoi(ts) && cudaMalloc(&q.ts, 128 * sizeof(long long)) == cudaSuccess) cudaMemset(q.ts, 0, 128 * sizeof(long long));
   }
