@@ -204,16 +204,11 @@ def main():
     enc = pkg.CnnEncoder(ctx, B, HEIGHT, WIDTH, widths=WIDTHS, n_out=N_OUT, n_sigmoid=N_SIG)
 
     # checkpoint: rank 0 builds it, one NCCL broadcast, every rank loads its own copy
+    from ai_gamer_b200 import sharding as SH
+
     nbytes = enc.checkpoint_bytes()
-    if rank == 0:
-        blob = SY.serialize_cnn_checkpoint(SY.make_cnn_params(0, widths=WIDTHS), WIDTH, HEIGHT)
-        assert len(blob) == nbytes
-        t_blob = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
-    else:
-        t_blob = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
-    if world > 1:
-        dist.broadcast(t_blob, 0)
-    enc.load_bytes(t_blob.cpu().numpy().tobytes())
+    blob = SY.serialize_cnn_checkpoint(SY.make_cnn_params(0, widths=WIDTHS), WIDTH, HEIGHT) if rank == 0 else None
+    enc.load_bytes(SH.broadcast_bytes(blob, nbytes, 0, "cuda"))
 
     # inputs: rotate over enough frame batches to exceed the 126 MB L2
     n_rot = max(2, -(-150_000_000 // (B * HEIGHT * WIDTH * 4)))
@@ -268,10 +263,7 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    ms, e2e_ms = SH.max_over_ranks([ms, e2e_s * 1e3], "cuda")
 
     latency = None
     if rank == 0 and not args.no_latency:

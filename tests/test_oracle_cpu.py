@@ -3,6 +3,7 @@ reference arithmetic is fully specified and (b) against PyTorch's CPU fp32/fp64 
 ones the reference delegates to cuDNN/cuBLAS (convolution conventions, BatchNorm, GEMM orientation,
 LSTM gate order, attention).  No GPU needed."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -252,3 +253,46 @@ def test_cnn_pipeline_small_runs_and_is_deterministic():
     assert f1.shape == (2, 16) and o1.shape == (2, 18)
     assert np.array_equal(o1, o2) and np.isfinite(o1.astype(np.float32)).all()
     assert (o1[:, :16] >= 0).all() and (o1[:, :16] <= 1).all() and (np.abs(o1[:, 16:].astype(np.float32)) <= 1).all()
+
+
+# ----------------------------------------------------------------------------- pinned to the reference
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_kernels.npz")
+
+
+def _ulp_diff(a_u16, b_u16):
+    """fp16 distance in units of the last place (sign-magnitude bit patterns mapped to a monotone integer line)."""
+    def key(u):
+        u = u.astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u & 0x7FFF)
+    return np.abs(key(a_u16) - key(b_u16))
+
+
+def test_oracle_matches_outputs_of_the_reference_kernels():
+    """tests/golden/reference_kernels.npz holds outputs of the reference's own CUDA kernels (CudaStuff.cu,
+    run on a B200 by tests/golden/make_reference_golden.py).  Byte work and the projections must be
+    bit-exact; results that pass through expf / rsqrtf may differ in the last fp16 place."""
+    g = np.load(GOLDEN)
+    n = g["pre_planar"].size // 3
+    planar = O.bgra_to_planar(g["pre_bgra"], n)
+    assert np.array_equal(planar, g["pre_planar"])                                   # CudaStuff.cu:63-74
+    assert np.array_equal(O.convert_normalize(planar).view(np.uint16), g["pre_half"])  # CudaStuff.cu:150-153, all 256 byte values
+    x = g["act_x"].view(np.float16)
+    assert np.array_equal(O.leaky_relu(x, 0.01).view(np.uint16), g["act_leaky"])     # CudaStuff.cu:400-405
+    for name, got in (("act_swish", O.swish(x)), ("act_sigmoid", O.sigmoid_head(x, 16, 14))):
+        d = _ulp_diff(got.view(np.uint16), g[name])
+        assert d.max() <= 1 and (d == 0).mean() > 0.995, name
+    B, inC, attC, H, W = (int(v) for v in g["sa_dims"])
+    sa = O.spatial_attention_ref(g["sa_x"].view(np.float16), g["sa_wk"].view(np.float16), g["sa_wq"].view(np.float16),
+                                 g["sa_wv"].view(np.float16), B, inC, attC, H, W, 64)
+    for key, name in (("keyMap", "sa_key"), ("queryMap", "sa_query"), ("valueMap", "sa_value")):
+        assert np.array_equal(sa[key].reshape(-1).view(np.uint16), g[name]), name      # CudaStuff.cu:673-700
+    for key, name in (("scores", "sa_scores"), ("out", "sa_out")):
+        d = _ulp_diff(sa[key].reshape(-1).view(np.uint16), g[name])
+        assert d.max() <= 1 and (d == 0).mean() > 0.97, name
+    N, C, HW = (int(v) for v in g["ln_dims"])
+    y, mean, var = O.layernorm_ref(g["ln_x"].view(np.float16), g["ln_gamma"], g["ln_beta"], N, C, HW, 1e-7)
+    np.testing.assert_allclose(mean, g["ln_mean"], rtol=2e-5, atol=2e-6)               # CudaStuff.cu:457-515
+    np.testing.assert_allclose(var, g["ln_var"], rtol=2e-5, atol=1e-7)
+    d = _ulp_diff(y.reshape(-1).view(np.uint16), g["ln_y"].reshape(-1))
+    big = np.abs(y.reshape(-1).astype(np.float32)) > 2e-3
+    assert d[big].max() <= 2 and (d == 0).mean() > 0.97
