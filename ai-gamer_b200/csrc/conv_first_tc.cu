@@ -275,6 +275,7 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint2* s_patch = reinterpret_cast<uint2*>(bars + 16);
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_patch + kPatchMax + 1);  // 4 x 2 KB, one tile per epilogue warp (16-byte aligned)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const ConvFirstGeom& g = p.g;
   const int blocks_x = (g.Wo + kBW - 1) / kBW, blocks_y = (g.Ho + kBH - 1) / kBH;
@@ -319,6 +320,14 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
     uint32_t nxt[kPix];
     // the pixels of a tile's patch this thread converts, loaded one tile ahead so that their latency
     // hides behind the row assembly of the current tile
+    // this thread's patch pixels never change place inside the patch: (row, column) once, not per tile
+    int ppy[kPix], ppx[kPix];
+#pragma unroll
+    for (int k = 0; k < kPix; ++k) {
+      const int i = r + k * kRows;
+      ppy[k] = i < PH * PW ? i / PW : -(1 << 20);  // past the end of the patch: always out of the image
+      ppx[k] = i - (i / PW) * PW;
+    }
     auto load_patch = [&](int tile) {
       const int bx = tile % blocks_x, t2 = tile / blocks_x;
       const int by = t2 % blocks_y, n = t2 / blocks_y;
@@ -326,10 +335,8 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
       const uint32_t* img = xin + (size_t)n * g.H * g.W;
 #pragma unroll
       for (int k = 0; k < kPix; ++k) {
-        const int i = r + k * kRows;
-        const int py = i / PW, px = i - py * PW;
-        const int ih = ih0 + py, iw = iw0 + px;
-        nxt[k] = (i < PH * PW && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? __ldg(img + (size_t)ih * g.W + iw) : 0u;
+        const int ih = ih0 + ppy[k], iw = iw0 + ppx[k];
+        nxt[k] = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? __ldg(img + (size_t)ih * g.W + iw) : 0u;
       }
     };
     if ((int)blockIdx.x < tiles) load_patch(blockIdx.x);
@@ -411,6 +418,54 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
       if (!mbar_wait_bounded(bar_tfull + 8 * st, ph, s_abort, p.gerr, 614)) break;
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (uint32_t)(st * p.NT) + ((uint32_t)(q * 32) << 16);
+      if (g.K == 32) {
+        // 32 channels = 64 bytes per pixel: the warp's 32 rows pass through a 2 KB staging tile (16-byte
+        // chunks XOR-swizzled, conflict free both ways) and leave as 8 pixels x 64 contiguous bytes per
+        // store instruction instead of 32 scattered 16-byte pieces
+        uint8_t* stg = s_stage + q * 2048;
+        const int gr = lane >> 2, gc = lane & 3, own = lane * 64, swzl = (lane >> 1) & 3;
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr, v);
+        __half* yp[4];
+        bool vj[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          yp[j] = reinterpret_cast<__half*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(yrow), 8 * j + gr));
+          vj[j] = __shfl_sync(0xffffffffu, valid ? 1 : 0, 8 * j + gr) != 0;
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int v8 = 0; v8 < 4; ++v8) {
+          const int n0 = v8 * 8;
+          const float4 s0 = reinterpret_cast<const float4*>(s_scale + n0)[0], s1 = reinterpret_cast<const float4*>(s_scale + n0)[1];
+          const float4 h0 = reinterpret_cast<const float4*>(s_shift + n0)[0], h1 = reinterpret_cast<const float4*>(s_shift + n0)[1];
+          const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+          float a[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) a[e] = fmaf(__uint_as_float(v[v8 * 8 + e]), sv[e], hv[e]);
+          if (g.act == AIG_ACT_SWISH) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = act_apply_fast(a[e], AIG_ACT_SWISH, 0.f);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = act_apply_fast(a[e], g.act, g.slope);
+          }
+          uint4 o;
+          __half2* oh2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+          for (int e2 = 0; e2 < 4; ++e2) oh2[e2] = __floats2half2_rn(a[2 * e2], a[2 * e2 + 1]);
+          *reinterpret_cast<uint4*>(stg + own + ((v8 ^ swzl) << 4)) = o;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int row = 8 * j + gr;
+          const uint4 o = *reinterpret_cast<const uint4*>(stg + row * 64 + ((gc ^ ((row >> 1) & 3)) << 4));
+          if (vj[j]) *reinterpret_cast<uint4*>(yp[j] + gc * 8) = o;
+        }
+        __syncwarp();
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < p.NT; c0 += 16) {
         uint32_t v[16];
@@ -422,11 +477,24 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
             const int n0 = c0 + v8 * 8;
             if (n0 >= g.K) break;
             if (vec_ok) {
-              uint4 o;
-              __half* oh8 = reinterpret_cast<__half*>(&o);
+              const float4 s0 = reinterpret_cast<const float4*>(s_scale + n0)[0], s1 = reinterpret_cast<const float4*>(s_scale + n0)[1];
+              const float4 h0 = reinterpret_cast<const float4*>(s_shift + n0)[0], h1 = reinterpret_cast<const float4*>(s_shift + n0)[1];
+              const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+              const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+              float a[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e)
-                oh8[e] = __float2half(act_apply_fast(__uint_as_float(v[v8 * 8 + e]) * s_scale[n0 + e] + s_shift[n0 + e], g.act, g.slope));
+              for (int e = 0; e < 8; ++e) a[e] = fmaf(__uint_as_float(v[v8 * 8 + e]), sv[e], hv[e]);
+              if (g.act == AIG_ACT_SWISH) {  // the activation of the frame encoder: no per-element dispatch
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = act_apply_fast(a[e], AIG_ACT_SWISH, 0.f);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a[e] = act_apply_fast(a[e], g.act, g.slope);
+              }
+              uint4 o;
+              __half2* oh2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+              for (int e2 = 0; e2 < 4; ++e2) oh2[e2] = __floats2half2_rn(a[2 * e2], a[2 * e2 + 1]);
               *reinterpret_cast<uint4*>(yrow + n0) = o;
             } else {
 #pragma unroll
@@ -544,7 +612,7 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
   if (t->patch_ok) {
     const long long tiles = (long long)g.batch * ceil_div(g.Ho, kBH) * ceil_div(g.Wo, kBW);
     t->grid_patch = (int)(tiles < 2 * ctx->sm_count ? tiles : 2 * ctx->sm_count);
-    t->smem_patch = t->smem + (size_t)kPatchMax * 8;
+    t->smem_patch = t->smem + (size_t)(kPatchMax + 1) * 8 + 4 * 2048;
   }
   *out = t;
   return AIG_OK;
