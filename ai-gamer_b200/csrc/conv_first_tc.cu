@@ -252,16 +252,19 @@ __global__ void pack_wimg_kernel(const __half* __restrict__ w, __half* __restric
 // conversion, bounds check or address arithmetic on global memory.  K index = tap*4 + channel (the
 // fourth channel's weights are zero), 100 for 5x5, still two 64-element K blocks.
 constexpr int kBH = 8, kBW = 16;
-constexpr int kPatchMax = 19 * 35;  // pixels: 5x5 taps at stride 2
+constexpr int kPatchMax = 19 * 36;  // pixels: 5x5 taps at stride 2, rows padded to an even length
 
 template <int KHW>
 __global__ void __launch_bounds__(kThreads, 2)
 conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y, const uint4* __restrict__ wimg, const TcParams p) {
-  constexpr int TAPS = KHW * KHW;
-  constexpr int KTOT = 4 * TAPS;
-  constexpr int NCH = (KTOT + 7) / 8;
+  // K order: filter row, then pairs of adjacent taps (two pixels = one 16-byte chunk; an odd last tap is
+  // padded with zeros), then channel: k = ((fr*CPR + fs/2)*2 + (fs&1))*4 + c
+  constexpr int CPR = (KHW + 1) / 2;      // 16-byte chunks per filter row
+  constexpr int NCH = KHW * CPR;
+  constexpr int KTOT = NCH * 8;
   constexpr int KSTEPS = (KTOT + 15) / 16;
   static_assert(KTOT <= 128, "filter too large for the single-tile K");
+  static_assert((kPatchMax & 1) == 0, "the staging tiles behind the patch must stay 16-byte aligned");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -275,12 +278,13 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint2* s_patch = reinterpret_cast<uint2*>(bars + 16);
-  uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_patch + kPatchMax + 1);  // 4 x 2 KB, one tile per epilogue warp (16-byte aligned)
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_patch + kPatchMax);  // 4 x 2 KB, one tile per epilogue warp (16-byte aligned)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const ConvFirstGeom& g = p.g;
   const int blocks_x = (g.Wo + kBW - 1) / kBW, blocks_y = (g.Ho + kBH - 1) / kBH;
   const int tiles = g.batch * blocks_y * blocks_x;
-  const int PH = (kBH - 1) * g.s + KHW, PW = (kBW - 1) * g.s + KHW;
+  // patch rows are an even number of pixels long so that every row starts on a 16-byte boundary
+  const int PH = (kBH - 1) * g.s + KHW, PW = ((kBW - 1) * g.s + KHW + 1) & ~1;
 
   for (int i = threadIdx.x; i < 2 * kABytes / 16; i += kThreads) reinterpret_cast<uint4*>(sA)[i] = make_uint4(0, 0, 0, 0);
   for (int i = threadIdx.x; i < 2 * p.NT * 128 / 16; i += kThreads) reinterpret_cast<uint4*>(sB)[i] = wimg[i];
@@ -362,13 +366,24 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
       if (!ok) continue;  // keep arriving at the producers' barrier; the other roles have drained
       if (!mbar_wait_bounded(bar_aempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 611)) { ok = false; continue; }
       uint8_t* a = sA + st * kABytes;
+      const bool pair_ok = (g.s & 1) == 0;  // even stride: every tap pair of this pixel starts on a 16-byte boundary
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
-        const int t0 = 2 * j, t1 = 2 * j + 1;
-        const uint2 lo = s_patch[pbase + (t0 / KHW) * PW + (t0 % KHW)];
-        uint2 hi = make_uint2(0u, 0u);
-        if (t1 < TAPS) hi = s_patch[pbase + (t1 / KHW) * PW + (t1 % KHW)];
-        *reinterpret_cast<uint4*>(a + (j >> 3) * (kRows * 128) + swz(r, j & 7)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        const int fr = j / CPR, f0 = 2 * (j % CPR);
+        const uint2* src = s_patch + pbase + fr * PW + f0;
+        uint4 ch;
+        if (f0 + 1 < KHW) {
+          if (pair_ok) {
+            ch = *reinterpret_cast<const uint4*>(src);
+          } else {
+            const uint2 lo = src[0], hi = src[1];
+            ch = make_uint4(lo.x, lo.y, hi.x, hi.y);
+          }
+        } else {
+          const uint2 lo = src[0];
+          ch = make_uint4(lo.x, lo.y, 0u, 0u);
+        }
+        *reinterpret_cast<uint4*>(a + (j >> 3) * (kRows * 128) + swz(r, j & 7)) = ch;
       }
       fence_proxy_async_smem();
       mbar_arrive(bar_afull + 8 * st);
@@ -522,15 +537,18 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
   }
 }
 
-// w [K][3][taps] fp16 -> the same shared-memory image with K index = tap*4 + c (c = 3: zero)
-__global__ void pack_wimg4_kernel(const __half* __restrict__ w, __half* __restrict__ img, int K, int NT, int taps) {
+// w [K][3][k*k] fp16 -> the same shared-memory image in the patch kernel's K order:
+// kk = ((fr*CPR + fs/2)*2 + (fs&1))*4 + c with CPR = (k+1)/2; c = 3 and the pad tap of an odd k stay zero
+__global__ void pack_wimg4_kernel(const __half* __restrict__ w, __half* __restrict__ img, int K, int NT, int k) {
   const int total = 2 * NT * 64;
+  const int cpr = (k + 1) / 2;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int kk = i % 128, n = i / 128;
     const int kb = kk >> 6, kl = kk & 63;
     __half v = __ushort_as_half((unsigned short)0);
-    const int tap = kk >> 2, c = kk & 3;
-    if (n < K && tap < taps && c < 3) v = w[((size_t)n * 3 + c) * taps + tap];
+    const int c = kk & 3, half_tap = (kk >> 2) & 1, chunk = kk >> 3;
+    const int fr = chunk / cpr, fs = 2 * (chunk % cpr) + half_tap;
+    if (n < K && fr < k && fs < k && c < 3) v = w[((size_t)n * 3 + c) * k * k + fr * k + fs];
     const size_t off = (size_t)kb * NT * 128 + (size_t)n * 128 + (((kl >> 3) ^ (n & 7)) << 4) + (kl & 7) * 2;
     *reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(img) + off) = v;
   }
@@ -612,7 +630,7 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
   if (t->patch_ok) {
     const long long tiles = (long long)g.batch * ceil_div(g.Ho, kBH) * ceil_div(g.Wo, kBW);
     t->grid_patch = (int)(tiles < 2 * ctx->sm_count ? tiles : 2 * ctx->sm_count);
-    t->smem_patch = t->smem + (size_t)(kPatchMax + 1) * 8 + 4 * 2048;
+    t->smem_patch = t->smem + (size_t)kPatchMax * 8 + 4 * 2048;
   }
   *out = t;
   return AIG_OK;
@@ -631,7 +649,7 @@ int conv_first_tc_set_weights(ConvFirstTc* t, const __half* w) {
   pack_wimg_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg, t->prm.g.K, t->prm.NT, taps);
   AIG_LAUNCH_OK(ctx);
   if (t->patch_ok) {
-    pack_wimg4_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg4, t->prm.g.K, t->prm.NT, taps);
+    pack_wimg4_kernel<<<ceil_div(2 * t->prm.NT * 64, 256), 256, 0, ctx->stream>>>(w, t->wimg4, t->prm.g.K, t->prm.NT, t->prm.g.k);
     AIG_LAUNCH_OK(ctx);
   }
   return AIG_OK;
