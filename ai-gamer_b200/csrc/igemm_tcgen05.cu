@@ -9,10 +9,11 @@
 //     output pixels of one output row (tw*segs = 128); each run is one TMA box (BK channels x tw
 //     pixels, element stride = conv stride) whose out-of-range pixels (padding) are zero-filled by TMA.
 //   B (N x K): weights repacked once to [out_c][tap][in_c] (K-major), one TMA box per K block.
-// A CTA tile is MS sub-tiles of 128 rows that share every weight block: operand traffic from L2, not
-// the tensor pipe, bounds these layers (measured ~22 B/clk/SM), the weight block is up to 2/3 of a
-// stage, and a tcgen05.mma costs the same ~200 clk for N = 64 as for N = 256, so sub-tiles are added
-// until the MS accumulators fill the 256 TMEM columns of one buffer.
+// A CTA tile is MS sub-tiles of 128 rows that share every weight block: operand traffic into shared
+// memory, not the tensor pipe, bounds these layers, and the weight block is up to 2/3 of a stage, so
+// sub-tiles are added until the MS accumulators fill the 256 TMEM columns of one buffer.
+// Stride-1 2-D layers and the fused down-sampling pair of a residual block take the patch-resident
+// kernel further down (pconv_kernel), which loads each activation patch once for all filter taps.
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
 // warps 2..9 = epilogue.  Persistent: grid = min(tiles, SMs), static tile striding.
 // Every mbarrier wait is bounded; on expiry the CTA raises the context's device error word and all

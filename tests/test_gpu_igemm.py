@@ -173,7 +173,9 @@ def test_first_layer_convs(env):
     # 2-D, from BGRA bytes (fused preprocessing) and from planar fp16
     # k = 5, 2, 3 run on the tensor-core gather kernel; k = 4 has no instantiation and takes the CUDA-core kernel
     for (B, H, W, K, k, s, p) in [(2, 144, 256, 32, 5, 2, 2), (3, 17, 23, 32, 2, 2, 0), (1, 20, 31, 40, 3, 1, 1),
-                                  (2, 18, 22, 32, 4, 2, 1), (1, 33, 47, 18, 5, 2, 2)]:
+                                  (2, 18, 22, 32, 4, 2, 1), (1, 33, 47, 18, 5, 2, 2),
+                                  # wide rows, partial 16-pixel blocks at the right edge, k = 3 and k = 2 at stride 2
+                                  (2, 40, 300, 32, 5, 2, 2), (1, 31, 200, 32, 3, 2, 1), (1, 32, 256, 32, 2, 2, 0), (3, 21, 131, 32, 5, 2, 2)]:
         frames = PL.make_frames(5, B, H, W)
         w = PL.he_normal(RNG, (K, 3, k, k))
         b = h(RNG.uniform(-0.2, 0.2, K))
