@@ -98,6 +98,23 @@ SIGNATURES = {
     "aig_resdown_plan_set_weights": [P, P, P, P, P, P, P, c_float, P, P],
     "aig_resdown_forward": [P, P, P, P],
     "aig_actions_from_outputs": [P, P, c_int, c_int, c_int],
+    # include/aig_compat.h: the reference's launcher names (no context argument; most return void)
+    "InitCUDA": [],
+    "ConvertAndNormalize": [P, P, c_size_t],
+    "UnConvertAndUnNormalize": [P, P, c_size_t],
+    "ConvertFloatToHalf": [P, P, c_size_t],
+    "ConvertHalfToFloat": [P, P, c_size_t],
+    "HeInit": [P, c_int, c_float],
+    "LeakyReluForward": [P, c_int, c_float],
+    "SwishForward": [P, c_int],
+    "SigmoidForward": [P, c_int, c_int, c_int],
+    "LayerNormForward": [P, P, P, P, P, P, c_int, c_int, c_int],
+    "SpatialAttentionForward": [P] * 9 + [c_int] * 5,
+    "ARGBtoRGB": [P, P, c_int],
+    "ARGBtoRGBplanar": [P, P, c_int],
+    "aig_compat_context": [],
+    "aig_compat_last_status": [],
+    "aig_compat_set_attention_group": [c_int],
 }
 AIG_CNN_MAX_BLOCKS = 7
 
@@ -184,7 +201,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_compat_context": c_void_p, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,

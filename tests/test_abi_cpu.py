@@ -27,6 +27,22 @@ def declared_symbols():
     return sorted(set(names))
 
 
+COMPAT_NAMES = ["InitCUDA", "ConvertAndNormalize", "UnConvertAndUnNormalize", "ConvertFloatToHalf", "ConvertHalfToFloat", "HeInit",
+                "LeakyReluForward", "SwishForward", "SigmoidForward", "LayerNormForward", "SpatialAttentionForward", "ARGBtoRGB",
+                "ARGBtoRGBplanar", "aig_compat_context", "aig_compat_last_status", "aig_compat_set_attention_group"]
+
+
+def test_library_exports_the_reference_launcher_names(pkg):
+    """include/aig_compat.h: the forward-path launchers of the reference (common.h:104-139, NvDisplayCap.h:68-69)
+    exist under their own names, and the header declares each of them."""
+    lib = ctypes.CDLL(pkg.LIB_PATH)
+    text = open(os.path.join(ROOT, "include", "aig_compat.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    for n in COMPAT_NAMES:
+        assert re.search(r"\b%s\s*\(" % n, text), n + " not declared"
+        assert hasattr(lib, n), n + " not exported"
+
+
 def test_library_exports_every_declared_symbol(pkg):
     lib = ctypes.CDLL(pkg.LIB_PATH)
     names = declared_symbols()
