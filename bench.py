@@ -58,7 +58,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -170,7 +170,7 @@ def run_reference(args, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=256, help="frames per GPU per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -299,8 +299,8 @@ def main():
             "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": "cnn2d_encoder_144x256_b%d" % B, "frames_per_gpu": B, "global_batch": world * B,
                        "sharding": "batch of independent frames, no step-loop collective",
-                       "l2": "inputs rotate over %d batches (%.0f MB > 126 MB L2); activations ~%.1f GB per step" % (
-                           n_rot, n_rot * B * HEIGHT * WIDTH * 4 / 1e6, B * 5.15e6 / 1e9)},
+                       "l2": "inputs rotate over %d batches (%.0f MB > 126 MB L2); activations written ~%.2f GB per step" % (
+                           n_rot, n_rot * B * HEIGHT * WIDTH * 4 / 1e6, B * 2.19e6 / 1e9)},
             "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": B * HEIGHT * WIDTH * 4,
                     "d2h_bytes_per_step": B * N_OUT * 4, "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": args.steps * enc.kernel_launches,
