@@ -100,3 +100,68 @@ def test_cnn_checkpoint_errors(env):
         enc.forward(torch.zeros(1, dtype=torch.uint8, device="cuda"))  # parameters not loaded
     enc.load_bytes(blob)
     enc.close()
+
+
+@gpu
+def test_full_size_properties(env):
+    """The benchmark's own size (256 frames of 144x256) is beyond what the CPU oracle finishes in seconds, so
+    the full-size run is checked through properties that do not need it: frames are independent (a frame's
+    outputs do not depend on the batch it travels in, up to the fp32 summation order of the tile shape chosen
+    for that batch), the run is deterministic bit for bit, the oracle agrees
+    on a sample of the frames, and the two convolution paths (fused down-sampling over space-to-depth vs the
+    two separate stride-2 convolutions) agree within the fp16 tolerance."""
+    U = env
+    import os
+
+    c = U.ctx()
+    pk = U.pkg()
+    B, H, W = 256, 144, 256
+    widths = (32, 64, 128, 256, 256)
+    params = PL.make_cnn_params(4, widths=widths, trivial=False)
+    blob = PL.serialize_cnn_checkpoint(params, W, H)
+    frames = PL.make_frames(11, B, H, W)
+    enc = pk.CnnEncoder(c, B, H, W, widths=widths)
+    enc.load_bytes(blob)
+    d_frames = U.dev(frames)
+    enc.forward(d_frames)
+    c.sync()
+    full = U.host(enc.outputs_f32()).copy()
+    assert np.isfinite(full).all()
+    enc.forward(d_frames)
+    c.sync()
+    assert np.array_equal(U.host(enc.outputs_f32()), full), "two runs on the same frames differ"
+    enc.close()
+    # the same frames in batches of 8: other tile shapes (channel-block groups are summed in another order),
+    # same values up to a few fp16 ulps; within one batch size the bytes do not depend on the position in the batch
+    small = pk.CnnEncoder(c, 8, H, W, widths=widths)
+    small.load_bytes(blob)
+    for lo in (0, 120, 248):
+        small.forward(U.dev(frames[lo:lo + 8]))
+        c.sync()
+        assert np.abs(U.host(small.outputs_f32()) - full[lo:lo + 8]).max() < 2e-3, "outputs depend on the batch composition"
+    small.forward(U.dev(np.ascontiguousarray(frames[7::-1])))
+    c.sync()
+    rev = U.host(small.outputs_f32()).copy()
+    small.forward(U.dev(frames[0:8]))
+    c.sync()
+    assert np.array_equal(U.host(small.outputs_f32()), rev[::-1]), "a frame's outputs depend on its position in the batch"
+    small.close()
+    # the oracle on three of the 256 frames
+    pick = [0, 131, 255]
+    _, _, want = PL.cnn_forward(params, frames[pick])
+    assert U.rel_err(full[pick], want.astype(np.float32), 0.05).max() < REL_TOL
+    a_got, a_want = O.actions(full[pick], 18, 16), O.actions(want.astype(np.float32), 18, 16)
+    clear = np.abs(want.astype(np.float32)[:, :16] - 0.5) > 2e-3
+    assert (a_got[:, :16] == a_want[:, :16])[clear].all()
+    # the unfused path (two separate stride-2 convolutions per block) on the same frames
+    os.environ["AIG_CNN_NO_FUSED_DOWN"] = "1"
+    try:
+        plain = pk.CnnEncoder(c, B, H, W, widths=widths)
+    finally:
+        del os.environ["AIG_CNN_NO_FUSED_DOWN"]
+    plain.load_bytes(blob)
+    plain.forward(d_frames)
+    c.sync()
+    other = U.host(plain.outputs_f32())
+    plain.close()
+    assert np.abs(other - full).max() < 4e-3   # outputs live in [-1, 1]
