@@ -101,7 +101,8 @@ int aig_agent_load_memory(aig_agent* a, const void* blob, size_t bytes) {
 // One frame per sequence (device BGRA [B][H][W][4]) -> outputs [B][n_out] (aig_agent_outputs_f32).
 int aig_agent_step(aig_agent* a, const uint8_t* bgra_dev) {
   if (!a || !bgra_dev) return AIG_ERR_INVALID;
-  int rc = aig_cnn_forward(a->cnn, bgra_dev);
+  // the encoder's launches replay from a CUDA graph (captured per input buffer on first use)
+  int rc = aig_cnn_forward_graph(a->cnn, bgra_dev);
   if (rc != AIG_OK) return afail(a, rc, aig_cnn_last_error(a->cnn));
   if ((rc = aig_conv_forward(a->bridge, aig_cnn_features(a->cnn), nullptr, a->emb)) != AIG_OK) return afail(a, rc, aig_last_error(a->ctx));
   if ((rc = aig_seq_step(a->seq, a->emb)) != AIG_OK) return afail(a, rc, aig_seq_last_error(a->seq));
