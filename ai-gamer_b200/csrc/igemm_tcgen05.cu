@@ -570,6 +570,7 @@ struct PconvParams {
   int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
   int G, groups;           // 64-channel blocks per patch unit, units per pass over the channels (G * groups == cblocks)
   int n_split;             // GEMM columns >= n_split go to seg[1]
+  int dist_n;              // 1: work items are (M tile, N tile) pairs spread over the CTAs (few M tiles: more CTAs stream weights)
   int sparse_tile0;        // N tiles >= this one use the sparse shortcut K schedule (INT_MAX: none)
   int sub_cblocks;         // 64-channel blocks per space-to-depth sub-position (sparse schedule)
   float slope;
@@ -603,6 +604,21 @@ struct PconvParams {
 //     high 16 bits: weight block index tap*cblocks + cb (K coordinate / 64, and slot of resident weights)
 constexpr int kTabHead = 34;
 constexpr int kTabMaxWords = kTabHead + 2 * 256;
+
+// Work items of a CTA: whole M tiles (all N tiles of one M tile in sequence, sharing its patch), or,
+// when there are too few M tiles to occupy the SMs, single (M tile, N tile) pairs.
+__device__ __forceinline__ int pconv_items(const PconvParams& p) { return p.dist_n ? p.m_tiles * p.n_tiles : p.m_tiles; }
+__device__ __forceinline__ void pconv_item(const PconvParams& p, int item, int& m_tile, int& n_lo, int& n_hi) {
+  if (p.dist_n) {
+    m_tile = item / p.n_tiles;
+    n_lo = item - m_tile * p.n_tiles;
+    n_hi = n_lo + 1;
+  } else {
+    m_tile = item;
+    n_lo = 0;
+    n_hi = p.n_tiles;
+  }
+}
 
 constexpr int kPconvThreads = 352;  // patch producer, MMA issuer, 8 epilogue warps, weight producer
 constexpr int kWeightWarp = 10;
@@ -679,8 +695,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       int it = 0, buf = 0;
       uint32_t ph = 0;
       bool ok = true;
-      const int units = p.groups == 1 ? 1 : p.n_tiles * p.groups;
-      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
+      const int n_items = pconv_items(p);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        int m_tile, n_lo, n_hi;
+        pconv_item(p, item, m_tile, n_lo, n_hi);
+        const int units = p.groups == 1 ? 1 : (n_hi - n_lo) * p.groups;
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
         const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
@@ -700,7 +719,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
         // the patch two tiles ahead: towards L2 now, so that its load later is an L2 hit
-        const int ahead = m_tile + 2 * (int)gridDim.x;
+        const int ahead = p.dist_n ? p.m_tiles : m_tile + 2 * (int)gridDim.x;  // (pairs re-read patches that are in L2 already)
         if (ahead < p.m_tiles) {
           const int avr0 = (int)(((long long)ahead * kM) / p.P);
           int an = avr0 / p.RP, ayy = avr0 - an * p.RP;
@@ -721,8 +740,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         bool ok = true;
         int stage = 0, it = 0;
         uint32_t wphase = 0;
-        for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
-          for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile) {
+        const int n_items = pconv_items(p);
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+          int m_tile, n_lo, n_hi;
+          pconv_item(p, item, m_tile, n_lo, n_hi);
+          for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile) {
             const bool sparse = n_tile >= p.sparse_tile0;
             const uint32_t* gs = s_tab + (sparse ? 17 : 0);
             const uint32_t* ent = s_tab + kTabHead;
@@ -745,10 +767,13 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
       int it = 0, cnt = 0, stage = 0, buf = 0;
       uint32_t wphase = 0, pph = 0;
-      for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x, ++it) {
+      const int n_items = pconv_items(p);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        int m_tile, n_lo, n_hi;
+        pconv_item(p, item, m_tile, n_lo, n_hi);
         const long long q0 = (long long)m_tile * kM;
         const int off0 = (int)(q0 - (q0 / p.P) * p.P);
-        for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile, ++cnt) {
+        for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
           const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
           const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
           if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 503)) { ok = false; break; }
@@ -760,10 +785,10 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const uint32_t* ent = s_tab + kTabHead;
           for (int g = 0; g < p.groups && ok; ++g) {
             // the patch unit of this group: a new one per (N tile, group), or the M tile's only one
-            const bool fresh = p.groups > 1 || n_tile == 0;
+            const bool fresh = p.groups > 1 || n_tile == n_lo;
             if (fresh) {
               if (!mbar_wait_bounded(bar_pfull + 8 * buf, pph, s_abort, p.gerr, 502)) { ok = false; break; }
-              if (p.ts && blockIdx.x == 0 && it < 16 && n_tile == 0 && g == 0) p.ts[it * 8 + 3] = clock64();
+              if (p.ts && blockIdx.x == 0 && it < 16 && n_tile == n_lo && g == 0) p.ts[it * 8 + 3] = clock64();
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
             const uint32_t e1 = gs[g + 1];
@@ -791,7 +816,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               }
             }
             // the unit may be overwritten once these MMAs have read it
-            if (ok && (p.groups > 1 || n_tile == p.n_tiles - 1)) {
+            if (ok && (p.groups > 1 || n_tile == n_hi - 1)) {
               umma_commit(bar_pempty + 8 * buf);
               if (++buf == p.patch_bufs) { buf = 0; pph ^= 1u; }
             }
@@ -809,8 +834,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     const int row_in_tile = q4 * 32 + lane;
     int cnt = 0;
     bool ok = true;
-    for (int m_tile = blockIdx.x; m_tile < p.m_tiles && ok; m_tile += gridDim.x) {
-      for (int n_tile = 0; n_tile < p.n_tiles && ok; ++n_tile, ++cnt) {
+    const int n_items = pconv_items(p);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      int m_tile, n_lo, n_hi;
+      pconv_item(p, item, m_tile, n_lo, n_hi);
+      for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
         const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
         const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
         const int nb = n_tile * NT;
@@ -820,7 +848,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         if (sg.residual) {
           // pull the residual rows of this CTA's next tile (and of its first tile) towards L2 now, so that
           // the loads in the epilogue steps below find them there instead of waiting on HBM
-          for (int which = (m_tile == (int)blockIdx.x ? 0 : 1); which < 2; ++which) {
+          for (int which = ((item == (int)blockIdx.x || p.dist_n) ? 0 : 1); which < (p.dist_n ? 1 : 2); ++which) {
             const int mt = m_tile + which * (int)gridDim.x;
             if (mt >= p.m_tiles) break;
 #pragma unroll 1
@@ -1241,11 +1269,22 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
     best = 1; best_opt = o; best_ms = ms; best_pb = pb; best_G = G; best_res = res; best_stages = (int)stages;
     best_acc = 2 * ms * opts[o].NT <= 512 ? 2 : 1;
   };
-  for (int o = 0; o < n_opts && best < 0; ++o) {
+  // few M tiles (small batches): the narrowest N tiling, one (M tile, N tile) pair per CTA, so that as many
+  // SMs as possible stream the weights -- at batch 1 a layer is one or two M tiles and its weights are
+  // all of its traffic
+  const bool small = ceil_div_ll(total_q, kTileM) * 4 <= ctx->sm_count && !f_nt;
+  q.dist_n = 0;
+  for (int oo = 0; oo < n_opts && best < 0; ++oo) {
+    const int o = small ? n_opts - 1 - oo : oo;
     const int NT = opts[o].NT, wblock = NT * 128;
     const int dense_kb = q.taps * q.cblocks;
     if (f_nt && NT != f_nt) continue;
+    if (!small && NT == 64 && o > 0) continue;  // the 64-wide tiling of a wider layer is for the small regime only
     int ms_top = 256 / NT < 1 ? 1 : 256 / NT;
+    if (small) {
+      ms_top = 1;
+      q.dist_n = opts[o].n_tiles > 1 ? 1 : 0;
+    }
     if (f_ms) ms_top = f_ms;
     if (ms_top * NT > 512) continue;
     while (!f_ms && ms_top > 1 && ceil_div_ll(total_q, ms_top * kTileM) < ctx->sm_count) ms_top /= 2;
@@ -1296,7 +1335,8 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
   pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + kPconvTail;
-  pl->pc_grid = q.m_tiles < ctx->sm_count ? q.m_tiles : ctx->sm_count;
+  const long long items = (long long)q.m_tiles * (q.dist_n ? q.n_tiles : 1);
+  pl->pc_grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
   return true;
 }
 
@@ -1404,12 +1444,13 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.seg[1] = q.seg[0];
   // N tilings: the natural tile width, and for wide layers also half of it (more sub-tiles per CTA tile
   // then share every weight block); Kpad is a multiple of both
-  PconvNtOption opts[2];
+  PconvNtOption opts[3];
   int n_opts = 0;
   const int NT0 = d.out_c <= 64 ? 64 : (d.out_c <= 128 ? 128 : 256);
   const int dense = q.taps * q.cblocks;
   opts[n_opts++] = PconvNtOption{NT0, pl->Kpad / NT0, dense * (pl->Kpad / NT0), 1 << 30};
   if (NT0 == 256) opts[n_opts++] = PconvNtOption{128, pl->Kpad / 128, dense * (pl->Kpad / 128), 1 << 30};
+  if (NT0 >= 128) opts[n_opts++] = PconvNtOption{64, pl->Kpad / 64, dense * (pl->Kpad / 64), 1 << 30};
   if (!pconv_choose_tile(ctx, pl, opts, n_opts, d.kh)) return AIG_OK;
   pl->pc_in_h = d.in_h;
   pl->pc_in_w = d.in_w;
@@ -1676,10 +1717,11 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
   q.seg[1].channels = out_c; q.seg[1].c0 = out_c; q.seg[1].act = AIG_ACT_NONE;
   // N tilings: main and shortcut columns in one tile (shortcut rows dense, mostly zero), or tiles of
   // their own, where the shortcut tiles walk only the channel blocks they read (needs in_c % 64 == 0)
-  PconvNtOption opts[2];
+  PconvNtOption opts[3];
   int n_opts = 0;
   const int dense = q.taps * q.cblocks, sparse = q.taps * q.sub_cblocks;
-  for (int NT = 256; NT >= 128; NT /= 2) {
+  for (int NT = 256; NT >= 64; NT /= 2) {
+    if (NT == 64 && N2 == 128) continue;  // keep main and shortcut columns of a 64-channel block in one tile
     if (N2 % NT != 0 || out_c % (NT / 2) != 0) continue;
     const int nt = N2 / NT;
     if (nt > 1 && out_c % NT == 0 && in_c % 64 == 0) {
