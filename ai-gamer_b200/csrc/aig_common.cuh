@@ -98,6 +98,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---- programmatic dependent launch ----
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in
+// the stream still runs: everything before griddep_wait() (barrier setup, TMEM allocation, loads of constant
+// weights) overlaps the predecessor's tail; griddep_wait() returns once the predecessor has completed and
+// its writes are visible.  Without the attribute both are no-ops.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- mbarrier ----
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -277,6 +277,7 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
   const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 16, bar_tfull = bar_afull + 32, bar_tempty = bar_afull + 48;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  griddep_launch_dependents();  // the first residual-block launch may set itself up under this kernel
   uint2* s_patch = reinterpret_cast<uint2*>(bars + 16);
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_patch + kPatchMax);  // 4 x 2 KB, one tile per epilogue warp (16-byte aligned)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

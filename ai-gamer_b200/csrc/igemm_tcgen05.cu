@@ -650,6 +650,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint8_t* s_stage = sm + tail + 5120 + (threadIdx.x >> 5) * 2048;  // per-warp staging tile of the epilogue (warps 2..9 use it)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  griddep_launch_dependents();  // the next launch may set itself up and prefetch its weights under this one
   for (int i = threadIdx.x; i < p.tab_words; i += kPconvThreads) s_tab[i] = p.tab[i];
   if (p.n_tiles == 1) {
     for (int i = threadIdx.x; i < NT; i += kPconvThreads) {
@@ -696,6 +697,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       const int n_items = pconv_items(p);
+      griddep_wait();  // activations come from the previous launch
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
         int m_tile, n_lo, n_hi;
         pconv_item(p, item, m_tile, n_lo, n_hi);
@@ -835,6 +837,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     int cnt = 0;
     bool ok = true;
     const int n_items = pconv_items(p);
+    griddep_wait();  // residual rows come from, and outputs may overwrite what was read by, earlier launches
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       int m_tile, n_lo, n_hi;
       pconv_item(p, item, m_tile, n_lo, n_hi);
@@ -1038,6 +1041,7 @@ struct aig_conv_plan {
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
   bool pc_wres = false;
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
+  bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
   bool is_down = false;                        // fused down-sampling pair (main k4 s2 p1 + shortcut k2 s2 p0)
 };
 
@@ -1211,8 +1215,18 @@ int launch_pconv(aig_conv_plan* pl) {
     AIG_CUDA_OK(ctx, cudaFuncSetAttribute(pconv_kernel<NT, MS, WRES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[ctx->device & 63] = true;
   }
-  pconv_kernel<NT, MS, WRES><<<pl->pc_grid, kPconvThreads, pl->pc_smem, ctx->stream>>>(pl->tmapP, pl->tmapBp, pl->pp);
-  AIG_LAUNCH_OK(ctx);
+  // programmatic dependent launch: this kernel may start under the tail of its predecessor (see griddep_wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl->pc_grid);
+  cfg.blockDim = dim3(kPconvThreads);
+  cfg.dynamicSmemBytes = (size_t)pl->pc_smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pl->pc_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES>, pl->tmapP, pl->tmapBp, pl->pp));
   return AIG_OK;
 }
 
@@ -1331,6 +1345,7 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   // N = 64 tiles saturate shared-memory bandwidth with operand reads (6 KB per 49-clk MMA); the staging
   // tile of the coalescing epilogue costs more there than the scattered stores it saves
   q.direct_store = NT == 64 ? 1 : 0;
+  if (const char* e = getenv("AIG_NO_PDL")) pl->pc_pdl = !atoi(e);
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
