@@ -10,6 +10,7 @@
 //   LayerNorm: float gamma[E], float beta[E]                           (LayerNorm.cpp:50-61)
 //   FC  : half W[E][n_out], half b[n_out]                              (FCLayer.cpp:70-81)
 #include <cuda_runtime.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <string>
@@ -17,6 +18,7 @@
 
 #include "aig_b200.h"
 #include "aig_host.h"
+#include "seq_step.h"
 
 struct aig_seq {
   aig_ctx* ctx = nullptr;
@@ -33,6 +35,7 @@ struct aig_seq {
   float* out_f32 = nullptr;
   bool loaded = false;
   int position = 0;
+  SeqStepFused* fused = nullptr;  // one-kernel streaming step for small batches (replaces the launches of aig_seq_step)
 };
 
 namespace {
@@ -84,6 +87,12 @@ int aig_seq_create(aig_ctx* ctx, const aig_seq_config* cfg, aig_seq** out) {
        cudaMemset(m->c_state, 0, state * 2) != cudaSuccess ||
        cudaMalloc(&m->params, aig_seq_param_bytes(&c) + 16 * 256) != cudaSuccess))
     rc = AIG_ERR_CUDA;
+  if (rc == AIG_OK) {
+    const int window = c.window > 0 ? c.window : c.seq_len;
+    const SeqStepConfig sc{c.batch, c.in_c, c.hidden, c.layers, c.heads, window, c.n_out, c.n_sigmoid, c.rope_base, 5.0f, 1};
+    const char* off = getenv("AIG_SEQ_NO_FUSED_STEP");
+    if (seq_step_fused_supported(sc) && !(off && atoi(off))) rc = seq_step_fused_create(ctx, sc, &m->fused);
+  }
   if (rc != AIG_OK) {
     aig_seq_destroy(m);
     return rc;
@@ -98,6 +107,7 @@ int aig_seq_destroy(aig_seq* m) {
   aig_lstm_plan_destroy(m->lstm_full);
   aig_lstm_plan_destroy(m->lstm_step);
   aig_mha_plan_destroy(m->mha);
+  seq_step_fused_destroy(m->fused);
   aig_conv_plan_destroy(m->fc_full);
   aig_conv_plan_destroy(m->fc_step);
   void* bufs[] = {m->params, m->y, m->a, m->n, m->logits, m->out_f32, m->h_state, m->c_state};
@@ -130,6 +140,7 @@ int aig_seq_load_memory(aig_seq* m, const void* blob, size_t bytes) {
   SEQ_OK(m, aig_mha_plan_set_weights(m->mha, m->wq, m->wk, m->wv, m->wo));
   SEQ_OK(m, aig_fc_plan_set_weights(m->fc_full, m->fcw, m->fcb, nullptr, nullptr, nullptr, nullptr, 0.f));
   SEQ_OK(m, aig_fc_plan_set_weights(m->fc_step, m->fcw, m->fcb, nullptr, nullptr, nullptr, nullptr, 0.f));
+  if (m->fused) SEQ_OK(m, seq_step_fused_set_weights(m->fused, m->lstm_w, m->wq, m->wk, m->wv, m->wo, m->ln_g, m->ln_b, m->fcw, m->fcb));
   m->loaded = true;
   return AIG_OK;
 }
@@ -159,6 +170,11 @@ int aig_seq_step(aig_seq* m, const aig_half* emb_t) {
   if (!m || !emb_t) return AIG_ERR_INVALID;
   if (!m->loaded) return sfail(m, AIG_ERR_INVALID, "parameters not loaded");
   const aig_seq_config& c = m->cfg;
+  if (m->fused) {
+    SEQ_OK(m, seq_step_fused_run(m->fused, emb_t, m->h_state, m->c_state, m->y, m->logits, m->out_f32, m->position));
+    ++m->position;
+    return AIG_OK;
+  }
   SEQ_OK(m, aig_lstm_forward(m->lstm_step, emb_t, m->y, m->h_state, m->c_state, 1));
   SEQ_OK(m, aig_mha_step(m->mha, m->y, m->a, m->position));
   ++m->position;
@@ -172,6 +188,7 @@ int aig_seq_reset(aig_seq* m) {
   if (cudaMemsetAsync(m->h_state, 0, state, s) != cudaSuccess || cudaMemsetAsync(m->c_state, 0, state, s) != cudaSuccess)
     return sfail(m, AIG_ERR_CUDA, "state reset failed");
   m->position = 0;
+  if (m->fused) seq_step_fused_reset(m->fused);
   return aig_mha_reset(m->mha);
 }
 

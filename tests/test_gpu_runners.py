@@ -28,10 +28,11 @@ def _seq_head(U, batch, seq_len, d, heads, window):
 
 
 @gpu
-def test_sequence_head_full_and_streaming(env):
+@pytest.mark.parametrize("B", [4, 6, 1])   # up to 4 sequences stream through the one-kernel step, more through the per-operator launches
+def test_sequence_head_full_and_streaming(env, B):
     U = env
     U.pkg()
-    B, T, d, heads = 4, 16, 128, 2
+    T, d, heads = 16, 128, 2
     p = PL.make_seq_params(5, d=d, hid=d, layers=2, heads=heads)
     emb = PL.make_embeddings(5, T, B, d)                    # [T][B][d]
     y, a, logits, want = PL.seq_forward(p, emb, rope_base=10000.0, window=0)
