@@ -565,6 +565,7 @@ struct PconvParams {
   int Ho, Wo, batch;
   int m_tiles, n_tiles;
   int patch_vrows, region_bytes, patch_bytes;
+  int tall_ok;             // the patch_vrows-row tensor map exists (one box per channel block where the patch stays in one image)
   int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
   int acc_bufs;            // TMEM accumulator buffers: 2, or 1 when MS*NT fills all 512 columns
   int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
@@ -625,7 +626,8 @@ constexpr int kWeightWarp = 10;
 
 template <int NT, int MS, bool WRES>
 __global__ void __launch_bounds__(kPconvThreads, 1)
-pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, const PconvParams p) {
+pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapAT, const __grid_constant__ CUtensorMap tmapB,
+             const PconvParams p) {
   constexpr int kM = MS * kTileM;
   constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
   extern __shared__ uint8_t smem_raw[];
@@ -675,6 +677,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     *s_abort = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmapA);
+    tma_prefetch_desc(&tmapAT);
     tma_prefetch_desc(&tmapB);
   }
   constexpr uint32_t kTmemCols = (2 * MS * NT > 512) ? 512u : (uint32_t)(2 * MS * NT);
@@ -711,25 +714,22 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
           mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
-          int n = n0, yy = yy0;
-          for (int r = 0; r < p.patch_vrows; ++r) {
+          if (p.tall_ok && yy0 + p.patch_vrows - 1 < p.RP + p.pad) {
+            // the patch ends inside image n0 or in the padding rows below it: one box of patch_vrows rows per channel
+            // block (rows past the image are zero-filled, which is what the shared padding rows hold)
             for (int l = 0; l < p.G; ++l)
-              tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
-            if (++yy == p.RP) { yy = 0; ++n; }
+              tma_load_5d(dst0 + l * p.region_bytes, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy0 - p.pad, 0, n0);
+          } else {
+            int n = n0, yy = yy0;
+            for (int r = 0; r < p.patch_vrows; ++r) {
+              for (int l = 0; l < p.G; ++l)
+                tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
+              if (++yy == p.RP) { yy = 0; ++n; }
+            }
           }
           if (++buf == p.patch_bufs) { buf = 0; ph ^= 1u; }
         }
         if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
-        // the patch two tiles ahead: towards L2 now, so that its load later is an L2 hit
-        const int ahead = p.dist_n ? p.m_tiles : m_tile + 2 * (int)gridDim.x;  // (pairs re-read patches that are in L2 already)
-        if (ahead < p.m_tiles) {
-          const int avr0 = (int)(((long long)ahead * kM) / p.P);
-          int an = avr0 / p.RP, ayy = avr0 - an * p.RP;
-          for (int r = 0; r < p.patch_vrows; ++r) {
-            for (int cb = 0; cb < p.cblocks; ++cb) tma_prefetch_5d(&tmapA, cb * 64, -p.pad, ayy - p.pad, 0, an);
-            if (++ayy == p.RP) { ayy = 0; ++an; }
-          }
-        }
       }
     }
   } else if (warp == kWeightWarp) {
@@ -1036,7 +1036,7 @@ struct aig_conv_plan {
   bool use_pconv = false;
   PconvParams pp{};
   uint32_t* pc_tab = nullptr;
-  CUtensorMap tmapP{}, tmapBp{};
+  CUtensorMap tmapP{}, tmapPT{}, tmapBp{};  // patch rows one per box / patch_vrows per box, weights
   const void* tmapP_ptr = nullptr;
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
   bool pc_wres = false;
@@ -1226,7 +1226,7 @@ int launch_pconv(aig_conv_plan* pl) {
   attr[0].val.programmaticStreamSerializationAllowed = pl->pc_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES>, pl->tmapP, pl->tmapBp, pl->pp));
+  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES>, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->pp));
   return AIG_OK;
 }
 
@@ -1422,6 +1422,17 @@ int encode_P(aig_conv_plan* pl, const void* x) {
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(P) failed: %d", (int)r);
+  pl->tmapPT = pl->tmapP;
+  pl->pp.tall_ok = 0;
+  const char* no_tall = getenv("AIG_PCONV_NO_TALL");
+  if (pl->pp.patch_vrows <= 256 && !(no_tall && atoi(no_tall))) {
+    box[2] = (cuuint32_t)pl->pp.patch_vrows;
+    r = enc(&pl->tmapPT, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) pl->pp.tall_ok = 1;
+    else pl->tmapPT = pl->tmapP;
+  }
   pl->tmapP_ptr = x;
   return AIG_OK;
 }
