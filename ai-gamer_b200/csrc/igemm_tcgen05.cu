@@ -567,7 +567,7 @@ struct PconvParams {
   int patch_vrows, region_bytes, patch_bytes;
   int tall_ok;             // the patch_vrows-row tensor map exists (one box per channel block where the patch stays in one image)
   int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
-  int acc_bufs;            // TMEM accumulator buffers: 2, or 1 when MS*NT fills all 512 columns
+  int acc_bufs;            // TMEM accumulator buffers of MS*NT columns: as many as fit in 512 columns, at most 4
   int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
   int G, groups;           // 64-channel blocks per patch unit, units per pass over the channels (G * groups == cblocks)
   int n_split;             // GEMM columns >= n_split go to seg[1]
@@ -642,11 +642,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 2048);
   const uint32_t bar_pfull = smem_u32(bars);          // [4]
   const uint32_t bar_pempty = bar_pfull + 32;         // [4]
-  const uint32_t bar_tfull = bar_pfull + 64;          // [2]
-  const uint32_t bar_tempty = bar_pfull + 80;         // [2]
-  const uint32_t bar_wfull = bar_pfull + 96;          // [w_stages] (resident: [0] only)
+  const uint32_t bar_tfull = bar_pfull + 64;          // [4]
+  const uint32_t bar_tempty = bar_pfull + 96;         // [4]
+  const uint32_t bar_wfull = bar_pfull + 128;         // [w_stages] (resident: [0] only)
   const uint32_t bar_wempty = bar_wfull + 8 * 32;     // [w_stages]
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 12 + 64);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint32_t* s_tab = s_tmem + 4;
   uint8_t* s_stage = sm + tail + 5120 + (threadIdx.x >> 5) * 2048;  // per-warp staging tile of the epilogue (warps 2..9 use it)
@@ -665,7 +665,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       mbar_init(bar_pfull + 8 * a, 1);
       mbar_init(bar_pempty + 8 * a, 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 8);
     }
@@ -680,7 +680,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     tma_prefetch_desc(&tmapAT);
     tma_prefetch_desc(&tmapB);
   }
-  constexpr uint32_t kTmemCols = (2 * MS * NT > 512) ? 512u : (uint32_t)(2 * MS * NT);
+  constexpr uint32_t kTmemCols = 512u;  // acc_bufs buffers of MS * NT columns each
   if (warp == 1) {
     tmem_alloc(smem_u32(s_tmem), kTmemCols);
     tmem_relinquish();
@@ -776,8 +776,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const long long q0 = (long long)m_tile * kM;
         const int off0 = (int)(q0 - (q0 / p.P) * p.P);
         for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
-          const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
-          const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
+          const int acc = cnt % p.acc_bufs;
+          const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
           if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 503)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
@@ -837,13 +837,39 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     int cnt = 0;
     bool ok = true;
     const int n_items = pconv_items(p);
+    // Position of this lane's row of sub-tile 0 of the current M tile as (image n, virtual row yy, virtual column
+    // vc).  It is divided out once; after that it moves by fixed strides (one sub-tile = 128 positions, one
+    // work item = gridDim.x M tiles), added digit by digit with carries, so the item loop holds no division.
+    struct Pos { int n, yy, vc; };
+    auto pos_of = [&](long long q) {
+      const int vr = (int)(q / p.P);
+      Pos a;
+      a.vc = (int)(q - (long long)vr * p.P);
+      a.n = vr / p.RP;
+      a.yy = vr - a.n * p.RP;
+      return a;
+    };
+    auto pos_add = [&](Pos a, const Pos& d) {  // d: a stride, split the same way (d.yy < RP, d.vc < P)
+      a.vc += d.vc;
+      const int c = a.vc >= p.P ? 1 : 0;
+      a.vc -= c * p.P;
+      a.yy += d.yy + c;
+      const int c2 = a.yy >= p.RP ? 1 : 0;
+      a.yy -= c2 * p.RP;
+      a.n += d.n + c2;
+      return a;
+    };
+    const Pos d_sub = pos_of(kTileM);
+    const Pos d_item = pos_of((long long)gridDim.x * kM);
+    Pos pos0 = pos_of((long long)blockIdx.x * kM + row_in_tile);  // (work items are whole M tiles unless dist_n)
     griddep_wait();  // residual rows come from, and outputs may overwrite what was read by, earlier launches
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       int m_tile, n_lo, n_hi;
       pconv_item(p, item, m_tile, n_lo, n_hi);
+      if (p.dist_n) pos0 = pos_of((long long)m_tile * kM + row_in_tile);
       for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
-        const int acc = p.acc_bufs == 2 ? (cnt & 1) : 0;
-        const uint32_t acc_phase = (uint32_t)(p.acc_bufs == 2 ? (cnt >> 1) : cnt) & 1u;
+        const int acc = cnt % p.acc_bufs;
+        const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
         const int nb = n_tile * NT;
         const float* sc = p.n_tiles == 1 ? s_scale : p.scale + nb;
         const float* sf = p.n_tiles == 1 ? s_shift : p.shift + nb;
@@ -854,11 +880,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           for (int which = ((item == (int)blockIdx.x || p.dist_n) ? 0 : 1); which < (p.dist_n ? 1 : 2); ++which) {
             const int mt = m_tile + which * (int)gridDim.x;
             if (mt >= p.m_tiles) break;
+            Pos a = which ? pos_add(pos0, d_item) : pos0;
 #pragma unroll 1
             for (int sub = 0; sub < MS; ++sub) {
-              const long long q = (long long)mt * kM + sub * kTileM + row_in_tile;
-              const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
-              const int n = vr / p.RP, yy = vr - n * p.RP;
+              const int n = a.n, yy = a.yy, vc = a.vc;
+              a = pos_add(a, d_sub);
               if (n < p.batch && yy < p.Ho && vc < p.Wo) {
                 const __half* rr = sg.residual + (((size_t)n * p.Ho + yy) * p.Wo + vc) * sg.channels + (nb - sg.c0 + col_lo);
                 for (int b = 0; b < NT; b += 128)  // NT/2 halfs = NT bytes per row segment
@@ -870,11 +896,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
         tc_fence_after();
         if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 5] = clock64();
+        Pos a = pos0;
 #pragma unroll 1
         for (int sub = 0; sub < MS; ++sub) {
-          const long long q = (long long)m_tile * kM + sub * kTileM + row_in_tile;
-          const int vr = (int)(q / p.P), vc = (int)(q - (long long)vr * p.P);
-          const int n = vr / p.RP, yy = vr - n * p.RP;
+          const int n = a.n, yy = a.yy, vc = a.vc;
+          a = pos_add(a, d_sub);
           const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
           const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
           size_t opix = pix;
@@ -904,6 +930,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 6] = clock64();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
       }
+      pos0 = pos_add(pos0, d_item);
     }
   }
 
@@ -1281,7 +1308,9 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   auto vrows_of = [&](int M) { return (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1; };
   auto take = [&](int o, int ms, int pb, int G, bool res, long long stages) {
     best = 1; best_opt = o; best_ms = ms; best_pb = pb; best_G = G; best_res = res; best_stages = (int)stages;
-    best_acc = 2 * ms * opts[o].NT <= 512 ? 2 : 1;
+    best_acc = 512 / (ms * opts[o].NT);
+    if (best_acc > 4) best_acc = 4;
+    if (const char* e = getenv("AIG_PCONV_ACC")) best_acc = std::min(best_acc, std::max(1, atoi(e)));
   };
   // few M tiles (small batches): the narrowest N tiling, one (M tile, N tile) pair per CTA, so that as many
   // SMs as possible stream the weights -- at batch 1 a layer is one or two M tiles and its weights are
