@@ -123,9 +123,7 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
           float a1 = fmaf(__uint_as_float(r[e + 1]), sv[e2 * 2 + 1], hv[e2 * 2 + 1]);
           if (RES) {
             // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
-            const float2 m = __half22float2(__floats2half2_rn(a0, a1));
-            const float2 rr = __half22float2(rh[e2]);
-            const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+            const float2 t = __half22float2(__hadd2(__floats2half2_rn(a0, a1), rh[e2]));
             a0 = t.x;
             a1 = t.y;
           }
@@ -175,9 +173,7 @@ __device__ __forceinline__ void epi_fused_cols(uint32_t t_addr, int col_lo, int 
           float a1 = fmaf(__uint_as_float(r[e + 1]), s[e + 1], h[e + 1]);
           if (RES) {
             // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
-            const float2 m = __half22float2(__floats2half2_rn(a0, a1));
-            const float2 rr = __half22float2(rh[e2]);
-            const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+            const float2 t = __half22float2(__hadd2(__floats2half2_rn(a0, a1), rh[e2]));
             a0 = t.x;
             a1 = t.y;
           }
@@ -253,9 +249,7 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
         float a1 = fmaf(__uint_as_float(r[e + 1]), sv[e2 * 2 + 1], hv[e2 * 2 + 1]);
         if (RES) {
           // the reference stores fp16 after BatchNorm and again after the add (ResConvLayer.cpp:35-36)
-          const float2 m = __half22float2(__floats2half2_rn(a0, a1));
-          const float2 rr = __half22float2(rh[e2]);
-          const float2 t = __half22float2(__floats2half2_rn(m.x + rr.x, m.y + rr.y));
+          const float2 t = __half22float2(__hadd2(__floats2half2_rn(a0, a1), rh[e2]));
           a0 = t.x;
           a1 = t.y;
         }
