@@ -539,9 +539,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
 // padding of one row is the left padding of the next).  With q = vr*P + vc, the input of output
 // position q for tap (fr, fs) is position q + fr*P + fs: one uniform shift per tap.  An M tile is M
 // consecutive positions q; its A operand for a tap is M consecutive 128-byte rows of the patch in
-// shared memory starting (fr*P + fs) rows further on, addressed by the UMMA descriptor alone.  Each
-// virtual row is one TMA box of P pixels x 64 channels starting at x = -p; padding and rows past the
-// batch are zero-filled by TMA.  Positions with vc >= Wo or vr % RP >= Ho are computed and dropped.
+// shared memory starting (fr*P + fs) rows further on, addressed by the UMMA descriptor alone.  A
+// virtual row is a TMA box of P pixels x 64 channels starting at x = -p (all rows of a patch in one
+// box where the patch stays inside one image); padding and rows past the batch are zero-filled by TMA.  Positions with vc >= Wo or vr % RP >= Ho are computed and dropped.
 // Weights stay resident in shared memory for the whole launch when they fit beside two patches,
 // otherwise they stream through a ring of (tap, 64-channel block) stages shared by the MS sub-tiles.
 struct OutSeg {
@@ -1365,8 +1365,8 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   q.w_stages = best_stages;
   q.acc_bufs = best_acc;
   q.m_tiles = (int)ceil_div_ll(total_q, M);
-  // N = 64 tiles saturate shared-memory bandwidth with operand reads (6 KB per 49-clk MMA); the staging
-  // tile of the coalescing epilogue costs more there than the scattered stores it saves
+  // at N = 64 a warp's column half is 64 bytes of a 128-byte output row: the staging tile of the coalescing
+  // epilogue costs more there than the scattered stores it saves (measured: 95 vs 93 us on a 64 -> 64 layer)
   q.direct_store = NT == 64 ? 1 : 0;
   if (const char* e = getenv("AIG_NO_PDL")) pl->pc_pdl = !atoi(e);
   pl->pc_NT = NT;
