@@ -32,6 +32,7 @@ SIGNATURES = {
     "aig_ctx_stream": [P],
     "aig_ctx_sync": [P],
     "aig_last_error": [P],
+    "aig_selftest_expiring_wait": [P, ctypes.c_longlong],
     "aig_device_sm_count": [P],
     "aig_memcpy": [P, P, P, c_size_t],
     "aig_graph_begin": [P],
@@ -180,8 +181,17 @@ SIGNATURES.update({
     "aig_refnn_create": [P, c_int, c_int, ctypes.c_char_p, PP],
     "aig_refnn_forward": [P, P, PP],
     "aig_refnn_input_size": [P, PI, PI],
+    "aig_compat_handle_create": [PP],
+    "aig_refnn_infer_frame": [P, P, P, P, P, P],
     "aig_refnn_destroy": [P],
     "aig_layers_last_error": [],
+    "aig_layer_create": [P, ctypes.c_char_p, PI, c_int, PP],
+    "aig_layer_forward": [P, P, PP],
+    "aig_layer_load_file": [P, ctypes.c_char_p],
+    "aig_layer_save_file": [P, ctypes.c_char_p],
+    "aig_layer_param_bytes": [P],
+    "aig_layer_out_count": [P],
+    "aig_layer_destroy": [P],
 })
 AIG_C3D_MAX_LAYERS = 6
 
@@ -201,7 +211,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_compat_context": c_void_p, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_compat_context": c_void_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,

@@ -40,8 +40,10 @@ def sources():
     return out
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, defines=()):
+    """defines: extra -D macros (AIG_TUNING compiles the kernels' timeline stamps and tile-search switches in)."""
     os.makedirs(OBJ, exist_ok=True)
+    extra = ["-D" + d for d in defines]
     hdr_t = _newest_header()
     jobs = []
     objs = []
@@ -49,7 +51,7 @@ def build(force=False, verbose=False):
         obj = os.path.join(OBJ, os.path.basename(src) + ".o")
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
-            cmd = ["nvcc"] + NVCC_FLAGS + (["-x", "cu"] if src.endswith(".cpp") else []) + ["-c", src, "-o", obj]
+            cmd = ["nvcc"] + NVCC_FLAGS + extra + (["-x", "cu"] if src.endswith(".cpp") else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):
@@ -69,4 +71,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, defines=[a[2:] for a in sys.argv[1:] if a.startswith("-D")]))

@@ -139,8 +139,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 #ifndef AIG_WAIT_CYCLES
 #define AIG_WAIT_CYCLES (600ll * 1000 * 1000)  // ~0.3 s at 1.9 GHz
 #endif
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  int* gerr, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* gerr, int code,
+                                                long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t it = 0;
@@ -148,13 +148,17 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 63u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > AIG_WAIT_CYCLES) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         atomicCAS(gerr, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* gerr, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, gerr, code, AIG_WAIT_CYCLES);
 }
 
 // ---- TMA (tiled mode; every CTA issues its own loads) ----

@@ -15,6 +15,23 @@ int aig_fail(aig_ctx* ctx, int code, const char* fmt, ...) {
 
 static thread_local std::string g_noctx_error;
 
+namespace {
+// One bounded wait on an mbarrier that nobody arrives at: the wait runs out after `limit_cycles`, records
+// `code` in the device error word and the kernel returns normally.
+__global__ void expiring_wait_kernel(int* gerr, long long limit_cycles, int code) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, gerr, code, limit_cycles);
+  __syncthreads();
+}
+}  // namespace
+
 extern "C" {
 
 int aig_ctx_create(aig_ctx** out, int device) {
@@ -89,6 +106,15 @@ int aig_ctx_sync(aig_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     return aig_fail(ctx, AIG_ERR_TIMEOUT, "a bounded device-side wait expired (kernel site code %d)", code);
   }
+  return AIG_OK;
+}
+
+int aig_selftest_expiring_wait(aig_ctx* ctx, long long limit_cycles) {
+  if (!ctx) return AIG_ERR_INVALID;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, limit_cycles > 0 && limit_cycles <= 200ll * 1000 * 1000, "selftest: limit must be 1 .. 2e8 cycles");
+  expiring_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_err, limit_cycles, 901);
+  AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }
 

@@ -576,7 +576,7 @@ struct PconvParams {
   const uint32_t* tab;     // K schedule tables (see PconvTab)
   int tab_words;
   int direct_store;        // epilogue stores straight from the row-owning lanes instead of through the staging tile
-  long long* ts;           // optional timeline of CTA 0 (8 stamps per tile, first 16 tiles), or null
+  long long* ts;           // tuning builds: timeline of CTA 0 (8 stamps per tile, first 16 tiles); null otherwise
 };
 
 // A operand descriptors here start on any 128-byte row of a 1024-byte swizzle atom, not only on its
@@ -614,6 +614,19 @@ __device__ __forceinline__ void pconv_item(const PconvParams& p, int item, int& 
     n_hi = p.n_tiles;
   }
 }
+
+// Per-tile clock64 stamps of CTA 0 (patch issue / patch ready / MMAs issued / accumulator ready / epilogue
+// done) exist only in a tuning build (-DAIG_TUNING); the shipped kernel carries none of it.
+#ifdef AIG_TUNING
+#define AIG_STAMP(cond, idx)                      \
+  do {                                            \
+    if (p.ts && (cond)) p.ts[idx] = clock64();    \
+  } while (0)
+#else
+#define AIG_STAMP(cond, idx) \
+  do {                       \
+  } while (0)
+#endif
 
 constexpr int kPconvThreads = 352;  // patch producer, MMA issuer, 8 epilogue warps, weight producer
 constexpr int kWeightWarp = 10;
@@ -702,7 +715,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
         const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 0] = clock64();
+        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 0);
         for (int u = 0; u < units && ok; ++u) {
           const int g = p.groups == 1 ? 0 : u % p.groups;
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
@@ -723,7 +736,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           }
           if (++buf == p.patch_bufs) { buf = 0; ph ^= 1u; }
         }
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 1] = clock64();
+        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 1);
       }
     }
   } else if (warp == kWeightWarp) {
@@ -751,7 +764,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
           }
-          if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 2] = clock64();
+          AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 2);
         }
       }
     }
@@ -784,7 +797,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             const bool fresh = p.groups > 1 || n_tile == n_lo;
             if (fresh) {
               if (!mbar_wait_bounded(bar_pfull + 8 * buf, pph, s_abort, p.gerr, 502)) { ok = false; break; }
-              if (p.ts && blockIdx.x == 0 && it < 16 && n_tile == n_lo && g == 0) p.ts[it * 8 + 3] = clock64();
+              AIG_STAMP(blockIdx.x == 0 && it < 16 && n_tile == n_lo && g == 0, it * 8 + 3);
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
             const uint32_t e1 = gs[g + 1];
@@ -819,7 +832,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           }
           if (ok) umma_commit(bar_tfull + 8 * acc);
         }
-        if (p.ts && blockIdx.x == 0 && it < 16) p.ts[it * 8 + 4] = clock64();
+        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 4);
       }
     }
   } else if (warp < kWeightWarp) {
@@ -889,7 +902,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
         tc_fence_after();
-        if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 5] = clock64();
+        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64, cnt * 8 + 5);
         Pos a = pos0;
 #pragma unroll 1
         for (int sub = 0; sub < MS; ++sub) {
@@ -921,7 +934,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         tc_fence_before();
         __syncwarp();
-        if (p.ts && blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64) p.ts[cnt * 8 + 6] = clock64();
+        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64, cnt * 8 + 6);
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
       }
       pos0 = pos_add(pos0, d_item);
@@ -1297,14 +1310,18 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   double best = -1;
   int best_ms = 0, best_acc = 2, best_pb = 2, best_stages = 0, best_opt = 0, best_G = 0;
   bool best_res = false;
-  int f_nt = 0, f_ms = 0, f_pb = 0, f_g = 0;  // tuning aid: AIG_PCONV_FORCE="NT,MS,patch buffers,G" restricts the search
+  int f_nt = 0, f_ms = 0, f_pb = 0, f_g = 0;  // tuning builds only: AIG_PCONV_FORCE="NT,MS,patch buffers,G" restricts the search
+#ifdef AIG_TUNING
   if (const char* f = getenv("AIG_PCONV_FORCE")) sscanf(f, "%d,%d,%d,%d", &f_nt, &f_ms, &f_pb, &f_g);
+#endif
   auto vrows_of = [&](int M) { return (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1; };
   auto take = [&](int o, int ms, int pb, int G, bool res, long long stages) {
     best = 1; best_opt = o; best_ms = ms; best_pb = pb; best_G = G; best_res = res; best_stages = (int)stages;
     best_acc = 512 / (ms * opts[o].NT);
     if (best_acc > 4) best_acc = 4;
+#ifdef AIG_TUNING
     if (const char* e = getenv("AIG_PCONV_ACC")) best_acc = std::min(best_acc, std::max(1, atoi(e)));
+#endif
   };
   // few M tiles (small batches): the narrowest N tiling, one (M tile, N tile) pair per CTA, so that as many
   // SMs as possible stream the weights -- at batch 1 a layer is one or two M tiles and its weights are
@@ -1447,8 +1464,11 @@ int encode_P(aig_conv_plan* pl, const void* x) {
   if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(P) failed: %d", (int)r);
   pl->tmapPT = pl->tmapP;
   pl->pp.tall_ok = 0;
-  const char* no_tall = getenv("AIG_PCONV_NO_TALL");
-  if (pl->pp.patch_vrows <= 256 && !(no_tall && atoi(no_tall))) {
+  bool tall = pl->pp.patch_vrows <= 256;
+#ifdef AIG_TUNING
+  if (const char* no_tall = getenv("AIG_PCONV_NO_TALL")) tall = tall && !atoi(no_tall);
+#endif
+  if (tall) {
     box[2] = (cuuint32_t)pl->pp.patch_vrows;
     r = enc(&pl->tmapPT, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1507,11 +1527,13 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   int rc = pconv_build_tables(ctx, pl);
   if (rc == AIG_OK) rc = encode_Bp(pl);
   if (rc != AIG_OK) return rc;
+#ifdef AIG_TUNING
   const char* ts = getenv("AIG_PCONV_TS");
   if (ts && atoi(ts)) {
     AIG_CUDA_OK(ctx, cudaMalloc(&q.ts, 128 * sizeof(long long)));
     AIG_CUDA_OK(ctx, cudaMemset(q.ts, 0, 128 * sizeof(long long)));
   }
+#endif
   pl->use_pconv = true;
   return AIG_OK;
 }
@@ -1558,8 +1580,9 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   return AIG_OK;
 }
 
-// Profiling aid (not part of the public interface): copies the timeline recorded by CTA 0 of the last
-// patch-resident launch (8 clock64 stamps per tile, 16 tiles) and the tile shape into out[0..135].
+#ifdef AIG_TUNING
+// Tuning builds only: copies the timeline recorded by CTA 0 of the last patch-resident launch (8 clock64
+// stamps per tile, 16 tiles) and the tile shape into out[0..135].
 int aig_conv_plan_debug_timeline(aig_conv_plan* pl, long long* out) {
   if (!pl || !out || !pl->use_pconv || !pl->pp.ts) return AIG_ERR_INVALID;
   cudaStreamSynchronize(pl->ctx->stream);
@@ -1568,6 +1591,7 @@ int aig_conv_plan_debug_timeline(aig_conv_plan* pl, long long* out) {
   out[132] = pl->pp.patch_bufs; out[133] = pl->pp.G; out[134] = pl->pp.acc_bufs; out[135] = 0;
   return AIG_OK;
 }
+#endif
 
 int aig_conv_plan_out_dims(const aig_conv_plan* pl, int* od, int* oh, int* ow) {
   if (!pl) return AIG_ERR_INVALID;
@@ -1780,9 +1804,11 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
     }
   }
   if (n_opts == 0 || !pconv_choose_tile(ctx, pl, opts, n_opts, 2)) return bail(aig_fail(ctx, AIG_ERR_UNSUPPORTED, "resdown plan: no tile fits shared memory"));
+#ifdef AIG_TUNING
   if (const char* ts = getenv("AIG_PCONV_TS")) {
     if (atoi(ts) && cudaMalloc(&q.ts, 128 * sizeof(long long)) == cudaSuccess) cudaMemset(q.ts, 0, 128 * sizeof(long long));
   }
+#endif
   pl->pc_in_h = Hb; pl->pc_in_w = Wb; pl->pc_in_c = C4;
   int rc = pconv_build_tables(ctx, pl);
   if (rc == AIG_OK) rc = encode_Bp(pl);

@@ -37,8 +37,8 @@ struct StepParams {
   __half *kcache, *vcache;
   __half *y, *logits;
   float* out_f32;
-  unsigned int* counter;
-  unsigned int bar_base;  // value of the counter when this launch started
+  unsigned int* counter;       // this launch's barrier counter: zero when the launch starts
+  unsigned int* counter_next;  // the next launch's counter, zeroed by this launch
   int* gerr;
 };
 
@@ -57,7 +57,7 @@ __device__ bool grid_barrier(const StepParams& p, int idx, int* s_flag) {
   if (threadIdx.x == 0) {
     __threadfence();
     red_release_gpu_add(p.counter, 1u);
-    const unsigned int target = p.bar_base + (unsigned int)(idx + 1) * gridDim.x;
+    const unsigned int target = (unsigned int)(idx + 1) * gridDim.x;
     const long long t0 = clock64();
     int ok = 1;
     while ((int)(ld_acquire_gpu(p.counter) - target) < 0) {
@@ -102,6 +102,10 @@ __global__ void __launch_bounds__(kThreads, 1) seq_step_kernel(const StepParams 
   const int gw = blockIdx.x * kWarps + warp, tw = gridDim.x * kWarps;
   const int H = p.H, B = p.B;
   int bar = 0;
+  // Two counters alternate between launches.  Each launch clears the one its successor will use (its last
+  // user, the launch before this one, has finished), so a launch always starts from zero even when an
+  // earlier launch gave up on a barrier and left its own counter short.
+  if (blockIdx.x == 0 && threadIdx.x == 0) *p.counter_next = 0u;
 
   // ---- LSTM layers: one warp per (sequence, hidden unit): the four gate rows of W and of R
   for (int l = 0; l < p.layers; ++l) {
@@ -272,8 +276,8 @@ struct SeqStepFused {
   SeqStepConfig cfg{};
   StepParams prm{};
   __half* buf = nullptr;        // transposed weights + scratch
-  unsigned int* counter = nullptr;
-  unsigned int bar_base = 0;
+  unsigned int* counter = nullptr;  // two counters, used by alternate launches
+  unsigned int launches = 0;
   int grid = 1;
   int stream_start = -1;
   bool weights_set = false;
@@ -296,12 +300,12 @@ int seq_step_fused_create(aig_ctx* ctx, const SeqStepConfig& c, SeqStepFused** o
   const size_t n_w = 4 * E * E + (size_t)c.n_out * E;
   const size_t n_s = (size_t)c.layers * BE + 6 * BE;
   const size_t n_c = 2 * (size_t)c.batch * c.window * E;
-  if (cudaMalloc(&s->buf, (n_w + n_s + n_c) * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->counter, sizeof(unsigned int)) != cudaSuccess) {
+  if (cudaMalloc(&s->buf, (n_w + n_s + n_c) * sizeof(__half)) != cudaSuccess || cudaMalloc(&s->counter, 2 * sizeof(unsigned int)) != cudaSuccess) {
     seq_step_fused_destroy(s);
     return aig_fail(ctx, AIG_ERR_CUDA, "fused sequence step: allocation failed");
   }
   cudaMemsetAsync(s->buf, 0, (n_w + n_s + n_c) * sizeof(__half), ctx->stream);
-  cudaMemsetAsync(s->counter, 0, sizeof(unsigned int), ctx->stream);
+  cudaMemsetAsync(s->counter, 0, 2 * sizeof(unsigned int), ctx->stream);
   StepParams& p = s->prm;
   p.B = c.batch; p.in_c = c.in_c; p.H = c.hidden; p.layers = c.layers; p.heads = c.heads; p.window = c.window;
   p.n_out = c.n_out; p.n_sig = c.n_sigmoid; p.double_bias = c.double_bias; p.rope_base = c.rope_base;
@@ -313,7 +317,6 @@ int seq_step_fused_create(aig_ctx* ctx, const SeqStepConfig& c, SeqStepFused** o
   p.q = sc; p.k = sc + BE; p.v = sc + 2 * BE; p.ctx = sc + 3 * BE; p.a = sc + 4 * BE; p.n = sc + 5 * BE;
   p.kcache = s->buf + n_w + n_s;
   p.vcache = p.kcache + (size_t)c.batch * c.window * E;
-  p.counter = s->counter;
   p.gerr = ctx->d_err;
   // blob offsets (halfs): per layer W then R, then per layer bW [and bR]
   size_t off = 0;
@@ -372,9 +375,7 @@ int seq_step_fused_set_weights(SeqStepFused* s, const aig_half* lstm_blob, const
 
 int seq_step_fused_reset(SeqStepFused* s) {
   s->stream_start = -1;
-  // also restart the barrier counter: after a step that gave up on a barrier it no longer matches bar_base
-  cudaMemsetAsync(s->counter, 0, sizeof(unsigned int), s->ctx->stream);
-  s->bar_base = 0;
+  cudaMemsetAsync(s->counter, 0, 2 * sizeof(unsigned int), s->ctx->stream);
   return AIG_OK;
 }
 
@@ -395,14 +396,9 @@ int seq_step_fused_run(SeqStepFused* s, const aig_half* emb, aig_half* h_state, 
   p.position = position;
   int n_valid = position - s->stream_start + 1;
   p.n_valid = n_valid > s->cfg.window ? s->cfg.window : n_valid;
-  // barrier bookkeeping: the counter only grows; restart it long before it could wrap
-  const unsigned int per_launch = (unsigned int)(s->cfg.layers + 3) * (unsigned int)s->grid;
-  if (s->bar_base > 0xF0000000u) {
-    AIG_CUDA_OK(ctx, cudaMemsetAsync(s->counter, 0, sizeof(unsigned int), ctx->stream));
-    s->bar_base = 0;
-  }
-  p.bar_base = s->bar_base;
-  s->bar_base += per_launch;
+  p.counter = s->counter + (s->launches & 1u);
+  p.counter_next = s->counter + ((s->launches + 1u) & 1u);
+  ++s->launches;
   void* args[] = {(void*)&p};
   AIG_CUDA_OK(ctx, cudaLaunchCooperativeKernel((const void*)seq_step_kernel, dim3(s->grid), dim3(kThreads), args, 0, ctx->stream));
   return AIG_OK;

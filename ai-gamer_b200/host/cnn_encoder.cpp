@@ -80,9 +80,9 @@ struct aig_cnn {
   bool fused_head = false;
   float sa_b = 0.f;
   bool loaded = false;
-  static constexpr int kGraphs = 4;    // captured forwards, keyed by input pointer
-  aig_graph* graphs[kGraphs] = {nullptr, nullptr, nullptr, nullptr};
-  const uint8_t* graph_ins[kGraphs] = {nullptr, nullptr, nullptr, nullptr};
+  static constexpr int kGraphs = 8;    // captured forwards, keyed by input pointer
+  aig_graph* graphs[kGraphs] = {};
+  const uint8_t* graph_ins[kGraphs] = {};
   int graph_next = 0;
   // pipelined host-buffer steps: private copy stream, two frame slots
   cudaStream_t copy_stream = nullptr;
@@ -514,14 +514,28 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
       aig_graph_destroy(m->graphs[slot]);
       m->graphs[slot] = nullptr;
     }
-    // one eager pass first so that every plan has encoded its tensor maps before capture
+    // one eager pass first so that every plan has encoded its tensor maps before capture; per-launch timing
+    // is suspended for both passes (its event records must not end up inside the graph)
+    const bool prof_was_on = m->prof_on;
+    m->prof_on = false;
     int rc = aig_cnn_forward(m, bgra_dev);
-    if (rc != AIG_OK) return rc;
-    CNN_OK(m, aig_graph_begin(m->ctx));
+    if (rc != AIG_OK) {
+      m->prof_on = prof_was_on;
+      return rc;
+    }
+    rc = aig_graph_begin(m->ctx);
+    if (rc != AIG_OK) {
+      m->prof_on = prof_was_on;
+      return fail(m, rc, aig_last_error(m->ctx));
+    }
     rc = aig_cnn_forward(m, bgra_dev);
     aig_graph* g = nullptr;
-    const int rc2 = aig_graph_end(m->ctx, &g);
-    if (rc != AIG_OK) return rc;
+    const int rc2 = aig_graph_end(m->ctx, &g);  // always ends the capture, also after a failed forward
+    m->prof_on = prof_was_on;
+    if (rc != AIG_OK) {
+      aig_graph_destroy(g);
+      return rc;
+    }
     if (rc2 != AIG_OK) return fail(m, rc2, aig_last_error(m->ctx));
     m->graphs[slot] = g;
     m->graph_ins[slot] = bgra_dev;

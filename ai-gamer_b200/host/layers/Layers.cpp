@@ -3,6 +3,8 @@
 // (common.h:15-34); the C hooks at the end of the file catch them.
 #include "Layers.h"
 
+#include "aig_compat.h"
+
 #include <string.h>
 
 #include <iostream>
@@ -18,18 +20,32 @@ void checkCuda(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
 // common.h:82-86 (CUDAMallocZero)
+// The reference issues every memset and copy on the legacy default stream, where they are ordered with its
+// kernels.  A context of this library may run on another (non-blocking) stream, which the legacy stream does
+// not order against, so each of these helpers finishes its work before it returns.
+void finishLegacyStream() { checkCuda(cudaStreamSynchronize(cudaStreamLegacy), "cudaStreamSynchronize"); }
 template <class T>
 void mallocZero(T** p, size_t count) {
   checkCuda(cudaMalloc(reinterpret_cast<void**>(p), count * sizeof(T)), "cudaMalloc");
   checkCuda(cudaMemset(*p, 0, count * sizeof(T)), "cudaMemset");
+  finishLegacyStream();
+}
+void fillOnes(float* dst, size_t count) {
+  std::vector<float> ones(count, 1.0f);
+  checkCuda(cudaMemcpy(dst, ones.data(), count * sizeof(float), cudaMemcpyHostToDevice), "fill ones");
+  finishLegacyStream();
 }
 // file -> staging buffer -> device, the pattern of every LoadParameters in the reference (e.g. ConvLayer.cpp:96-107)
 void loadArray(std::ifstream& file, unsigned char* buffer, void* dst, size_t bytes) {
   file.read(reinterpret_cast<char*>(buffer), (std::streamsize)bytes);
   if ((size_t)file.gcount() != bytes) throw std::runtime_error("checkpoint truncated");
   checkCuda(cudaMemcpy(dst, buffer, bytes, cudaMemcpyHostToDevice), "cudaMemcpy H2D");
+  finishLegacyStream();
 }
-void saveArray(std::ofstream& file, unsigned char* buffer, const void* src, size_t bytes) {
+// device -> staging buffer -> file (e.g. ConvLayer.cpp:84-95).  `ctx` is synchronised first so that kernels
+// still writing the array on the context's stream have finished.
+void saveArray(aig_ctx* ctx, std::ofstream& file, unsigned char* buffer, const void* src, size_t bytes) {
+  if (ctx) check(ctx, aig_ctx_sync(ctx), "SaveParameters");
   checkCuda(cudaMemcpy(buffer, src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
   file.write(reinterpret_cast<const char*>(buffer), (std::streamsize)bytes);
 }
@@ -100,8 +116,8 @@ void ConvLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   SyncWeights();
 }
 void ConvLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {
-  saveArray(file, buffer, weights_, weightCount_ * sizeof(__half));
-  saveArray(file, buffer, bias_, outC_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, weights_, weightCount_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, bias_, outC_ * sizeof(__half));
 }
 
 // ------------------------------------------------------------------------------------------ ConvLayer3D
@@ -160,6 +176,10 @@ void ConvLayer3D::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   loadArray(file, buffer, bias_, outC_ * sizeof(__half));
   SyncWeights();
 }
+void ConvLayer3D::SaveParameters(std::ofstream& file, unsigned char* buffer) {  // ConvLayer3D.cpp:128-133
+  saveArray(ctx_, file, buffer, weights_, weightCount_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, bias_, outC_ * sizeof(__half));
+}
 
 // ------------------------------------------------------------------------------------------ BatchNorm
 BatchNorm::BatchNorm(cudnnHandle_t cudnnHandle, cudnnBatchNormMode_t bnMode, int batchSize, int channels, int height, int width,
@@ -173,8 +193,7 @@ BatchNorm::BatchNorm(cudnnHandle_t cudnnHandle, cudnnBatchNormMode_t bnMode, int
   paramCount_ = mode_ == CUDNN_BATCHNORM_SPATIAL ? (size_t)c_ : (size_t)c_ * hw_;
   float** arrays[6] = {&bnScale_, &bnBias_, &bnRunningMean_, &bnRunningVar_, &bnSavedMean_, &bnSavedInvVariance_};
   for (float** a : arrays) mallocZero(a, paramCount_);
-  std::vector<float> ones(paramCount_, 1.0f);  // scale = 1 as in BatchNorm.cpp:15-22
-  checkCuda(cudaMemcpy(bnScale_, ones.data(), paramCount_ * sizeof(float), cudaMemcpyHostToDevice), "bn scale init");
+  fillOnes(bnScale_, paramCount_);  // scale = 1 as in BatchNorm.cpp:15-22
   mallocZero(&outData_, (size_t)outNCHW_);
 }
 BatchNorm::~BatchNorm() {
@@ -193,7 +212,7 @@ void BatchNorm::LoadParameters(std::ifstream& file, unsigned char* buffer) {
 }
 void BatchNorm::SaveParameters(std::ofstream& file, unsigned char* buffer) {
   float* arrays[6] = {bnScale_, bnBias_, bnRunningMean_, bnRunningVar_, bnSavedMean_, bnSavedInvVariance_};
-  for (float* a : arrays) saveArray(file, buffer, a, paramCount_ * sizeof(float));
+  for (float* a : arrays) saveArray(ctx_, file, buffer, a, paramCount_ * sizeof(float));
 }
 
 // ------------------------------------------------------------------------------------------ activations
@@ -268,8 +287,8 @@ void FCLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   SyncWeights();
 }
 void FCLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {
-  saveArray(file, buffer, weights_, weightCount_ * sizeof(__half));
-  saveArray(file, buffer, bias_, outC_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, weights_, weightCount_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, bias_, outC_ * sizeof(__half));
 }
 
 // ------------------------------------------------------------------------------------------ ResConvLayer
@@ -329,8 +348,7 @@ LayerNorm::LayerNorm(int batchSize, int channels, int height, int width, const c
   mallocZero(&mean_, (size_t)c_);
   mallocZero(&variance_, (size_t)c_);
   mallocZero(&outData_, (size_t)outNCHW_);
-  std::vector<float> ones(c_, 1.0f);
-  checkCuda(cudaMemcpy(gamma_, ones.data(), c_ * sizeof(float), cudaMemcpyHostToDevice), "gamma init");
+  fillOnes(gamma_, (size_t)c_);
 }
 LayerNorm::~LayerNorm() { cudaFree(gamma_); cudaFree(beta_); cudaFree(mean_); cudaFree(variance_); cudaFree(outData_); }
 __half* LayerNorm::Forward(__half* data) {
@@ -341,6 +359,10 @@ __half* LayerNorm::Forward(__half* data) {
 void LayerNorm::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   loadArray(file, buffer, gamma_, c_ * sizeof(float));
   loadArray(file, buffer, beta_, c_ * sizeof(float));
+}
+void LayerNorm::SaveParameters(std::ofstream& file, unsigned char* buffer) {  // LayerNorm.cpp:50-55
+  saveArray(nullptr, file, buffer, gamma_, c_ * sizeof(float));
+  saveArray(nullptr, file, buffer, beta_, c_ * sizeof(float));
 }
 
 // ------------------------------------------------------------------------------------------ SpatialAttentionLayer
@@ -378,33 +400,55 @@ void SpatialAttentionLayer::LoadParameters(std::ifstream& file, unsigned char* b
   loadArray(file, buffer, queryWeights_, (size_t)inC_ * 9 * sizeof(__half));
   loadArray(file, buffer, valueWeights_, (size_t)inC_ * attC_ * sizeof(__half));
 }
+void SpatialAttentionLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {  // SpatialAttentionLayer.cpp:143-150
+  saveArray(ctx_, file, buffer, keyWeights_, (size_t)inC_ * 9 * sizeof(__half));
+  saveArray(ctx_, file, buffer, queryWeights_, (size_t)inC_ * 9 * sizeof(__half));
+  saveArray(ctx_, file, buffer, valueWeights_, (size_t)inC_ * attC_ * sizeof(__half));
+}
 
 // ------------------------------------------------------------------------------------------ LSTMLayer
-LSTMLayer::LSTMLayer(cudnnHandle_t cudnnHandle, int seqLength, int numLayers, int hiddenSize, int batchSize, int inC, const char* layerName,
-                     bool train)
-    : ctx_(cudnnHandle), seq_(seqLength), layers_(numLayers), hidden_(hiddenSize), batch_(batchSize), inC_(inC) {
+void LSTMLayer::init(const char* layerName, bool train, float clip, int doubleBias, int batchMajor) {
   g_default_ctx = ctx_;
   layerName_ = layerName;
   train_ = train;
-  // LSTMLayer.cpp:14-15: cell clip +-5, two bias vectors (the library default); seq-major tensors
-  check(ctx_, aig_lstm_plan_create(ctx_, seq_, layers_, hidden_, batch_, inC_, 5.0f, 1, 0, &plan_), layerName);
-  weightCount_ = aig_lstm_weight_count(inC_, hidden_, layers_, 1);
+  check(ctx_, aig_lstm_plan_create(ctx_, seq_, layers_, hidden_, batch_, inC_, clip, doubleBias, batchMajor, &plan_), layerName);
+  weightCount_ = aig_lstm_weight_count(inC_, hidden_, layers_, doubleBias);
   mallocZero(&weights_, weightCount_);
   mallocZero(&outData_, (size_t)seq_ * batch_ * hidden_);
+  mallocZero(&hy_, (size_t)layers_ * batch_ * hidden_);
+  mallocZero(&cy_, (size_t)layers_ * batch_ * hidden_);
   outNCHW_ = batch_ * hidden_;
   outDesc_ = {batch_, hidden_, 1, 1};
   check(ctx_, aig_lstm_plan_set_weights(plan_, H(weights_)), layerName);
 }
+// LSTMLayer.cpp:4-40: cell clip +-5 (:15), two bias vectors per gate (the library default), seq-major tensors
+LSTMLayer::LSTMLayer(cudnnHandle_t cudnnHandle, int seqLength, int numLayers, int hiddenSize, int batchSize, int inC, const char* layerName,
+                     bool train)
+    : ctx_(cudnnHandle), seq_(seqLength), layers_(numLayers), hidden_(hiddenSize), batch_(batchSize), inC_(inC), v8_(false) {
+  init(layerName, train, 5.0f, 1, 0);
+}
+// LSTMLayerv8.cpp:4-9: CUDNN_RNN_SINGLE_INP_BIAS, no cell clip, CUDNN_RNN_DATA_LAYOUT_BATCH_MAJOR_UNPACKED
+LSTMLayer::LSTMLayer(cudnnHandle_t cudnnHandle, cublasHandle_t, int batchSize, int seqLength, int inCHW, int outC, int numLayers,
+                     const char* layerName, bool train)
+    : ctx_(cudnnHandle), seq_(seqLength), layers_(numLayers), hidden_(outC), batch_(batchSize), inC_(inCHW), v8_(true) {
+  init(layerName, train, 0.0f, 0, 1);
+}
 LSTMLayer::~LSTMLayer() {
   aig_lstm_plan_destroy(plan_);
-  cudaFree(weights_); cudaFree(outData_);
+  cudaFree(weights_); cudaFree(outData_); cudaFree(hy_); cudaFree(cy_);
 }
 __half* LSTMLayer::Forward(__half* data) {
-  check(ctx_, aig_lstm_forward(plan_, H(data), H(outData_), nullptr, nullptr, 0), layerName_);
+  check(ctx_, aig_lstm_forward(plan_, H(data), H(outData_), H(hy_), H(cy_), 0), layerName_);
+  if (v8_) return hy_;  // LSTMLayerv8.cpp:81: the final hidden state of every layer, [layers][batch][hidden]
   return outData_ + (size_t)(seq_ - 1) * batch_ * hidden_;  // LSTMLayer.cpp:103: the last step's rows
 }
 void LSTMLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
+  // the input projection keeps its own packed copy of W and the folded biases: refresh it
+  check(ctx_, aig_lstm_plan_set_weights(plan_, H(weights_)), layerName_);
+}
+void LSTMLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {  // LSTMLayer.cpp:139-142
+  saveArray(ctx_, file, buffer, weights_, weightCount_ * sizeof(__half));
 }
 
 // ------------------------------------------------------------------------------------------ MultiHeadAttentionLayer
@@ -438,6 +482,13 @@ void MultiHeadAttentionLayer::LoadParameters(std::ifstream& file, unsigned char*
   loadArray(file, buffer, wv_, bytes);
   loadArray(file, buffer, wo_, bytes);
   check(ctx_, aig_mha_plan_set_weights(plan_, H(wq_), H(wk_), H(wv_), H(wo_)), layerName_);
+}
+void MultiHeadAttentionLayer::SaveParameters(std::ofstream& file, unsigned char* buffer) {  // MHALayer.cpp:191-200
+  const size_t bytes = (size_t)embed_ * embed_ * sizeof(__half);
+  saveArray(ctx_, file, buffer, wq_, bytes);
+  saveArray(ctx_, file, buffer, wk_, bytes);
+  saveArray(ctx_, file, buffer, wv_, bytes);
+  saveArray(ctx_, file, buffer, wo_, bytes);
 }
 
 // ------------------------------------------------------------------------------------------ NN
@@ -525,6 +576,32 @@ int aig_refnn_forward(void* nn, aig_half* x_nchw_dev, const aig_half** out_dev) 
     return AIG_ERR_CUDA;
   }
 }
+// cudnnCreate as the reference calls it (Infer.cpp:76-79): a handle on the legacy default stream
+int aig_compat_handle_create(aig_ctx** out) { return out ? cudnnCreate(out) : AIG_ERR_INVALID; }
+
+// The loop body of Infer::Inference (Infer.cpp:103-112) written with the reference's own names and nothing
+// added: ARGBtoRGBplanar (inside GrabFrameInt8, NvDisplayCap.h:70-87), ConvertAndNormalize, NN::Forward,
+// ConvertHalfToFloat, cudaMemcpy device-to-host.  No stream or event call appears, as in the reference: the
+// order comes from the legacy default stream, so `nn` must have been built on a handle from
+// aig_compat_handle_create (or cudnnCreate of cudnn_shim.h).  planar_dev: 3*w*h bytes, frame_half_dev: 3*w*h
+// halves, out_f32_dev / out_host: numCtrls_ floats.
+int aig_refnn_infer_frame(void* nn, unsigned char* bgra_dev, unsigned char* planar_dev, aig_half* frame_half_dev, float* out_f32_dev,
+                          float* out_host) {
+  if (!nn || !bgra_dev || !planar_dev || !frame_half_dev || !out_f32_dev || !out_host) return AIG_ERR_INVALID;
+  NN* net = static_cast<NN*>(nn);
+  const int n = net->inWidth_ * net->inHeight_;
+  try {
+    if (ARGBtoRGBplanar(bgra_dev, planar_dev, n) != cudaSuccess) throw std::runtime_error("ARGBtoRGBplanar failed");
+    ConvertAndNormalize(reinterpret_cast<__half*>(frame_half_dev), planar_dev, (size_t)3 * n);
+    __half* out = net->Forward(reinterpret_cast<__half*>(frame_half_dev));
+    ConvertHalfToFloat(out, out_f32_dev, numCtrls_);
+    checkCuda(cudaMemcpy(out_host, out_f32_dev, numCtrls_ * sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy D2H");
+    return aig_compat_last_status();
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_CUDA;
+  }
+}
 int aig_refnn_input_size(void* nn, int* w, int* h) {
   if (!nn) return AIG_ERR_INVALID;
   if (w) *w = static_cast<NN*>(nn)->inWidth_;
@@ -533,6 +610,89 @@ int aig_refnn_input_size(void* nn, int* w, int* h) {
 }
 int aig_refnn_destroy(void* nn) {
   delete static_cast<NN*>(nn);
+  return AIG_OK;
+}
+
+// One hook per use of a layer object, for every class of Layers.h: `kind` is the class name ("LSTMLayerV8" picks the
+// LSTMLayerv8.h:10 constructor) and iargs are the constructor's integer arguments in declaration order (the
+// int* size arguments are passed by value).  Handle-less classes run on `ctx` too.
+int aig_layer_create(aig_ctx* ctx, const char* kind, const int* a, int n, void** out) {
+  if (!ctx || !kind || !a || !out) return AIG_ERR_INVALID;
+  *out = nullptr;
+  const std::string k(kind);
+  auto need = [&](int want) {
+    if (n != want) throw std::runtime_error(k + ": expected " + std::to_string(want) + " integer arguments");
+  };
+  try {
+    aigSetDefaultContext(ctx);
+    constexpr float wd = 0.000001f;
+    Layer* L = nullptr;
+    if (k == "ConvLayer") { need(8); int h = a[6], w = a[7]; L = new ConvLayer(ctx, a[0], a[1], a[2], a[3], a[4], a[5], &h, &w, "ConvLayer", false, wd); }
+    else if (k == "ConvLayer3D") { need(12); int w = a[9], h = a[10], d = a[11]; L = new ConvLayer3D(ctx, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8], &w, &h, &d, "ConvLayer3D", false, wd); }
+    else if (k == "BatchNorm") { need(5); L = new BatchNorm(ctx, a[0] ? CUDNN_BATCHNORM_SPATIAL : CUDNN_BATCHNORM_PER_ACTIVATION, a[1], a[2], a[3], a[4], "BatchNorm", false, wd); }
+    else if (k == "Activate") { need(4); L = new Activate(ctx, CUDNN_ACTIVATION_RELU, 1.0, a[0], a[1], a[2], a[3], "Activate"); }
+    else if (k == "Swish") { need(1); L = new Swish(a[0], "Swish"); }
+    else if (k == "LeakyReLU") { need(1); L = new LeakyReLU(a[0], "LeakyReLU"); }
+    else if (k == "Sigmoid") { need(3); L = new Sigmoid(a[0], a[1], a[2], "Sigmoid"); }
+    else if (k == "FCLayer") { need(3); L = new FCLayer(ctx, ctx, a[0], a[1], a[2], "FCLayer", false, wd); }
+    else if (k == "ResConvLayer") { need(5); int h = a[3], w = a[4]; L = new ResConvLayer(ctx, a[0], a[1], a[2], &h, &w, "ResConvLayer", false); }
+    else if (k == "LayerNorm") { need(4); L = new LayerNorm(a[0], a[1], a[2], a[3], "LayerNorm", wd); }
+    else if (k == "SpatialAttentionLayer") { need(5); L = new SpatialAttentionLayer(ctx, a[0], a[1], a[2], a[3], a[4], "SpatialAttention", false, wd); }
+    else if (k == "LSTMLayer") { need(5); L = new LSTMLayer(ctx, a[0], a[1], a[2], a[3], a[4], "LSTM", false); }
+    else if (k == "LSTMLayerV8") { need(5); L = new LSTMLayer(ctx, ctx, a[0], a[1], a[2], a[3], a[4], "LSTM", false); }
+    else if (k == "MultiHeadAttentionLayer") { need(4); L = new MultiHeadAttentionLayer(ctx, ctx, a[0], a[1], a[2], a[3], "MHA", false, wd); }
+    else if (k == "Dropout") { need(4); L = new Dropout(ctx, 0.5f, a[0], a[1], a[2], a[3], "Dropout", false); }
+    else throw std::runtime_error("unknown layer class " + k);
+    *out = L;
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_INVALID;
+  }
+}
+// Layer::Forward: x and *out_dev are device pointers in the layer's own (reference) layout
+int aig_layer_forward(void* layer, aig_half* x, const aig_half** out_dev) {
+  if (!layer || !x || !out_dev) return AIG_ERR_INVALID;
+  try {
+    *out_dev = reinterpret_cast<const aig_half*>(static_cast<Layer*>(layer)->Forward(reinterpret_cast<__half*>(x)));
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_CUDA;
+  }
+}
+size_t aig_layer_param_bytes(void* layer) { return layer ? static_cast<Layer*>(layer)->GetParameterSize() : 0; }
+int aig_layer_out_count(void* layer) { return layer ? static_cast<Layer*>(layer)->outNCHW_ : 0; }
+// Layer::LoadParameters / SaveParameters on a file that holds exactly this layer's payload, through a pinned
+// staging buffer of GetParameterSize() bytes like NN.cpp:62-75 and :113-128 provide.
+static int layer_file_io(void* layer, const char* path, bool save) {
+  if (!layer || !path) return AIG_ERR_INVALID;
+  Layer* L = static_cast<Layer*>(layer);
+  unsigned char* buffer = nullptr;
+  const size_t n = L->GetParameterSize();
+  if (cudaMallocHost(reinterpret_cast<void**>(&buffer), n ? n : 1) != cudaSuccess) return AIG_ERR_CUDA;
+  int rc = AIG_OK;
+  try {
+    if (save) {
+      std::ofstream f(path, std::ios::binary);
+      if (!f.is_open()) throw std::runtime_error(std::string("cannot write ") + path);
+      L->SaveParameters(f, buffer);
+    } else {
+      std::ifstream f(path, std::ios::binary);
+      if (!f.is_open()) throw std::runtime_error(std::string("cannot read ") + path);
+      L->LoadParameters(f, buffer);
+    }
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    rc = AIG_ERR_IO;
+  }
+  cudaFreeHost(buffer);
+  return rc;
+}
+int aig_layer_load_file(void* layer, const char* path) { return layer_file_io(layer, path, false); }
+int aig_layer_save_file(void* layer, const char* path) { return layer_file_io(layer, path, true); }
+int aig_layer_destroy(void* layer) {
+  delete static_cast<Layer*>(layer);
   return AIG_OK;
 }
 

@@ -74,6 +74,7 @@ class ConvLayer3D final : public Layer {
   ~ConvLayer3D() override;
   __half* Forward(__half* data) override;
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
+  void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return (weightCount_ + outC_) * sizeof(__half); }
   void SyncWeights();
   __half *weights_ = nullptr, *bias_ = nullptr, *outData_ = nullptr;
@@ -185,6 +186,7 @@ class LayerNorm final : public Layer {
   ~LayerNorm() override;
   __half* Forward(__half* data) override;
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
+  void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return 2 * (size_t)c_ * sizeof(float); }
   float *gamma_ = nullptr, *beta_ = nullptr, *mean_ = nullptr, *variance_ = nullptr;
   __half* outData_ = nullptr;
@@ -203,6 +205,7 @@ class SpatialAttentionLayer final : public Layer {
   ~SpatialAttentionLayer() override;
   __half* Forward(__half* data) override;
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
+  void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return ((size_t)2 * inC_ * 9 + (size_t)inC_ * attC_) * sizeof(__half); }
   __half *keyWeights_ = nullptr, *queryWeights_ = nullptr, *valueWeights_ = nullptr, *keyMap_ = nullptr, *queryMap_ = nullptr,
          *valueMap_ = nullptr, *attentionScores_ = nullptr, *outData_ = nullptr;
@@ -213,21 +216,32 @@ class SpatialAttentionLayer final : public Layer {
   int attC_, batchSize_, inC_, inH_, inW_;
 };
 
-// LSTMLayer.h:8 / LSTMLayer.cpp:75-104 (seq-major input, returns the last step's rows)
+// The reference has two files that both define `LSTMLayer` (they cannot be linked together); here both
+// constructor forms live on one class.
+//   LSTMLayer.h:8 / LSTMLayer.cpp:75-104 (cuDNN 7 API): seq-major x [T][B][inC], two bias vectors, cell clip 5,
+//     Forward returns the last step's rows [B][hidden] inside outData_ [T][B][hidden].
+//   LSTMLayerv8.h:10 / LSTMLayerv8.cpp:78-82 (cuDNN 8 API): batch-major x [B][T][inCHW], one bias vector, no
+//     clip, Forward returns hy_ = the final hidden state of every layer [layers][B][outC]; outData_ holds the
+//     whole output sequence [B][T][outC] (the reference's own outData_ is sized for one step only).
 class LSTMLayer final : public Layer {
  public:
   LSTMLayer(cudnnHandle_t cudnnHandle, int seqLength, int numLayers, int hiddenSize, int batchSize, int inC, const char* layerName,
             bool train);
+  LSTMLayer(cudnnHandle_t cudnnHandle, cublasHandle_t cublasHandle, int batchSize, int seqLength, int inCHW, int outC, int numLayers,
+            const char* layerName, bool train);
   ~LSTMLayer() override;
   __half* Forward(__half* data) override;
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
+  void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return weightCount_ * sizeof(__half); }
-  __half *weights_ = nullptr, *outData_ = nullptr;
+  __half *weights_ = nullptr, *outData_ = nullptr, *hy_ = nullptr, *cy_ = nullptr;
 
  private:
+  void init(const char* layerName, bool train, float clip, int doubleBias, int batchMajor);
   aig_ctx* ctx_;
   aig_lstm_plan* plan_ = nullptr;
   int seq_, layers_, hidden_, batch_, inC_;
+  bool v8_;
 };
 
 // MHALayer.h:9 / MHALayer.cpp:128-146
@@ -238,6 +252,7 @@ class MultiHeadAttentionLayer final : public Layer {
   ~MultiHeadAttentionLayer() override;
   __half* Forward(__half* data) override;
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
+  void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return 4 * (size_t)embed_ * embed_ * sizeof(__half); }
   __half *wq_ = nullptr, *wk_ = nullptr, *wv_ = nullptr, *wo_ = nullptr, *outData_ = nullptr;
 

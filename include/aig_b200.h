@@ -47,6 +47,12 @@ void* aig_ctx_stream(aig_ctx* ctx);
  * bounded device-side wait).  The device error word is cleared. */
 int aig_ctx_sync(aig_ctx* ctx);
 const char* aig_last_error(aig_ctx* ctx);
+/* Self-test of the time-out path every kernel of this library shares (no counterpart in the reference, whose
+ * kernels never wait on one another).  Launches one small kernel whose only work is a bounded wait on a
+ * barrier that nobody arrives at; after `limit_cycles` SM clocks (at most 2e8, about 0.1 s) the wait gives up,
+ * records an error code for the context and the kernel returns normally.  The next aig_ctx_sync then returns
+ * AIG_ERR_TIMEOUT once, and the context stays usable. */
+int aig_selftest_expiring_wait(aig_ctx* ctx, long long limit_cycles);
 int aig_device_sm_count(aig_ctx* ctx);
 /* Asynchronous copy on the context's stream (any direction; the checkCUDA(cudaMemcpy(...)) calls of
  * the reference's LoadParameters/SaveParameters and Infer.cpp:112). */

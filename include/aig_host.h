@@ -148,8 +148,35 @@ const aig_half* aig_c3d_features(aig_c3d* m);   /* [batch][widths[n_layers]*4] p
 int aig_refnn_create(aig_ctx* ctx, int w, int h, const char* ckpt_path, void** out);
 int aig_refnn_forward(void* nn, aig_half* x_nchw_dev, const aig_half** out_dev);
 int aig_refnn_input_size(void* nn, int* w, int* h);
+/* cudnnCreate / cublasCreate as Infer.cpp:76-79 calls them: a context bound to the legacy default stream, on
+ * which the reference's launchers (aig_compat.h), its layers and its cudaMemcpy calls run in issue order. */
+int aig_compat_handle_create(aig_ctx** out);
+/* The loop body of Infer::Inference (Infer.cpp:103-112) through the reference's own names, with no
+ * synchronisation added: ARGBtoRGBplanar, ConvertAndNormalize, NN::Forward, ConvertHalfToFloat, cudaMemcpy to
+ * the host.  `nn` must live on a handle from aig_compat_handle_create.  bgra_dev [h][w][4] bytes; planar_dev
+ * 3*w*h bytes and frame_half_dev 3*w*h halves are scratch; out_f32_dev and out_host hold 16 floats. */
+int aig_refnn_infer_frame(void* nn, unsigned char* bgra_dev, unsigned char* planar_dev, aig_half* frame_half_dev,
+                          float* out_f32_dev, float* out_host);
 int aig_refnn_destroy(void* nn);
 const char* aig_layers_last_error(void);
+
+/* Any single layer class of Layers.h through C: `kind` is the class name -- ConvLayer (ConvLayer.h:8),
+ * ConvLayer3D (ConvLayer3D.h:8), BatchNorm (BatchNorm.h:7; first integer 1 = spatial, 0 = per activation),
+ * Activate (Activate.h:7), Swish (Swish.h:6), LeakyReLU (LeakyReLU.h:7), Sigmoid (Sigmoid.h:5), FCLayer
+ * (FCLayer.h:8), ResConvLayer (ResConvLayer.h:12), LayerNorm (LayerNorm.h:6), SpatialAttentionLayer
+ * (SpatialAttentionLayer.h:7), LSTMLayer (LSTMLayer.h:8), LSTMLayerV8 (the LSTMLayerv8.h:10 constructor form),
+ * MultiHeadAttentionLayer (MHALayer.h:9), Dropout (Dropout.h:8) -- and iargs are that constructor's integer
+ * arguments in declaration order (sizes that the reference passes as int* go by value).
+ * forward = Layer::Forward (Layer.h:7); load/save = Layer::LoadParameters / SaveParameters (Layer.h:10-11) on a
+ * file that holds exactly the layer's payload; param_bytes = GetParameterSize() (the staging size, Layer.h:14);
+ * out_count = outNCHW_ (Layer.h:18). */
+int aig_layer_create(aig_ctx* ctx, const char* kind, const int* iargs, int n_iargs, void** out);
+int aig_layer_forward(void* layer, aig_half* x_dev, const aig_half** out_dev);
+int aig_layer_load_file(void* layer, const char* path);
+int aig_layer_save_file(void* layer, const char* path);
+size_t aig_layer_param_bytes(void* layer);
+int aig_layer_out_count(void* layer);
+int aig_layer_destroy(void* layer);
 
 #ifdef __cplusplus
 }

@@ -51,6 +51,27 @@ def test_library_exports_every_declared_symbol(pkg):
     assert not missing, "declared in include/*.h but not exported: %s" % missing
 
 
+def exported_symbols(path):
+    """Dynamic, defined function symbols of a shared library (`nm -D --defined-only`)."""
+    import subprocess
+
+    out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+    return sorted({ln.split()[2] for ln in out.splitlines() if len(ln.split()) == 3 and ln.split()[1] in "TW"})
+
+
+def test_every_exported_entry_point_is_declared_in_a_header(pkg):
+    """The reverse direction: nothing with the library's prefix, and none of the reference's launcher names, is
+    exported without a declaration in include/*.h (no undocumented back doors, no debugging hooks)."""
+    declared = set(declared_symbols())
+    text = open(os.path.join(ROOT, "include", "aig_compat.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared |= set(re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\(", text))
+    exported = [n for n in exported_symbols(pkg.LIB_PATH) if n.startswith("aig_") or n in COMPAT_NAMES]
+    assert len(exported) > 100
+    undeclared = [n for n in exported if n not in declared]
+    assert not undeclared, "exported but declared in no header: %s" % undeclared
+
+
 def test_python_binding_declares_every_symbol(pkg):
     missing = [n for n in declared_symbols() if n not in pkg.SIGNATURES]
     assert not missing, "no ctypes signature for: %s" % missing

@@ -1,0 +1,219 @@
+"""GPU parity at the benchmark configurations' own sizes.
+
+The CUDA path runs every configuration at its full batch; the CPU oracle runs on all of it where that
+takes seconds (the 256-frame encoder batch) and on a sample of the independent units (clips, frame
+sequences) where it does not.  Units are independent on this path, so a sampled unit's outputs must
+match the oracle whatever batch it travelled in.  Tolerances: 2e-2 relative on the key/mouse outputs of
+the feed-forward encoders and on the key/mouse logits of the recurrent configurations (fp16 storage, fp32
+accumulation against the oracle's double accumulation; 64 recurrent steps carry their state in fp16),
+button decisions equal in at least 99.9 % of the cases, mouse deltas within one count.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from oracle import pipelines as PL
+
+gpu = pytest.mark.gpu
+TOL = 2e-2
+WIDTHS = (32, 64, 128, 256, 256)
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from tests import gpu_util as U
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    O.set_threads(__import__("os").cpu_count() or 1)
+    return U
+
+
+def _logit_err(got, want_logits, n_sig=16):
+    """Error on the key/mouse logits, relative to max(|logit|, rms of the logits): the outputs are mapped back
+    through the inverse sigmoid (buttons) and inverse tanh (mouse axes); saturated outputs (|logit| > 4), where
+    an fp16 output no longer resolves the logit, are left out."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want_logits, np.float64)
+    p = np.clip(got[..., :n_sig], 1e-6, 1 - 1e-6)
+    lg = np.concatenate([np.log(p / (1 - p)), np.arctanh(np.clip(got[..., n_sig:], -1 + 1e-6, 1 - 1e-6))], axis=-1)
+    rms = float(np.sqrt(np.mean(want * want)))
+    use = np.abs(want) < 4.0
+    return float((np.abs(lg - want) / np.maximum(np.abs(want), rms))[use].max())
+
+
+def _check_actions(got, want, n_out=18, n_sig=16, min_agree=0.999):
+    """Infer.cpp:8-57 decisions on both sides: buttons must agree in >= min_agree of all decisions (and in
+    every decision whose oracle value is not within 2e-3 of the threshold), mouse deltas within one count."""
+    a_got, a_want = O.actions(got, n_out, n_sig), O.actions(want, n_out, n_sig)
+    same = a_got[:, :n_sig] == a_want[:, :n_sig]
+    clear = np.abs(want[:, :n_sig] - 0.5) > 2e-3
+    assert same[clear].all(), "a button decision away from the threshold differs"
+    assert same.mean() >= min_agree, "button agreement %.5f over %d decisions" % (same.mean(), same.size)
+    assert np.abs(a_got[:, n_sig:] - a_want[:, n_sig:]).max() <= 1
+    return float(same.mean()), int(same.size)
+
+
+@gpu
+def test_frame_encoder_all_256_frames_against_the_oracle(env):
+    """The headline workload itself: 256 BGRA frames of 144x256 in one batch, the oracle on every frame."""
+    U = env
+    c, pk = U.ctx(), U.pkg()
+    B, H, W = 256, 144, 256
+    params = PL.make_cnn_params(4, widths=WIDTHS, trivial=False)
+    frames = PL.make_frames(11, B, H, W)
+    enc = pk.CnnEncoder(c, B, H, W, widths=WIDTHS)
+    enc.load_bytes(PL.serialize_cnn_checkpoint(params, W, H))
+    enc.forward(U.dev(frames))
+    c.sync()
+    got = U.host(enc.outputs_f32())
+    enc.close()
+    _, _, want = PL.cnn_forward(params, frames)
+    want = want.astype(np.float32)
+    assert U.rel_err(got, want, 0.05).max() < TOL
+    agree, n = _check_actions(got, want)
+    assert n == 256 * 16
+    print("frame encoder: %d button decisions, agreement %.5f, max rel err %.2e" % (n, agree, U.rel_err(got, want, 0.05).max()))
+
+
+@gpu
+def test_clip_encoder_full_size(env):
+    """Temporal encoder at its configuration: 16 clips of 8 x 144 x 256 (ConvLayer3D.cpp:106-111 three times,
+    channels 3 -> 32 -> 64 -> 128); the oracle on the first and the last clip."""
+    U = env
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    B, D, H, W = 16, 8, 144, 256
+    p = PL.make_conv3d_params(9, trivial=False)
+    clips = PL.make_clips(9, B, D, H, W)
+    enc = R.ClipEncoder(U.ctx(), B, D, H, W)
+    enc.load_bytes(PL.serialize_conv3d_params(p))
+    enc.forward(U.dev(clips))
+    got_feat = U.host(enc.features()).astype(np.float32)
+    got = U.host(enc.outputs_f32())
+    enc.forward(U.dev(clips))
+    assert np.array_equal(U.host(enc.outputs_f32()), got), "two runs on the same clips differ"
+    enc.close()
+    pick = [0, B - 1]
+    feat, _, want = PL.conv3d_forward(p, clips[pick])
+    want = want.astype(np.float32)
+    assert U.scaled_err(got_feat[pick], feat.astype(np.float32)) < 1e-2
+    assert U.rel_err(got[pick], want, 0.05).max() < TOL
+    _check_actions(got[pick], want)
+    assert np.isfinite(got).all()
+
+
+@gpu
+def test_sequence_head_full_size(env):
+    """Sequence head at its configuration: 128 sequences x 64 steps x 512, two LSTM layers
+    (LSTMLayer.cpp:75-104), 8 heads x 64 causal attention with rotary embedding (MHALayer.cpp:128-146),
+    row LayerNorm, FC; the oracle on four of the sequences, every one of their 64 steps."""
+    U = env
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    B, T, d, heads = 128, 64, 512, 8
+    p = PL.make_seq_params(12, d=d, hid=d, layers=2, heads=heads)
+    emb = PL.make_embeddings(12, T, B, d)                                  # [T][B][d]
+    head = R.SeqHead(U.ctx(), B, T, in_c=d, hidden=d, layers=2, heads=heads, rope_base=10000.0, window=0)
+    head.load_bytes(PL.serialize_seq_params(p))
+    head.forward(U.dev(np.ascontiguousarray(emb.transpose(1, 0, 2))))
+    got_y = U.host(head.lstm_output()).astype(np.float32)                  # [B][T][d]
+    got = U.host(head.outputs_f32())                                       # [B][T][n_out]
+    head.close()
+    pick = [0, 41, 90, 127]
+    y, _, logits, want = PL.seq_forward(p, np.ascontiguousarray(emb[:, pick]), rope_base=10000.0, window=0)
+    want = want.astype(np.float32)
+    err_y = np.abs(got_y[pick] - y.transpose(1, 0, 2).astype(np.float32)).max()
+    assert err_y < 8e-3, "LSTM output after 64 steps: max |h - oracle| = %.4g" % err_y
+    # 64 recurrent steps in fp16 state, then LayerNorm: the tolerance is the stated one, on the logits
+    err_l = _logit_err(got[pick], logits)
+    assert err_l < TOL, "logits: max relative error %.4g" % err_l
+    assert np.abs(got[pick] - want).max() < 5e-3
+    _check_actions(got[pick].reshape(-1, 18), want.reshape(-1, 18))
+    assert np.isfinite(got).all()
+
+
+@gpu
+def test_sequence_head_streaming_128_sequences_ring_wraps(env):
+    """The batched streaming step (128 sequences, the per-operator path) for 80 steps over a 64-slot ring
+    cache: equal to the oracle's sliding-window forward on two of the sequences, before and after the wrap."""
+    U = env
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    B, T, d, heads, window = 128, 80, 512, 8, 64
+    p = PL.make_seq_params(13, d=d, hid=d, layers=2, heads=heads)
+    emb = PL.make_embeddings(13, T, B, d)
+    head = R.SeqHead(U.ctx(), B, window, in_c=d, hidden=d, layers=2, heads=heads, rope_base=10000.0, window=window)
+    head.load_bytes(PL.serialize_seq_params(p))
+    pick = [3, 126]
+    outs = []
+    for t in range(T):
+        head.step(U.dev(np.ascontiguousarray(emb[t])))
+        outs.append(U.host(head.outputs_f32(step=True))[pick])
+    head.close()
+    got = np.stack(outs, axis=1)                                           # [2][T][n_out]
+    _, _, logits, want = PL.seq_forward(p, np.ascontiguousarray(emb[:, pick]), rope_base=10000.0, window=window)
+    want = want.astype(np.float32)
+    assert _logit_err(got[:, :window], logits[:, :window]) < TOL
+    assert _logit_err(got[:, window:], logits[:, window:]) < TOL, "outputs drift once the ring cache wraps"
+    assert np.abs(got - want).max() < 5e-3
+
+
+@gpu
+def test_streaming_agent_full_geometry(env):
+    """The whole agent at its configuration (Infer.cpp:96-114 loop body): full 144x256 encoder -> FC 256->512
+    -> 2 x LSTM-512 with carried state -> 8 x 64 attention over a 64-slot ring -> LayerNorm -> FC, one frame
+    per call for 80 frames at batch 1 (the one-kernel step), so the ring wraps; then 128 sequences per call
+    (the batched path) for a few frames with the oracle on the first and the last sequence."""
+    U = env
+    import torch
+
+    U.pkg()
+    from ai_gamer_b200 import runners as R
+
+    H, W, d, heads, window = 144, 256, 512, 8, 64
+    p = PL.make_agent_params(5, widths=WIDTHS, d=d, layers=2, heads=heads)
+    blob = PL.serialize_agent_params(p, W, H)
+
+    def oracle(frames_tb):                                                  # [T][B][H][W][4] -> logits, outputs [B][T][n_out]
+        emb = np.stack([O.fc(PL.cnn_forward(p["cnn"], f)[0], p["bw"], p["bb"]) for f in frames_tb])
+        r = PL.seq_forward(p["seq"], emb, rope_base=10000.0, window=window)
+        return r[2], r[3].astype(np.float32)
+
+    # ---- batch 1, 80 frames
+    T = 80
+    frames = PL.make_frames(500, T, H, W)[:, None]                          # [T][1][H][W][4]
+    agent = R.Agent(U.ctx(), 1, H, W, widths=WIDTHS, d=d, layers=2, heads=heads, window=window)
+    assert len(blob) == agent.param_bytes()
+    agent.load_bytes(blob)
+    out_h = torch.empty((1, 18), dtype=torch.float32).pin_memory()
+    outs = []
+    for t in range(T):
+        agent.step_host(torch.from_numpy(frames[t]).pin_memory(), out_h)
+        outs.append(out_h.numpy().copy())
+    agent.close()
+    got = np.stack(outs, axis=1)                                            # [1][T][n_out]
+    logits, want = oracle(frames)
+    assert _logit_err(got, logits) < TOL
+    assert np.abs(got - want).max() < 5e-3
+    _check_actions(got.reshape(-1, 18), want.reshape(-1, 18))
+    # ---- 128 sequences per call
+    B, T = 128, 4
+    frames = PL.make_frames(600, T * B, H, W).reshape(T, B, H, W, 4)
+    agent = R.Agent(U.ctx(), B, H, W, widths=WIDTHS, d=d, layers=2, heads=heads, window=window)
+    agent.load_bytes(blob)
+    outs = []
+    for t in range(T):
+        agent.step(U.dev(frames[t]))
+        outs.append(U.host(agent.outputs_f32()))
+    agent.close()
+    got = np.stack(outs, axis=1)                                            # [B][T][n_out]
+    pick = [0, B - 1]
+    logits, want = oracle(np.ascontiguousarray(frames[:, pick]))
+    assert _logit_err(got[pick], logits) < TOL
+    assert np.abs(got[pick] - want).max() < 5e-3
+    assert np.isfinite(got).all()

@@ -123,14 +123,16 @@ def test_clip_encoder_matches_oracle(env):
 
 
 @gpu
-def test_fc_layernorm_swish_twin(env):
-    """The CPU-runnable configuration's GPU twin: FC 1024->1024, row LayerNorm (eps 1e-5), Swish on 32 rows."""
+@pytest.mark.parametrize("rows", [32, 64])
+def test_fc_layernorm_swish_twin(env, rows):
+    """The CPU-runnable configuration's GPU twin: FC 1024->1024, row LayerNorm (eps 1e-5), Swish; 64 rows is the
+    configuration's own batch."""
     U = env
     pk = U.pkg()
     import torch
 
     c = U.ctx()
-    rows, d = 32, 1024
+    d = 1024
     p = PL.make_fc_ln_params(11, d, d)
     x = np.random.default_rng(11).standard_normal((rows, d)).astype(np.float16)
     want = PL.fc_ln_swish_forward(p, x)
