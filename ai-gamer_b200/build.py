@@ -44,6 +44,9 @@ def build(force=False, verbose=False, defines=()):
     """defines: extra -D macros (AIG_TUNING compiles the kernels' timeline stamps and tile-search switches in)."""
     os.makedirs(OBJ, exist_ok=True)
     extra = ["-D" + d for d in defines]
+    stamp = os.path.join(OBJ, ".defines")  # objects built with other macros are stale
+    if not os.path.exists(stamp) or open(stamp).read() != " ".join(extra):
+        force = True
     hdr_t = _newest_header()
     jobs = []
     objs = []
@@ -67,6 +70,8 @@ def build(force=False, verbose=False, defines=()):
             list(ex.map(run, jobs))
     if jobs or not os.path.exists(LIB):
         run(["nvcc", "-shared", "-o", LIB] + objs + ["-lcudart"])
+    with open(stamp, "w") as f:
+        f.write(" ".join(extra))
     return LIB
 
 

@@ -628,15 +628,23 @@ __device__ __forceinline__ void pconv_item(const PconvParams& p, int item, int& 
   } while (0)
 #endif
 
-constexpr int kPconvThreads = 352;  // patch producer, MMA issuer, 8 epilogue warps, weight producer
-constexpr int kWeightWarp = 10;
+// Warp roles: warp 0 = patch producer, warp 1 = MMA issuer + TMEM owner, warp 2 = weight producer, warp 3 idle,
+// warps 4 .. 4+EW-1 = epilogue.  EW = 8: two warps per TMEM lane quarter, each half of a tile's columns.
+// EW = 16: two such teams; with several sub-tiles per tile the teams take alternate sub-tiles, with one they
+// take alternate tiles, so twice as many warps hide the latencies of the epilogue's TMEM loads, special-function
+// operations and global accesses.
+constexpr int kPconvProducerWarps = 4;
+constexpr int kWeightWarp = 2;
+__host__ __device__ constexpr int pconv_threads(int ew) { return (kPconvProducerWarps + ew) * 32; }
 
-template <int NT, int MS, bool WRES>
-__global__ void __launch_bounds__(kPconvThreads, 1)
+template <int NT, int MS, bool WRES, int EW>
+__global__ void __launch_bounds__(pconv_threads(EW), 1)
 pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapAT, const __grid_constant__ CUtensorMap tmapB,
              const PconvParams p) {
   constexpr int kM = MS * kTileM;
   constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
+  constexpr int kPconvThreads = pconv_threads(EW);
+  constexpr int kArrivals = (EW == 16 && MS == 1) ? 8 : EW;  // epilogue warps that drain one accumulator buffer
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -656,7 +664,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint32_t* s_tab = s_tmem + 4;
-  uint8_t* s_stage = sm + tail + 5120 + (threadIdx.x >> 5) * 2048;  // per-warp staging tile of the epilogue (warps 2..9 use it)
+  uint8_t* s_stage = sm + tail + 5120 + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;  // per-warp staging tile of the epilogue warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   griddep_launch_dependents();  // the next launch may set itself up and prefetch its weights under this one
@@ -674,7 +682,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
     for (int a = 0; a < 4; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 8);
+      mbar_init(bar_tempty + 8 * a, kArrivals);
     }
     const int nw = WRES ? 1 : p.w_stages;
     for (int s = 0; s < nw; ++s) {
@@ -835,10 +843,12 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 4);
       }
     }
-  } else if (warp < kWeightWarp) {
-    // ------------------------------------------------------------------ epilogue (warps 2..9)
+  } else if (warp >= kPconvProducerWarps) {
+    // ------------------------------------------------------------------ epilogue
+    const int ew = warp - kPconvProducerWarps;
     const int q4 = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (ew >> 2) & 1;
+    const int team = ew >> 3;  // 0 when EW == 8
     const int col_lo = half * (NT / 2), col_hi = col_lo + NT / 2;
     const int row_in_tile = q4 * 32 + lane;
     int cnt = 0;
@@ -875,6 +885,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       pconv_item(p, item, m_tile, n_lo, n_hi);
       if (p.dist_n) pos0 = pos_of((long long)m_tile * kM + row_in_tile);
       for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
+        if (EW == 16 && MS == 1 && (cnt & 1) != team) continue;  // the other team's tile
         const int acc = cnt % p.acc_bufs;
         const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
         const int nb = n_tile * NT;
@@ -892,6 +903,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             for (int sub = 0; sub < MS; ++sub) {
               const int n = a.n, yy = a.yy, vc = a.vc;
               a = pos_add(a, d_sub);
+              if (EW == 16 && MS > 1 && (sub & 1) != team) continue;
               if (n < p.batch && yy < p.Ho && vc < p.Wo) {
                 const __half* rr = sg.residual + (((size_t)n * p.Ho + yy) * p.Wo + vc) * sg.channels + (nb - sg.c0 + col_lo);
                 for (int b = 0; b < NT; b += 128)  // NT/2 halfs = NT bytes per row segment
@@ -902,12 +914,13 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
         tc_fence_after();
-        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64, cnt * 8 + 5);
+        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 5);
         Pos a = pos0;
 #pragma unroll 1
         for (int sub = 0; sub < MS; ++sub) {
           const int n = a.n, yy = a.yy, vc = a.vc;
           a = pos_add(a, d_sub);
+          if (EW == 16 && MS > 1 && (sub & 1) != team) continue;  // the other team's sub-tile
           const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
           const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
           size_t opix = pix;
@@ -934,7 +947,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         tc_fence_before();
         __syncwarp();
-        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == 64, cnt * 8 + 6);
+        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 6);
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
       }
       pos0 = pos_add(pos0, d_item);
@@ -1072,7 +1085,7 @@ struct aig_conv_plan {
   uint32_t* pc_tab = nullptr;
   CUtensorMap tmapP{}, tmapPT{}, tmapBp{};  // patch rows one per box / patch_vrows per box, weights
   const void* tmapP_ptr = nullptr;
-  int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1;
+  int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1, pc_EW = 8;
   bool pc_wres = false;
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
   bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
@@ -1238,21 +1251,23 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
 
 
 // ---- patch-resident path: host side ------------------------------------------------------
-constexpr int kPconvTail = 5120 /*scale,shift, barriers, K schedule tables*/ + 12 * 2048 /*epilogue staging, one tile per warp slot*/;
-constexpr int kPconvBudget = 227 * 1024 - 1024 /*align*/ - kPconvTail;
+// Shared memory behind the patches and weights: scale/shift, barriers and K schedule tables, then one 2 KB staging
+// tile per epilogue warp (the coalescing epilogue; N = 64 tiles store directly and need none).
+constexpr int pconv_tail(int ew, bool direct_store) { return 5120 + (direct_store ? 0 : ew * 2048); }
+constexpr int pconv_budget(int ew, bool direct_store) { return 227 * 1024 - 1024 /*align*/ - pconv_tail(ew, direct_store); }
 
-template <int NT, int MS, bool WRES>
+template <int NT, int MS, bool WRES, int EW>
 int launch_pconv(aig_conv_plan* pl) {
   static bool attr_set[64] = {};
   aig_ctx* ctx = pl->ctx;
   if (!attr_set[ctx->device & 63]) {
-    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(pconv_kernel<NT, MS, WRES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(pconv_kernel<NT, MS, WRES, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[ctx->device & 63] = true;
   }
   // programmatic dependent launch: this kernel may start under the tail of its predecessor (see griddep_wait)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)pl->pc_grid);
-  cfg.blockDim = dim3(kPconvThreads);
+  cfg.blockDim = dim3(pconv_threads(EW));
   cfg.dynamicSmemBytes = (size_t)pl->pc_smem;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
@@ -1260,13 +1275,14 @@ int launch_pconv(aig_conv_plan* pl) {
   attr[0].val.programmaticStreamSerializationAllowed = pl->pc_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES>, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->pp));
+  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES, EW>, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->pp));
   return AIG_OK;
 }
 
 template <int NT, int MS>
 int dispatch_pconv_w(aig_conv_plan* pl) {
-  return pl->pc_wres ? launch_pconv<NT, MS, true>(pl) : launch_pconv<NT, MS, false>(pl);
+  if (pl->pc_EW == 16) return pl->pc_wres ? launch_pconv<NT, MS, true, 16>(pl) : launch_pconv<NT, MS, false, 16>(pl);
+  return pl->pc_wres ? launch_pconv<NT, MS, true, 8>(pl) : launch_pconv<NT, MS, false, 8>(pl);
 }
 
 int dispatch_pconv(aig_conv_plan* pl) {
@@ -1328,10 +1344,16 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   // all of its traffic
   const bool small = ceil_div_ll(total_q, kTileM) * 4 <= ctx->sm_count && !f_nt;
   q.dist_n = 0;
+  int ew = 16;  // epilogue warps
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_EW")) ew = atoi(e) == 8 ? 8 : 16;
+#endif
+  pl->pc_EW = ew;
   for (int oo = 0; oo < n_opts && best < 0; ++oo) {
     const int o = small ? n_opts - 1 - oo : oo;
     const int NT = opts[o].NT, wblock = NT * 128;
     const int dense_kb = q.taps * q.cblocks;
+    const int kPconvBudget = pconv_budget(ew, NT == 64);
     if (f_nt && NT != f_nt) continue;
     if (!small && NT == 64 && o > 0) continue;  // the 64-wide tiling of a wider layer is for the small regime only
     int ms_top = 256 / NT < 1 ? 1 : 256 / NT;
@@ -1389,7 +1411,7 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
-  pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + kPconvTail;
+  pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + pconv_tail(ew, NT == 64);
   const long long items = (long long)q.m_tiles * (q.dist_n ? q.n_tiles : 1);
   pl->pc_grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
   return true;
