@@ -1281,7 +1281,9 @@ int launch_pconv(aig_conv_plan* pl) {
 
 template <int NT, int MS>
 int dispatch_pconv_w(aig_conv_plan* pl) {
+#ifdef AIG_TUNING
   if (pl->pc_EW == 16) return pl->pc_wres ? launch_pconv<NT, MS, true, 16>(pl) : launch_pconv<NT, MS, false, 16>(pl);
+#endif
   return pl->pc_wres ? launch_pconv<NT, MS, true, 8>(pl) : launch_pconv<NT, MS, false, 8>(pl);
 }
 
@@ -1344,9 +1346,11 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   // all of its traffic
   const bool small = ceil_div_ll(total_q, kTileM) * 4 <= ctx->sm_count && !f_nt;
   q.dist_n = 0;
-  int ew = 16;  // epilogue warps
+  // epilogue warps: 16 (two teams) measured 5-20 % slower than 8 on every layer of the encoder, the register
+  // cap of a 640-thread CTA costs more than the extra warps hide; tuning builds can still select it
+  int ew = 8;
 #ifdef AIG_TUNING
-  if (const char* e = getenv("AIG_PCONV_EW")) ew = atoi(e) == 8 ? 8 : 16;
+  if (const char* e = getenv("AIG_PCONV_EW")) ew = atoi(e) == 16 ? 16 : 8;
 #endif
   pl->pc_EW = ew;
   for (int oo = 0; oo < n_opts && best < 0; ++oo) {

@@ -525,6 +525,90 @@ def streaming_latency(env, n_frames):
             "p50_ms": float(np.percentile(lat, 50)), "p99_ms": float(np.percentile(lat, 99)), "mean_ms": float(lat.mean())}
 
 
+def reference_call_pattern(env):
+    """The reference's own layer classes (oracle/_ref/libaig_reflayers.so: its sources compiled unchanged, calling
+    cuDNN / cuBLAS as it does) run layer by layer on the encoder trunk of the headline workload at 256 frames:
+    ConvLayer(3->32, k5 s2 p2) + BatchNorm + Swish, then four ResConvLayer blocks 32->64->128->256->256 -- the
+    launch pattern of NN::Forward (NN.cpp:93-100) on this GPU.  A reported baseline beside the CPU one; it is a
+    comparator built only where the reference tree was present, and nothing of it is part of the product."""
+    import ctypes
+
+    path = os.path.join(ROOT, "oracle", "_ref", "libaig_reflayers.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libaig_reflayers.so was not built (reference tree absent at build time)"}
+    torch = env.torch
+    ref = ctypes.CDLL(path)
+    P = ctypes.c_void_p
+    ref.ref_layer_create.restype, ref.ref_layer_create.argtypes = P, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    ref.ref_layer_forward.restype, ref.ref_layer_forward.argtypes = P, [P, P]
+    ref.ref_layer_destroy.argtypes = [P]
+    ref.ref_last_error.restype = ctypes.c_char_p
+    if ref.ref_init() != 0:
+        return {"unavailable": ref.ref_last_error().decode()}
+    B = 256
+    torch.cuda.synchronize()
+
+    def make(kind, *a):
+        arr = (ctypes.c_int * len(a))(*a)
+        h = ref.ref_layer_create(kind.encode(), arr, len(a))
+        if not h:
+            raise RuntimeError(ref.ref_last_error().decode())
+        return h
+
+    try:
+        chain = [("conv0 k5s2", make("ConvLayer", B, 3, WIDTHS[0], 5, 2, 2, HEIGHT, WIDTH)), ("conv0 BatchNorm", make("BatchNorm", 1, B, WIDTHS[0], 72, 128)),
+                 ("conv0 Swish", make("Swish", B * WIDTHS[0] * 72 * 128))]
+        h, w = 72, 128
+        for i in range(4):
+            chain.append(("ResConv%d %d->%d" % (i, WIDTHS[i], WIDTHS[i + 1]), make("ResConvLayer", B, WIDTHS[i], WIDTHS[i + 1], h, w)))
+            h, w = (h + 2 - 4) // 2 + 1, (w + 2 - 4) // 2 + 1
+    except RuntimeError as e:
+        return {"unavailable": str(e)}
+    legacy = torch.cuda.default_stream()
+    with torch.cuda.stream(legacy):
+        xs = [torch.rand((B, 3, HEIGHT, WIDTH), device="cuda").half() for _ in range(3)]      # 3 x 56.6 MB > 126 MB L2
+    torch.cuda.synchronize()
+
+    def forward(i, events=None):
+        data = ctypes.c_void_p(xs[i % 3].data_ptr())
+        for j, (_, layer) in enumerate(chain):
+            if events is not None:
+                events[j].record(legacy)
+            out = ref.ref_layer_forward(layer, data)
+            if not out:
+                raise RuntimeError(ref.ref_last_error().decode())
+            data = ctypes.c_void_p(out)
+        if events is not None:
+            events[len(chain)].record(legacy)
+
+    try:
+        for i in range(3):
+            forward(i)
+        torch.cuda.synchronize()
+        steps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(legacy)
+        for i in range(steps):
+            forward(i)
+        e1.record(legacy)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(chain) + 1)] for _ in range(5)]
+        for i in range(5):
+            forward(i, ev[i])
+        torch.cuda.synchronize()
+        layers = [{"site": chain[j][0], "ms": float(np.mean([ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(5)]))} for j in range(len(chain))]
+    except RuntimeError as e:
+        return {"unavailable": str(e)}
+    finally:
+        for _, layer in chain:
+            ref.ref_layer_destroy(layer)
+    tf = FLOP_PER_FRAME * B / (ms * 1e-3) / 1e12
+    return {"value": B / (ms * 1e-3), "unit": "frames/s", "ms_per_step": ms, "frames": B, "tflops": tf, "frac": tf / env.peaks["tensor"],
+            "what": "the reference's ConvLayer/BatchNorm/Swish/ResConvLayer classes (cuDNN, NCHW fp16, compute type HALF) on the encoder trunk, "
+                    "46 library launches per step, planar fp16 input already on the device, no head", "layers": layers}
+
+
 LEGS = {"cnn2d": leg_cnn2d, "conv3d": leg_conv3d, "seqhead": leg_seqhead, "agent_batched": leg_agent_batched}
 GLOBAL_BATCH = {"cnn2d": None, "conv3d": 16, "seqhead": SEQ_B, "agent_batched": 128}
 
@@ -575,6 +659,8 @@ def main():
             r["metric"] = METRICS[w][0]
             r["config"] = {"workload": METRICS[w][2]}
         line["workloads"] = extra
+        if env.world == 1 and wl == "cnn2d" and args.legs == "all":
+            line["reference_call_pattern"] = reference_call_pattern(env)
         if not args.no_cpu_baseline and env.world == 1:
             line["cpu_baseline"] = cpu_baseline_block(wl, 5 if wl == "cnn2d" else 3)
             for w in extra:
