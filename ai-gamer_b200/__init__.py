@@ -90,6 +90,7 @@ SIGNATURES = {
     "aig_conv0_plan_set_weights": [P, P, P, P, P, P, P, c_float],
     "aig_conv0_forward_bgra": [P, P, P],
     "aig_conv0_forward_nchw": [P, P, P],
+    "aig_conv0_forward_rgb_planar": [P, P, P],
     "aig_s2d_elems": [c_int, c_int, c_int, c_int],
     "aig_nhwc_to_s2d": [P, P, P, c_int, c_int, c_int, c_int],
     "aig_s2d_to_nhwc": [P, P, P, c_int, c_int, c_int, c_int],
@@ -416,6 +417,10 @@ class Conv0Plan(_Plan):
 
     def forward_bgra(self, bgra, y):
         self.check(lib().aig_conv0_forward_bgra(self.handle, ptr(bgra), ptr(y)))
+        return y
+
+    def forward_rgb_planar(self, rgb, y):
+        self.check(lib().aig_conv0_forward_rgb_planar(self.handle, ptr(rgb), ptr(y)))
         return y
 
     def forward_nchw(self, x, y):

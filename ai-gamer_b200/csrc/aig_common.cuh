@@ -134,6 +134,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread may sleep in hardware up to `ns` nanoseconds (it wakes as soon
+// as the phase completes), so a long wait costs a handful of instructions instead of a hot polling loop
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after ~AIG_WAIT_CYCLES SM cycles, raises the CTA-wide abort flag and the
 // context's device error word, and returns false; every role then drains to the common exit.
 #ifndef AIG_WAIT_CYCLES
@@ -159,6 +173,21 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int* gerr, int code) {
   return mbar_wait_limit(bar, parity, abort_flag, gerr, code, AIG_WAIT_CYCLES);
+}
+// The same bound for roles that may sleep while they wait (producers far ahead, epilogue warps between tiles):
+// every poll suspends up to ~2 us in hardware, the abort flag and the clock are checked on every wake-up.
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* gerr, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > AIG_WAIT_CYCLES) {
+      *abort_flag = 1;
+      atomicCAS(gerr, 0, code);
+      return false;
+    }
+  }
 }
 
 // ---- TMA (tiled mode; every CTA issues its own loads) ----

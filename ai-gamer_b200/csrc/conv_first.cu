@@ -5,6 +5,7 @@
 // output tile is staged in shared memory and each thread produces one output pixel x 32 channels.
 // Output is channels-last fp16 with bias + folded BatchNorm + activation applied.
 #include "aig_common.cuh"
+#include "conv_first_rows.h"
 #include "conv_first_tc.h"
 
 namespace {
@@ -168,6 +169,8 @@ struct aig_conv0_plan {
   size_t smem = 0;
   dim3 grid;
   ConvFirstTc* tc = nullptr;  // tensor-core path when the filter geometry has an instantiation
+  ConvFirstRows* rows = nullptr;  // row-resident tensor-core path for uint8 frames (5x5, stride 2, 32 channels)
+  __half* planar_scratch = nullptr;  // planar uint8 frames converted to fp16, for geometries without the row kernel
 };
 
 static int conv0_create(aig_ctx* ctx, int batch, int D, int H, int W, int K, int kd, int k, int sd, int s, int pd, int pad,
@@ -215,6 +218,13 @@ static int conv0_create(aig_ctx* ctx, int batch, int D, int H, int W, int K, int
       return rc;
     }
   }
+  if (conv_first_rows_supported(geo)) {
+    const int rc = conv_first_rows_create(ctx, geo, pl->scale, pl->shift, &pl->rows);
+    if (rc != AIG_OK) {
+      aig_conv0_plan_destroy(pl);
+      return rc;
+    }
+  }
   *out = pl;
   return AIG_OK;
 }
@@ -236,6 +246,8 @@ int aig_conv0_plan_destroy(aig_conv0_plan* pl) {
   DeviceGuard g(pl->ctx->device);
   cudaStreamSynchronize(pl->ctx->stream);
   conv_first_tc_destroy(pl->tc);
+  conv_first_rows_destroy(pl->rows);
+  cudaFree(pl->planar_scratch);
   cudaFree(pl->w);
   cudaFree(pl->scale);
   cudaFree(pl->shift);
@@ -267,6 +279,10 @@ int aig_conv0_plan_set_weights(aig_conv0_plan* pl, const aig_half* w, const aig_
     const int rc = conv_first_tc_set_weights(pl->tc, (const __half*)w);
     if (rc != AIG_OK) return rc;
   }
+  if (pl->rows) {
+    const int rc = conv_first_rows_set_weights(pl->rows, (const __half*)w);
+    if (rc != AIG_OK) return rc;
+  }
   pl->weights_set = true;
   return AIG_OK;
 }
@@ -278,6 +294,10 @@ int aig_conv0_plan_set_output_s2d(aig_conv0_plan* pl, int enable) {
   if (!pl->tc) return AIG_OK;
   // block extents of a following k4 s2 p1 / k2 s2 p0 pair: one more block than its output extent
   const int Hb = (pl->p.Ho - 2) / 2 + 2, Wb = (pl->p.Wo - 2) / 2 + 2;
+  if (pl->rows) {
+    const int rc = conv_first_rows_set_s2d(pl->rows, enable, Hb, Wb);
+    if (rc != AIG_OK) return rc;
+  }
   return conv_first_tc_set_s2d(pl->tc, enable, Hb, Wb);
 }
 
@@ -288,10 +308,27 @@ int aig_conv0_forward_bgra(aig_conv0_plan* pl, const uint8_t* bgra, aig_half* y)
   AIG_REQUIRE(ctx, bgra && y && pl->weights_set, "conv0 forward: null pointer or weights not set");
   AIG_REQUIRE(ctx, pl->p.D == 1 && pl->p.kd == 1, "conv0 forward_bgra: 2-D plans only");
   AIG_REQUIRE(ctx, ((uintptr_t)bgra & 3) == 0 && ((uintptr_t)y & 15) == 0, "conv0 forward: misaligned tensors");
+  if (pl->rows && ((uintptr_t)bgra & 15) == 0) return conv_first_rows_forward(pl->rows, bgra, 0, (__half*)y);
   if (pl->tc) return conv_first_tc_forward(pl->tc, bgra, true, (__half*)y);
   conv_first_kernel<true><<<pl->grid, kTH * kTW, pl->smem, ctx->stream>>>(bgra, (__half*)y, pl->p);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
+}
+
+int aig_conv0_forward_rgb_planar(aig_conv0_plan* pl, const uint8_t* rgb, aig_half* y) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  AIG_REQUIRE(ctx, rgb && y && pl->weights_set, "conv0 forward: null pointer or weights not set");
+  AIG_REQUIRE(ctx, pl->p.D == 1 && pl->p.kd == 1, "conv0 forward_rgb_planar: 2-D plans only");
+  AIG_REQUIRE(ctx, ((uintptr_t)y & 15) == 0, "conv0 forward: misaligned output");
+  if (pl->rows && ((uintptr_t)rgb & 15) == 0) return conv_first_rows_forward(pl->rows, rgb, 1, (__half*)y);
+  // other geometries: ConvertAndNormalize into a planar fp16 copy (CudaStuff.cu:150-157), then the planar path
+  const size_t n = (size_t)pl->p.batch * 3 * pl->p.H * pl->p.W;
+  if (!pl->planar_scratch) AIG_CUDA_OK(ctx, cudaMalloc(&pl->planar_scratch, n * sizeof(__half)));
+  const int rc = aig_convert_normalize(ctx, (aig_half*)pl->planar_scratch, rgb, n);
+  if (rc != AIG_OK) return rc;
+  return aig_conv0_forward_nchw(pl, (const aig_half*)pl->planar_scratch, y);
 }
 
 int aig_conv0_forward_nchw(aig_conv0_plan* pl, const aig_half* x, aig_half* y) {

@@ -281,6 +281,7 @@ class Env:
         self.timer = Timer(self.world, "cuda")
         self.peaks = measured_peaks()
         self.args = args
+        self.profile = False   # profiler captures: a few untimed steps only
 
     def broadcast(self, make_blob, nbytes):
         """Rank 0 builds the parameter bytes, one NCCL broadcast, every rank loads its own copy."""
@@ -311,6 +312,9 @@ def leg_cnn2d(env, full):
            "clocks": res["clocks"], "gpu_launches": K * enc.kernel_launches, "launches_per_step": enc.kernel_launches,
            "l2": "inputs rotate over %d batches (%.0f MB > 126 MB L2); activations written ~%.2f GB per step" % (
                n_rot, n_rot * B * HEIGHT * WIDTH * 4 / 1e6, B * 2.19e6 / 1e9)}
+    if env.profile:
+        enc.close()
+        return out
     # ---- per-launch durations: the same forwards with one CUDA event between consecutive launches (the event
     # records cost a few % of a step, which is why they are not in the regions above), clocks sampled around it
     prof_n = max(50, min(400, int(1.0 / max(ms * 1e-3, 1e-6))))
@@ -394,7 +398,7 @@ def leg_conv3d(env, full):
     enc.load_bytes(env.broadcast(lambda: SY.serialize_conv3d_params(SY.make_conv3d_params(0)), enc.param_bytes()))
     n_rot = 6                                                                   # 6 x 28.3 MB of clips > 126 MB L2
     clips = [torch.rand((B, 3, D, HEIGHT, WIDTH), device="cuda", generator=torch.Generator("cuda").manual_seed(7 + i + 100 * env.rank)).half() for i in range(n_rot)]
-    K = max(args.steps, 10)
+    K = args.steps if env.profile else max(args.steps, 10)
     res = env.timer.regions(lambda i: enc.forward(clips[i % n_rot]), K, args.warmup, env.local_rank if env.rank == 0 else None)
     ms = res["ms_per_step"]
     enc.close()
@@ -437,7 +441,7 @@ def leg_seqhead(env, full):
     head.load_bytes(env.broadcast(lambda: SY.serialize_seq_params(SY.make_seq_params(0)), head.param_bytes()))
     n_rot = 16                                                                  # 16 x 8.4 MB of embeddings > 126 MB L2
     embs = [torch.randn(B * T * d, device="cuda", generator=torch.Generator("cuda").manual_seed(11 + i + 100 * env.rank)).half() for i in range(n_rot)]
-    K = max(args.steps, 10)
+    K = args.steps if env.profile else max(args.steps, 10)
     res = env.timer.regions(lambda i: head.forward(embs[i % n_rot]), K, args.warmup, env.local_rank if env.rank == 0 else None)
     ms = res["ms_per_step"]
     head.close()
@@ -491,7 +495,7 @@ def leg_agent_batched(env, full):
     n_rot = 8                                                                   # 8 x 18.9 MB of frames > 126 MB L2
     gen = torch.Generator("cuda").manual_seed(23 + 100 * env.rank)
     frames = [torch.randint(0, 256, (B, HEIGHT, WIDTH, 4), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(n_rot)]
-    K = 64                                                                      # one region = 64 frames of every sequence
+    K = args.steps if env.profile else 64                                       # one region = 64 frames of every sequence
     res = env.timer.regions(lambda i: agent.step(frames[i % n_rot]), K, max(args.warmup, n_rot), env.local_rank if env.rank == 0 else None)
     ms = res["ms_per_step"]
     agent.close()
@@ -626,6 +630,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (used for short profiler captures)")
     ap.add_argument("--no-latency", action="store_true", help="skip the batch-1 streaming latency leg")
     ap.add_argument("--latency-frames", type=int, default=1000)
+    ap.add_argument("--profile-iters", type=int, default=0,
+                    help="profiler captures: run only this many untimed steps of --workload (no regions, no other legs) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -635,6 +641,15 @@ def main():
 
     env = Env(args)
     wl = args.workload
+    if args.profile_iters > 0:
+        MIN_REGIONS_SAVED = globals()["MIN_REGIONS"], globals()["MIN_TOTAL_S"]
+        globals()["MIN_REGIONS"], globals()["MIN_TOTAL_S"] = 1, 0.0      # one region of --profile-iters steps
+        args.steps, args.warmup, args.no_e2e = args.profile_iters, 3, True
+        env.profile = True
+        LEGS[wl](env, False)
+        globals()["MIN_REGIONS"], globals()["MIN_TOTAL_S"] = MIN_REGIONS_SAVED
+        env.close()
+        return
     head = LEGS[wl](env, True)
     extra = {}
     others = [w for w in LEGS if w != wl] if args.legs == "all" else ([] if args.legs == "none" else [w for w in args.legs.split(",") if w in LEGS and w != wl])

@@ -218,6 +218,10 @@ int aig_conv0_plan_set_weights(aig_conv0_plan* plan, const aig_half* w_kcrs, con
                                const float* bn_gamma, const float* bn_beta, const float* bn_mean,
                                const float* bn_var, float bn_eps);
 int aig_conv0_forward_bgra(aig_conv0_plan* plan, const uint8_t* bgra, aig_half* y_nhwc);
+/* Same convolution from planar uint8 frames [B][3][H][W] (planes R, G, B): what GrabFrameInt8(planar = true)
+ * delivers (NvDisplayCap.h:70-87) and what the reference's recordings store per frame
+ * (input_recorder.cpp:122-133); the /255 normalisation (CudaStuff.cu:150-157) happens in the load. */
+int aig_conv0_forward_rgb_planar(aig_conv0_plan* plan, const uint8_t* rgb_planar, aig_half* y_nhwc);
 /* Same convolution from an already normalised planar fp16 NCHW input (the operator-API path). */
 int aig_conv0_forward_nchw(aig_conv0_plan* plan, const aig_half* x_nchw, aig_half* y_nhwc);
 

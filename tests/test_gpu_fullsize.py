@@ -69,12 +69,14 @@ def test_frame_encoder_all_256_frames_against_the_oracle(env):
     c.sync()
     got = U.host(enc.outputs_f32())
     enc.close()
-    _, _, want = PL.cnn_forward(params, frames)
+    _, logits, want = PL.cnn_forward(params, frames)
     want = want.astype(np.float32)
-    assert U.rel_err(got, want, 0.05).max() < TOL
+    err_l = _logit_err(got, logits)
+    assert err_l < TOL, "key/mouse logits: max relative error %.4g" % err_l
+    assert np.abs(got - want).max() < 2e-3                                # outputs live in [-1, 1]
     agree, n = _check_actions(got, want)
     assert n == 256 * 16
-    print("frame encoder: %d button decisions, agreement %.5f, max rel err %.2e" % (n, agree, U.rel_err(got, want, 0.05).max()))
+    print("frame encoder: %d button decisions, agreement %.5f, max logit err %.2e" % (n, agree, err_l))
 
 
 @gpu

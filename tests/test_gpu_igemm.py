@@ -224,6 +224,49 @@ def _s2d_host(x_nhwc):
     return out
 
 
+@gpu
+@pytest.mark.parametrize("B,H,W", [(2, 144, 256), (3, 32, 64), (1, 17, 48), (2, 7, 16), (5, 40, 240)])
+def test_first_layer_from_uint8_frames_row_kernel(env, B, H, W):
+    """The encoder's own first layer (3 -> 32, 5x5, stride 2, pad 2) on the row-resident kernel: BGRA pixels and
+    planar RGB planes of the same frames give the same bytes, both match the oracle, and the space-to-depth
+    output is the block rearrangement of the plain one (borders left untouched)."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    pk = U.pkg()
+    K = 32
+    frames = PL.make_frames(B * 7 + H, B, H, W)                              # [B][H][W][4] = B,G,R,A
+    planar = np.ascontiguousarray(frames[..., [2, 1, 0]].transpose(0, 3, 1, 2))   # [B][3][H][W] = R,G,B planes
+    w = PL.he_normal(RNG, (K, 3, 5, 5))
+    b = h(RNG.uniform(-0.2, 0.2, K))
+    bn = PL.bn_params(RNG, K, trivial=False)
+    x = O.preprocess_frames(frames)
+    assert np.array_equal(x, O.convert_normalize(planar.ravel()).reshape(planar.shape))
+    want = O.swish(O.batchnorm(O.conv2d(x, w, b, 2, 2), *bn))
+    Ho, Wo = want.shape[2], want.shape[3]
+    plan = pk.Conv0Plan(c, B, H, W, K, 5, 2, 2, act=pk.ACT_SWISH)
+    plan.set_weights(U.dev(w), U.dev(b), bn=[U.dev(q) for q in bn])
+    dy = torch.zeros(want.size, dtype=torch.float16, device="cuda")
+    plan.forward_bgra(U.dev(frames), dy)
+    c.sync()
+    got = U.host(dy).reshape(B, Ho, Wo, K).copy()
+    assert U.scaled_err(U.nchw(got), want) < 4e-3
+    dy.zero_()
+    plan.forward_rgb_planar(U.dev(planar), dy)
+    c.sync()
+    assert np.array_equal(U.host(dy).reshape(B, Ho, Wo, K), got), "planar RGB and BGRA frames give different results"
+    if Ho >= 2 and Wo >= 2:
+        pk.lib().aig_conv0_plan_set_output_s2d(plan.handle, 1)
+        n = pk.lib().aig_s2d_elems(B, Ho, Wo, K)
+        ds = torch.full((n,), 0.0, dtype=torch.float16, device="cuda")
+        plan.forward_rgb_planar(U.dev(planar), ds)
+        c.sync()
+        hb, wb = (Ho - 2) // 2 + 2, (Wo - 2) // 2 + 2
+        assert np.array_equal(U.host(ds).reshape(B, hb, wb, 4, K), _s2d_host(got))
+    plan.close()
+
+
 RESDOWN = [
     # B, C, H, W, K
     (2, 32, 24, 32, 64),     # N = 128 in one tile, 32-channel sub-positions
