@@ -136,6 +136,9 @@ SIGNATURES.update({
     "aig_cnn_load_file": [P, ctypes.c_char_p],
     "aig_cnn_forward": [P, P],
     "aig_cnn_forward_graph": [P, P],
+    "aig_cnn_forward_rgb": [P, P],
+    "aig_cnn_forward_graph_rgb": [P, P],
+    "aig_cnn_submit_host_rgb": [P, c_int, P, P],
     "aig_cnn_infer_host": [P, P, P],
     "aig_cnn_submit_host": [P, c_int, P, P],
     "aig_cnn_wait": [P, c_int],
@@ -194,6 +197,15 @@ SIGNATURES.update({
     "aig_layer_out_count": [P],
     "aig_layer_destroy": [P],
 })
+SIGNATURES.update({
+    "aig_recording_open": [ctypes.c_char_p, PP],
+    "aig_recording_close": [P],
+    "aig_recording_last_error": [P],
+    "aig_recording_info": [P, PI, PI, ctypes.POINTER(ctypes.c_longlong)],
+    "aig_recording_read": [P, ctypes.c_longlong, c_int, P, P, P],
+    "aig_recording_targets": [P, P, c_int, P],
+    "aig_cnn_infer_recording": [P, P, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, P],
+})
 AIG_C3D_MAX_LAYERS = 6
 
 
@@ -212,7 +224,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_compat_context": c_void_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_compat_context": c_void_p, "aig_recording_last_error": ctypes.c_char_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
@@ -460,6 +472,13 @@ class CnnEncoder:
         fn = lib().aig_cnn_forward_graph if graph else lib().aig_cnn_forward
         self.check(fn(self.handle, ptr(bgra_dev)))
 
+    def forward_rgb(self, rgb_planar_dev, graph=False):
+        fn = lib().aig_cnn_forward_graph_rgb if graph else lib().aig_cnn_forward_rgb
+        self.check(fn(self.handle, ptr(rgb_planar_dev)))
+
+    def submit_host_rgb(self, slot, rgb_host, out_host):
+        self.check(lib().aig_cnn_submit_host_rgb(self.handle, slot, ptr(rgb_host), ptr(out_host)))
+
     def infer_host(self, bgra_host, out_host):
         self.check(lib().aig_cnn_infer_host(self.handle, ptr(bgra_host), ptr(out_host)))
 
@@ -566,3 +585,58 @@ class MhaPlan(_Plan):
 
     def reset(self):
         self.check(lib().aig_mha_reset(self.handle))
+
+
+class Recording:
+    """aig_recording: a recording file of the reference's input recorder (int32 width, height; per frame a 10-byte
+    input header and a planar RGB uint8 frame)."""
+
+    def __init__(self, path):
+        self.handle = c_void_p()
+        rc = lib().aig_recording_open(str(path).encode(), ctypes.byref(self.handle))
+        if rc != 0:
+            raise AigError(rc, lib().aig_recording_last_error(None).decode())
+        w, h, n = c_int(), c_int(), ctypes.c_longlong()
+        lib().aig_recording_info(self.handle, ctypes.byref(w), ctypes.byref(h), ctypes.byref(n))
+        self.width, self.height, self.n_records = w.value, h.value, n.value
+
+    def check(self, rc):
+        if rc != 0:
+            raise AigError(rc, lib().aig_recording_last_error(self.handle).decode())
+
+    def read(self, first, count):
+        """(frames uint8 [count][3][h][w], key_states uint16 [count], mouse int32 [count][2]) as numpy arrays."""
+        import numpy as np
+
+        frames = np.empty((count, 3, self.height, self.width), np.uint8)
+        keys = np.empty(count, np.uint16)
+        mouse = np.empty((count, 2), np.int32)
+        self.check(lib().aig_recording_read(self.handle, first, count, ptr(frames), ptr(keys), ptr(mouse)))
+        return frames, keys, mouse
+
+    @staticmethod
+    def targets(keys, mouse):
+        import numpy as np
+
+        keys, mouse = np.ascontiguousarray(keys, np.uint16), np.ascontiguousarray(mouse, np.int32)
+        out = np.empty((keys.size, 16), np.float32)
+        rc = lib().aig_recording_targets(ptr(keys), ptr(mouse), keys.size, ptr(out))
+        if rc != 0:
+            raise AigError(rc, "aig_recording_targets")
+        return out
+
+    def infer(self, encoder, first, count):
+        """Frame encoder outputs [count][n_out] for records first .. first+count-1 (planar RGB straight from the file)."""
+        import numpy as np
+
+        out = np.empty((count, encoder.cfg.n_out), np.float32)
+        rc = lib().aig_cnn_infer_recording(encoder.handle, self.handle, first, count, encoder.cfg.batch, encoder.cfg.n_out, ptr(out))
+        if rc != 0:
+            msg = lib().aig_recording_last_error(self.handle).decode() or lib().aig_cnn_last_error(encoder.handle).decode()
+            raise AigError(rc, msg)
+        return out
+
+    def close(self):
+        if self.handle:
+            lib().aig_recording_close(self.handle)
+            self.handle = c_void_p()

@@ -83,6 +83,7 @@ struct aig_cnn {
   static constexpr int kGraphs = 8;    // captured forwards, keyed by input pointer
   aig_graph* graphs[kGraphs] = {};
   const uint8_t* graph_ins[kGraphs] = {};
+  bool graph_planar[kGraphs] = {};
   int graph_next = 0;
   // pipelined host-buffer steps: private copy stream, two frame slots
   cudaStream_t copy_stream = nullptr;
@@ -409,8 +410,11 @@ int aig_cnn_load_file(aig_cnn* m, const char* path) {
   return aig_cnn_load_memory(m, buf.data(), (size_t)n);
 }
 
-// NN::Forward (NN.cpp:93-100) over device-resident BGRA frames; results stay on the device.
-int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) {
+}  // extern "C"
+
+// NN::Forward (NN.cpp:93-100) over device-resident frames (BGRA pixels, or planar R,G,B uint8 planes); results
+// stay on the device.
+static int cnn_forward_impl(aig_cnn* m, const uint8_t* bgra_dev, bool planar) {
   if (!m || !bgra_dev) return AIG_ERR_INVALID;
   if (!m->loaded) return fail(m, AIG_ERR_INVALID, "parameters not loaded");
   const aig_cnn_config& c = m->cfg;
@@ -422,7 +426,8 @@ int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) {
     if (prof) cudaEventRecord(m->prof_ev[ev0 + si++], ps);
   };
   tick();
-  CNN_OK(m, aig_conv0_forward_bgra(m->conv0, bgra_dev, m->act0));
+  if (planar) CNN_OK(m, aig_conv0_forward_rgb_planar(m->conv0, bgra_dev, m->act0));
+  else CNN_OK(m, aig_conv0_forward_bgra(m->conv0, bgra_dev, m->act0));
   tick();
   const aig_half* x = m->act0;
   for (auto& b : m->blocks) {
@@ -463,6 +468,11 @@ int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) {
   return AIG_OK;
 }
 
+extern "C" {
+
+int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev) { return cnn_forward_impl(m, bgra_dev, false); }
+int aig_cnn_forward_rgb(aig_cnn* m, const uint8_t* rgb_planar_dev) { return cnn_forward_impl(m, rgb_planar_dev, true); }
+
 // Per-launch timing of the eager forward: begin allocates events for up to max_steps forwards; end
 // synchronises and returns, per launch site, the mean milliseconds over the recorded steps.
 int aig_cnn_profile_begin(aig_cnn* m, int max_steps) {
@@ -501,12 +511,14 @@ const char* aig_cnn_site_name(aig_cnn* m, int i) { return (m && i >= 0 && i < (i
 double aig_cnn_site_flops(aig_cnn* m, int i) { return (m && i >= 0 && i < (int)m->sites.size()) ? m->sites[i].flops : 0.0; }
 double aig_cnn_site_bytes(aig_cnn* m, int i) { return (m && i >= 0 && i < (int)m->sites.size()) ? m->sites[i].bytes : 0.0; }
 
-// Same, replayed as one CUDA graph (captured on first use for this input pointer).
-int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
+}  // extern "C"
+
+// Same, replayed as one CUDA graph (captured on first use for this input pointer and frame format).
+static int cnn_forward_graph_impl(aig_cnn* m, const uint8_t* bgra_dev, bool planar) {
   if (!m || !bgra_dev) return AIG_ERR_INVALID;
   int slot = -1;
   for (int i = 0; i < aig_cnn::kGraphs; ++i)
-    if (m->graphs[i] && m->graph_ins[i] == bgra_dev) slot = i;
+    if (m->graphs[i] && m->graph_ins[i] == bgra_dev && m->graph_planar[i] == planar) slot = i;
   if (slot < 0) {
     slot = m->graph_next;
     m->graph_next = (m->graph_next + 1) % aig_cnn::kGraphs;
@@ -518,7 +530,7 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
     // is suspended for both passes (its event records must not end up inside the graph)
     const bool prof_was_on = m->prof_on;
     m->prof_on = false;
-    int rc = aig_cnn_forward(m, bgra_dev);
+    int rc = cnn_forward_impl(m, bgra_dev, planar);
     if (rc != AIG_OK) {
       m->prof_on = prof_was_on;
       return rc;
@@ -528,7 +540,7 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
       m->prof_on = prof_was_on;
       return fail(m, rc, aig_last_error(m->ctx));
     }
-    rc = aig_cnn_forward(m, bgra_dev);
+    rc = cnn_forward_impl(m, bgra_dev, planar);
     aig_graph* g = nullptr;
     const int rc2 = aig_graph_end(m->ctx, &g);  // always ends the capture, also after a failed forward
     m->prof_on = prof_was_on;
@@ -539,20 +551,29 @@ int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) {
     if (rc2 != AIG_OK) return fail(m, rc2, aig_last_error(m->ctx));
     m->graphs[slot] = g;
     m->graph_ins[slot] = bgra_dev;
+    m->graph_planar[slot] = planar;
   }
   CNN_OK(m, aig_graph_launch(m->ctx, m->graphs[slot]));
   return AIG_OK;
 }
+
+extern "C" {
+
+int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev) { return cnn_forward_graph_impl(m, bgra_dev, false); }
+int aig_cnn_forward_graph_rgb(aig_cnn* m, const uint8_t* rgb_planar_dev) { return cnn_forward_graph_impl(m, rgb_planar_dev, true); }
 
 // Pipelined frame steps with host buffers.  submit(slot) queues, without waiting, the host->device
 // copy of one batch on a private copy stream, the forward on the context stream once the copy has
 // landed, and the device->host copy of the outputs; wait(slot) blocks until that slot's outputs are
 // in the caller's buffer.  With the two slots used alternately the copy of step i+1 runs under the
 // forward of step i.  Host buffers should be pinned.
-int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host) {
+}  // extern "C"
+
+static int cnn_submit_host_impl(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host, bool planar) {
   if (!m || !bgra_host || !out_host || slot < 0 || slot > 1) return AIG_ERR_INVALID;
   const aig_cnn_config& c = m->cfg;
-  const size_t fb = (size_t)c.batch * c.height * c.width * 4;
+  const size_t fb = (size_t)c.batch * c.height * c.width * 4;             // slot buffers hold either format
+  const size_t copy_bytes = (size_t)c.batch * c.height * c.width * (planar ? 3 : 4);
   cudaStream_t s = (cudaStream_t)aig_ctx_stream(m->ctx);
   if (!m->copy_stream) {
     CNN_CUDA(m, cudaStreamCreateWithFlags(&m->copy_stream, cudaStreamNonBlocking));
@@ -565,16 +586,25 @@ int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* o
   }
   // the slot's frame buffer is free once the forward that last read it has run
   if (m->slot_used[slot]) CNN_CUDA(m, cudaStreamWaitEvent(m->copy_stream, m->ev_used[slot], 0));
-  CNN_CUDA(m, cudaMemcpyAsync(m->frames_slot[slot], bgra_host, fb, cudaMemcpyHostToDevice, m->copy_stream));
+  CNN_CUDA(m, cudaMemcpyAsync(m->frames_slot[slot], bgra_host, copy_bytes, cudaMemcpyHostToDevice, m->copy_stream));
   CNN_CUDA(m, cudaEventRecord(m->ev_h2d[slot], m->copy_stream));
   CNN_CUDA(m, cudaStreamWaitEvent(s, m->ev_h2d[slot], 0));
-  const int rc = aig_cnn_forward_graph(m, m->frames_slot[slot]);
+  const int rc = cnn_forward_graph_impl(m, m->frames_slot[slot], planar);
   if (rc != AIG_OK) return rc;
   CNN_CUDA(m, cudaEventRecord(m->ev_used[slot], s));
   m->slot_used[slot] = true;
   CNN_CUDA(m, cudaMemcpyAsync(out_host, m->out_f32, (size_t)c.batch * c.n_out * sizeof(float), cudaMemcpyDeviceToHost, s));
   CNN_CUDA(m, cudaEventRecord(m->ev_done[slot], s));
   return AIG_OK;
+}
+
+extern "C" {
+
+int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host) {
+  return cnn_submit_host_impl(m, slot, bgra_host, out_host, false);
+}
+int aig_cnn_submit_host_rgb(aig_cnn* m, int slot, const uint8_t* rgb_planar_host, float* out_host) {
+  return cnn_submit_host_impl(m, slot, rgb_planar_host, out_host, true);
 }
 
 int aig_cnn_wait(aig_cnn* m, int slot) {

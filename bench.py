@@ -305,6 +305,8 @@ def leg_cnn2d(env, full):
     rng = np.random.default_rng(1000 + env.rank)
     host_frames = [torch.from_numpy(rng.integers(0, 256, (B, HEIGHT, WIDTH, 4), dtype=np.uint8)).pin_memory() for _ in range(n_rot)]
     dev_frames = [f.cuda() for f in host_frames]
+    # the same frames as planar R, G, B planes (what the reference's recorder stores and GrabFrameInt8(planar) delivers)
+    host_planar = [f[..., [2, 1, 0]].permute(0, 3, 1, 2).contiguous().pin_memory() for f in host_frames]
     K = args.steps
     res = env.timer.regions(lambda i: enc.forward(dev_frames[i % n_rot]), K, args.warmup, env.local_rank if env.rank == 0 else None)
     ms = res["ms_per_step"]
@@ -341,29 +343,34 @@ def leg_cnn2d(env, full):
     if not args.no_e2e:
         host_outs = [torch.empty((B, N_OUT), dtype=torch.float32).pin_memory() for _ in range(2)]
 
-        def e2e_region(k, i0):
-            env.timer.barrier()
-            t0 = time.perf_counter()
-            for i in range(k):
-                if i >= 2:
+        def e2e_leg(submit, frames, bytes_per_px, entry):
+            def e2e_region(k, i0):
+                env.timer.barrier()
+                t0 = time.perf_counter()
+                for i in range(k):
+                    if i >= 2:
+                        enc.wait(i & 1)
+                    submit(i & 1, frames[(i0 + i) % n_rot], host_outs[i & 1])
+                for i in range(max(k - 2, 0), k):
                     enc.wait(i & 1)
-                enc.submit_host(i & 1, host_frames[(i0 + i) % n_rot], host_outs[i & 1])
-            for i in range(max(k - 2, 0), k):
-                enc.wait(i & 1)
-            torch.cuda.synchronize()
-            dt = time.perf_counter() - t0
-            env.timer.barrier()
-            return dt * 1e3
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                env.timer.barrier()
+                return dt * 1e3
 
-        e2e_region(4, 0)
-        trial = env.timer.max_over_ranks([e2e_region(K, 0)])[0]
-        reps = int(min(MAX_REGIONS, max(MIN_REGIONS, math.ceil(MIN_TOTAL_S * 1e3 / max(trial, 1e-3)))))
-        ems = np.array(env.timer.max_over_ranks([e2e_region(K, r * K) for r in range(reps)]))
-        e_ms = float(np.median(ems)) / K
-        h2d = B * HEIGHT * WIDTH * 4
-        e2e = {"value": env.world * B / (e_ms * 1e-3), "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * N_OUT * 4,
-               "ms_per_step": e_ms, "ms_per_step_min": float(ems.min()) / K, "ms_per_step_max": float(ems.max()) / K, "repeats": reps,
-               "h2d_gbs_per_gpu": h2d / (e_ms * 1e-3) / 1e9, "entry_point": "aig_cnn_submit_host / aig_cnn_wait (BGRA frames, 4 bytes per pixel)"}
+            e2e_region(4, 0)
+            trial = env.timer.max_over_ranks([e2e_region(K, 0)])[0]
+            reps = int(min(MAX_REGIONS, max(MIN_REGIONS, math.ceil(MIN_TOTAL_S * 1e3 / max(trial, 1e-3)))))
+            ems = np.array(env.timer.max_over_ranks([e2e_region(K, r * K) for r in range(reps)]))
+            e_ms = float(np.median(ems)) / K
+            h2d = B * HEIGHT * WIDTH * bytes_per_px
+            return {"value": env.world * B / (e_ms * 1e-3), "unit": "frames/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * N_OUT * 4,
+                    "ms_per_step": e_ms, "ms_per_step_min": float(ems.min()) / K, "ms_per_step_max": float(ems.max()) / K, "repeats": reps,
+                    "h2d_gbs_per_gpu": h2d / (e_ms * 1e-3) / 1e9, "entry_point": entry}
+
+        # headline: planar RGB host frames, 3 bytes per pixel; beside it the BGRA form of the same frames
+        e2e = e2e_leg(enc.submit_host_rgb, host_planar, 3, "aig_cnn_submit_host_rgb / aig_cnn_wait (planar R,G,B uint8 frames, 3 bytes per pixel)")
+        e2e["bgra"] = e2e_leg(enc.submit_host, host_frames, 4, "aig_cnn_submit_host / aig_cnn_wait (BGRA frames, 4 bytes per pixel)")
     # ---- roofline of the convolution-GEMM kernel class (every residual-block launch of a step)
     layers = [{"site": n, "ms": round(m_, 5), "tflops": round(f / (m_ * 1e-3) / 1e12, 2) if m_ > 0 and f else None,
                "gbs": round(b_ / (m_ * 1e-3) / 1e9, 1) if m_ > 0 else None} for n, m_, f, b_ in sites]

@@ -42,8 +42,13 @@ int aig_cnn_load_file(aig_cnn* m, const char* path);
 /* NN::Forward (NN.cpp:93-100) preceded by the frame preprocessing (Infer.cpp:103,109) on BGRA
  * frames [batch][height][width][4] resident in device memory.  Asynchronous on the context stream. */
 int aig_cnn_forward(aig_cnn* m, const uint8_t* bgra_dev);
+/* The same from planar uint8 frames [batch][3][height][width] (planes R, G, B): the layout
+ * GrabFrameInt8(planar = true) produces (NvDisplayCap.h:70-87) and the reference's recordings store
+ * (input_recorder.cpp:122-133), 3 bytes per pixel instead of 4. */
+int aig_cnn_forward_rgb(aig_cnn* m, const uint8_t* rgb_planar_dev);
 /* The same work replayed from a CUDA graph captured on first use. */
 int aig_cnn_forward_graph(aig_cnn* m, const uint8_t* bgra_dev);
+int aig_cnn_forward_graph_rgb(aig_cnn* m, const uint8_t* rgb_planar_dev);
 /* One frame step with host buffers (Infer.cpp:103-112): host->device copy of the frames, forward,
  * half->float, device->host copy of [batch][n_out] floats, stream synchronise. */
 int aig_cnn_infer_host(aig_cnn* m, const uint8_t* bgra_host, float* out_host);
@@ -52,6 +57,8 @@ int aig_cnn_infer_host(aig_cnn* m, const uint8_t* bgra_host, float* out_host);
  * slot's outputs have arrived.  Alternating slots 0 and 1 lets the copy of step i+1 run under the
  * forward of step i.  Host buffers should be pinned and must stay valid until wait() returns. */
 int aig_cnn_submit_host(aig_cnn* m, int slot, const uint8_t* bgra_host, float* out_host);
+/* The same with planar uint8 RGB frames in host memory (a quarter fewer bytes over PCIe). */
+int aig_cnn_submit_host_rgb(aig_cnn* m, int slot, const uint8_t* rgb_planar_host, float* out_host);
 int aig_cnn_wait(aig_cnn* m, int slot);
 /* Device views of the last forward's results. */
 const aig_half* aig_cnn_outputs_half(aig_cnn* m);  /* [batch][n_out] after sigmoid/tanh */
@@ -71,6 +78,27 @@ int aig_cnn_site_count(aig_cnn* m);
 const char* aig_cnn_site_name(aig_cnn* m, int i);
 double aig_cnn_site_flops(aig_cnn* m, int i);
 double aig_cnn_site_bytes(aig_cnn* m, int i);
+
+/* ---------------------------------------------------------------------------------------------
+ * Recording files of the reference's input recorder and offline inference over them.  Layout: int32 width,
+ * int32 height (input_recorder.cpp:24-27), then per frame uint16 keyStates, int32 mouseDeltaX, int32 mouseDeltaY
+ * (10 bytes, packed) and 3*width*height bytes of planar RGB (input_recorder.cpp:122-133).  Records are counted
+ * like the reference's index scan (main.cpp:41-92): whole records only. */
+typedef struct aig_recording aig_recording;
+int aig_recording_open(const char* path, aig_recording** out);
+int aig_recording_close(aig_recording* r);
+const char* aig_recording_last_error(aig_recording* r);   /* r may be null after a failed open */
+int aig_recording_info(const aig_recording* r, int* width, int* height, long long* n_records);
+/* `count` consecutive records from `first` (host buffers; any of the three may be null): frames
+ * [count][3][height][width] as stored, key_states [count], mouse_dxdy [count][2]. */
+int aig_recording_read(aig_recording* r, long long first, int count, uint8_t* frames, uint16_t* key_states, int32_t* mouse_dxdy);
+/* The behaviour-cloning targets the reference trains on (Train.cpp:70-76): targets [count][16], button j = bit j
+ * of keyStates for j < 14, then mouseDeltaX / 256 and mouseDeltaY / 256. */
+int aig_recording_targets(const uint16_t* key_states, const int32_t* mouse_dxdy, int count, float* targets);
+/* Frame encoder over records [first, first + count) in batches of `batch` (= the encoder's batch size; the last
+ * batch is padded by repeating its final frame), fed as planar RGB through aig_cnn_submit_host_rgb with two
+ * batches in flight.  out_host [count][n_out] fp32. */
+int aig_cnn_infer_recording(aig_cnn* m, aig_recording* r, long long first, long long count, int batch, int n_out, float* out_host);
 
 /* ---------------------------------------------------------------------------------------------
  * Sequence head: LSTMLayer (layers x hidden, double bias, clip 5) -> MultiHeadAttentionLayer (causal,

@@ -165,3 +165,58 @@ def test_full_size_properties(env):
     other = U.host(plain.outputs_f32())
     plain.close()
     assert np.abs(other - full).max() < 4e-3   # outputs live in [-1, 1]
+
+
+@gpu
+def test_recording_file_to_batched_inference(env, tmp_path):
+    """Records of the reference's recording format -> planar RGB frames -> batched inference through the pipelined
+    host entry point: same outputs as the device path on the BGRA form of the same frames, action agreement with the
+    oracle on every record, the last (partial) batch included."""
+    U = env
+    import struct
+
+    c = U.ctx()
+    pk = U.pkg()
+    B, H, W, n = 4, 144, 256, 11
+    widths = (32, 64, 128, 256, 256)
+    params = PL.make_cnn_params(6, widths=widths, trivial=False)
+    bgra = PL.make_frames(21, n, H, W)
+    planar = np.ascontiguousarray(bgra[..., [2, 1, 0]].transpose(0, 3, 1, 2))          # what the recorder stores
+    rng = np.random.default_rng(2)
+    keys = rng.integers(0, 1 << 14, n).astype(np.uint16)
+    mouse = rng.integers(-200, 200, (n, 2)).astype(np.int32)
+    path = tmp_path / "training_data.bin"
+    with open(path, "wb") as f:
+        f.write(struct.pack("<ii", W, H))
+        for i in range(n):
+            f.write(struct.pack("<Hii", int(keys[i]), int(mouse[i, 0]), int(mouse[i, 1])))
+            f.write(planar[i].tobytes())
+    rec = pk.Recording(path)
+    assert (rec.width, rec.height, rec.n_records) == (W, H, n)
+    enc = pk.CnnEncoder(c, B, H, W, widths=widths)
+    enc.load_bytes(PL.serialize_cnn_checkpoint(params, W, H))
+    got = rec.infer(enc, 0, n)
+    # the device path on BGRA frames, batch by batch
+    want_dev = []
+    for lo in range(0, n, B):
+        chunk = bgra[lo:lo + B]
+        if chunk.shape[0] < B:
+            chunk = np.concatenate([chunk, np.repeat(chunk[-1:], B - chunk.shape[0], axis=0)])
+        enc.forward(U.dev(chunk))
+        c.sync()
+        want_dev.append(U.host(enc.outputs_f32())[: min(B, n - lo)])
+    assert np.array_equal(got, np.concatenate(want_dev)), "planar RGB records and BGRA frames give different outputs"
+    # a sub-range
+    assert np.array_equal(rec.infer(enc, 3, 5), got[3:8])
+    _, _, want = PL.cnn_forward(params, bgra)
+    want = want.astype(np.float32)
+    assert np.abs(got - want).max() < 2e-3
+    a_got, a_want = O.actions(got, 18, 16), O.actions(want, 18, 16)
+    clear = np.abs(want[:, :16] - 0.5) > 2e-3
+    assert (a_got[:, :16] == a_want[:, :16])[clear].all()
+    # the recorded inputs come back as the reference's training targets (Train.cpp:70-76)
+    _, k, m = rec.read(0, n)
+    t = pk.Recording.targets(k, m)
+    assert np.array_equal(t[:, :14], ((keys[:, None] >> np.arange(14)) & 1).astype(np.float32))
+    enc.close()
+    rec.close()
