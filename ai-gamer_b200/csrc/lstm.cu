@@ -55,7 +55,21 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
 __device__ __forceinline__ void red_release_gpu_add(unsigned int* p, unsigned int v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// Gate non-linearities through the special-function unit (ex2 and rcp approximations, relative error ~2^-22, far
+// below the fp16 rounding of h and c): an exact expf, IEEE division and tanhf per gate made the 128-thread
+// epilogue the longest part of a step.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+__device__ __forceinline__ float tanh_fast(float x) {  // 2*sigmoid(2x) - 1
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -2.8853900817779268f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return fmaf(2.0f, r, -1.0f);
+}
 
 // U = hidden units per CTA (4U gate columns): 8, 16 or 32.
 template <int U>
@@ -206,15 +220,15 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tmapR, const __grid_co
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int u = u0 + e;
-          const float ig = sigmoidf_(__uint_as_float(ri[e]) + gx[0 * U + u]);
-          const float fg = sigmoidf_(__uint_as_float(rf[e]) + gx[1 * U + u]);
-          const float gg = tanhf(__uint_as_float(rg[e]) + gx[2 * U + u]);
-          const float og = sigmoidf_(__uint_as_float(ro[e]) + gx[3 * U + u]);
+          const float ig = sigmoid_fast(__uint_as_float(ri[e]) + gx[0 * U + u]);
+          const float fg = sigmoid_fast(__uint_as_float(rf[e]) + gx[1 * U + u]);
+          const float gg = tanh_fast(__uint_as_float(rg[e]) + gx[2 * U + u]);
+          const float og = sigmoid_fast(__uint_as_float(ro[e]) + gx[3 * U + u]);
           float cn = fg * c[u] + ig * gg;
           if (p.clip > 0.f) cn = fminf(p.clip, fmaxf(-p.clip, cn));
           const __half ch = __float2half(cn);
           c[u] = __half2float(ch);
-          hout[u] = __float2half(og * tanhf(c[u]));
+          hout[u] = __float2half(og * tanh_fast(c[u]));
         }
       }
       // accumulator drained: the MMA issuer may start the next step as soon as h_t is published
@@ -360,8 +374,8 @@ int aig_lstm_plan_create(aig_ctx* ctx, int seq_len, int layers, int hidden, int 
   pl->T = seq_len; pl->L = layers; pl->H = hidden; pl->B = batch; pl->in_c = in_c;
   pl->clip = clip; pl->double_bias = double_bias != 0; pl->batch_major = batch_major != 0;
   pl->groups = ceil_div(batch, kRows);
-  // units per CTA: as many CTAs as fit beside each other, 16 units (64 gate columns) by default
-  pl->U = 16;
+  // units per CTA: the fewest (most CTAs side by side, shortest epilogue per step) that still fit the device
+  pl->U = 8;
   while (pl->U < 32 && (hidden / pl->U) * pl->groups > ctx->sm_count) pl->U *= 2;
   pl->NC = hidden / pl->U;
   if (pl->NC * pl->groups > ctx->sm_count) {
@@ -483,6 +497,7 @@ int aig_lstm_forward(aig_lstm_plan* pl, const aig_half* x, aig_half* y, aig_half
     prm.counter = pl->counters + (size_t)l * pl->groups;
     prm.gerr = ctx->d_err;
     switch (pl->U) {
+      case 8: rc = launch_recurrent<8>(pl, pl->mapR[l], mY, mH0, prm); break;
       case 16: rc = launch_recurrent<16>(pl, pl->mapR[l], mY, mH0, prm); break;
       case 32: rc = launch_recurrent<32>(pl, pl->mapR[l], mY, mH0, prm); break;
       default: rc = aig_fail(ctx, AIG_ERR_UNSUPPORTED, "lstm: unsupported units per CTA %d", pl->U);
