@@ -60,6 +60,7 @@ SIGNATURES = {
     "aig_spatial_mask_forward": [P, P, P, c_float, P, c_int, c_int, c_int],
     "aig_global_avgpool_nhwc": [P, P, P, c_int, c_int, c_int],
     "aig_adaptive_avgpool3d_ndhwc": [P, P, P] + [c_int] * 7,
+    "aig_fc_head_forward": [P, P, P, P, P, P, c_int, c_int, c_int, c_int],
     "aig_cnn_head_forward": [P, P, P, c_float, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int],
     "aig_conv_plan_create": [P, ctypes.POINTER(ConvDesc), PP],
     "aig_conv_plan_destroy": [P],

@@ -458,6 +458,49 @@ __global__ void global_avgpool_nhwc_kernel(const __half* __restrict__ x, __half*
   }
 }
 
+// block per (b, cell): 512 threads = (C/8 channel vectors, 16 bytes each) x position groups; every thread sums a
+// strided subset of the cell's D x h x w positions, then a fixed-order tree over the groups (deterministic)
+__global__ void __launch_bounds__(512) adaptive_avgpool3d_vec_kernel(const __half* __restrict__ x, __half* __restrict__ y, int batch, int D, int H, int W, int C,
+                                                                     int ph, int pw) {
+  __shared__ float s_part[512 * 8];
+  const int cell = blockIdx.x % (ph * pw), b = blockIdx.x / (ph * pw);
+  const int oh = cell / pw, ow = cell % pw;
+  const int h0 = (oh * H) / ph, h1 = ((oh + 1) * H + ph - 1) / ph;
+  const int w0 = (ow * W) / pw, w1 = ((ow + 1) * W + pw - 1) / pw;
+  const int cw = w1 - w0, chh = h1 - h0, npos = D * chh * cw;
+  const int cv = C / 8, groups = 512 / cv;            // C/8 divides 512
+  const int v = threadIdx.x % cv, g = threadIdx.x / cv;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (g < groups) {
+    for (int pos = g; pos < npos; pos += groups) {
+      const int iw = w0 + pos % cw, t = pos / cw, ih = h0 + t % chh, d = t / chh;
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + ((((size_t)b * D + d) * H + ih) * W + iw) * C) + v);
+      const __half2* hq = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(hq[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) s_part[threadIdx.x * 8 + e] = acc[e];
+  __syncthreads();
+  for (int half = groups / 2; half >= 1; half /= 2) {
+    if (g < half) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_part[threadIdx.x * 8 + e] += s_part[(threadIdx.x + half * cv) * 8 + e];
+    }
+    __syncthreads();
+  }
+  if (g == 0) {
+    const float inv = 1.0f / (float)npos;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[((size_t)b * C + v * 8 + e) * ph * pw + cell] = __float2half(s_part[threadIdx.x * 8 + e] * inv);
+  }
+}
+
 __global__ void adaptive_avgpool3d_kernel(const __half* __restrict__ x, __half* __restrict__ y, int batch, int D, int H,
                                           int W, int C, int ph, int pw) {
   // block per (b, cell); threads over channels; output order [b][c][ph][pw]
@@ -474,6 +517,30 @@ __global__ void adaptive_avgpool3d_kernel(const __half* __restrict__ x, __half* 
         s += rs;
       }
     y[((size_t)b * C + c) * ph * pw + cell] = __float2half(s / (float)(D * (h1 - h0) * (w1 - w0)));
+  }
+}
+
+// FC head for a handful of rows in one launch: y = half(half(x . W) + b) (the two roundings of FCLayer.cpp:50-51),
+// sigmoid on the first n_sig outputs and tanh on the rest (Sigmoid.cpp:8-12 and the tanh tail), fp16 and fp32
+// results (ConvertHalfToFloat).  One block per row, one warp per output, fp32 accumulation in a fixed order.
+__global__ void fc_head_kernel(const __half* __restrict__ x, const __half* __restrict__ w_in_out, const __half* __restrict__ bias,
+                               __half* __restrict__ out_h, float* __restrict__ out_f, int in_c, int n_out, int n_sig) {
+  extern __shared__ float fch_x[];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < in_c; i += blockDim.x) fch_x[i] = __half2float(x[(size_t)row * in_c + i]);
+  __syncthreads();
+  for (int o = warp; o < n_out; o += nwarps) {
+    float acc = 0.f;
+    for (int k = lane; k < in_c; k += 32) acc = fmaf(fch_x[k], __half2float(w_in_out[(size_t)k * n_out + o]), acc);
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) {
+      float v = __half2float(__float2half(acc));
+      v = __half2float(__float2half(v + (bias ? __half2float(bias[o]) : 0.f)));
+      const float a = o < n_sig ? 1.0f / (1.0f + expf(-v)) : tanhf(v);
+      const __half h = __float2half(a);
+      out_h[(size_t)row * n_out + o] = h;
+      if (out_f) out_f[(size_t)row * n_out + o] = __half2float(h);
+    }
   }
 }
 
@@ -771,7 +838,22 @@ int aig_adaptive_avgpool3d_ndhwc(aig_ctx* ctx, const aig_half* x, aig_half* y, i
   AIG_REQUIRE(ctx, x && y && batch >= 0 && d > 0 && h > 0 && w > 0 && c > 0 && ph > 0 && pw > 0 && ph <= h && pw <= w,
               "aig_adaptive_avgpool3d_ndhwc: bad arguments");
   if (batch == 0) return AIG_OK;
-  adaptive_avgpool3d_kernel<<<batch * ph * pw, 128, 0, ctx->stream>>>((const __half*)x, (__half*)y, batch, d, h, w, c, ph, pw);
+  if (c % 8 == 0 && 512 % (c / 8) == 0 && ((uintptr_t)x & 15) == 0)
+    adaptive_avgpool3d_vec_kernel<<<batch * ph * pw, 512, 0, ctx->stream>>>((const __half*)x, (__half*)y, batch, d, h, w, c, ph, pw);
+  else
+    adaptive_avgpool3d_kernel<<<batch * ph * pw, 128, 0, ctx->stream>>>((const __half*)x, (__half*)y, batch, d, h, w, c, ph, pw);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int aig_fc_head_forward(aig_ctx* ctx, const aig_half* x, const aig_half* w_in_out, const aig_half* bias, aig_half* out_half, float* out_f32,
+                        int rows, int in_c, int n_out, int n_sigmoid) {
+  AIG_ENTER(ctx);
+  AIG_REQUIRE(ctx, x && w_in_out && out_half && rows >= 0 && in_c > 0 && n_out > 0 && n_sigmoid >= 0 && n_sigmoid <= n_out && in_c <= 12288,
+              "aig_fc_head_forward: bad arguments");
+  if (rows == 0) return AIG_OK;
+  fc_head_kernel<<<rows, 256, in_c * sizeof(float), ctx->stream>>>((const __half*)x, (const __half*)w_in_out, (const __half*)bias, (__half*)out_half,
+                                                                    out_f32, in_c, n_out, n_sigmoid);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }

@@ -24,6 +24,7 @@ struct aig_c3d {
   std::vector<aig_half*> acts;
   std::vector<int> d, h, w;
   aig_half *feat = nullptr, *logits = nullptr;
+  aig_half *fcw = nullptr, *fcb = nullptr;   // FC parameters as loaded ([in][out], [out])
   float* out_f32 = nullptr;
   uint8_t* params = nullptr;
   bool loaded = false;
@@ -138,6 +139,8 @@ int aig_c3d_load_memory(aig_c3d* m, const void* blob, size_t bytes) {
   aig_half* fb = (aig_half*)take((size_t)c.n_out * 2);
   if (!fw || !fb) return cfail(m, AIG_ERR_CUDA, aig_last_error(m->ctx));
   C3D_OK(m, aig_fc_plan_set_weights(m->fc, fw, fb, nullptr, nullptr, nullptr, nullptr, 0.f));
+  m->fcw = fw;
+  m->fcb = fb;
   C3D_OK(m, aig_ctx_sync(m->ctx));
   m->loaded = true;
   return AIG_OK;
@@ -152,6 +155,11 @@ int aig_c3d_forward(aig_c3d* m, const aig_half* clips) {
   for (size_t i = 0; i < m->convs.size(); ++i) C3D_OK(m, aig_conv_forward(m->convs[i], m->acts[i], nullptr, m->acts[i + 1]));
   const int L = c.n_layers - 1;
   C3D_OK(m, aig_adaptive_avgpool3d_ndhwc(m->ctx, m->acts[L], m->feat, c.batch, m->d[L], m->h[L], m->w[L], c.widths[c.n_layers], 2, 2));
+  if (c.batch <= 64) {
+    // FC, sigmoid / tanh and the half -> float conversion in one launch (a block per clip)
+    C3D_OK(m, aig_fc_head_forward(m->ctx, m->feat, m->fcw, m->fcb, m->logits, m->out_f32, c.batch, c.widths[c.n_layers] * 4, c.n_out, c.n_sigmoid));
+    return AIG_OK;
+  }
   C3D_OK(m, aig_conv_forward(m->fc, m->feat, nullptr, m->logits));
   C3D_OK(m, aig_sigmoid_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));
   if (c.n_sigmoid < c.n_out) C3D_OK(m, aig_tanh_tail_forward(m->ctx, m->logits, c.n_out, c.n_sigmoid, c.batch * c.n_out));

@@ -137,6 +137,12 @@ int aig_global_avgpool_nhwc(aig_ctx* ctx, const aig_half* x_nhwc, aig_half* y, i
 int aig_cnn_head_forward(aig_ctx* ctx, const aig_half* x_nhwc, const aig_half* mask_w, float mask_b,
                          const aig_half* fc_w, const aig_half* fc_b, aig_half* feat, aig_half* out_half,
                          float* out_f32, int batch, int hw, int c, int n_out, int n_sigmoid);
+/* FCLayer::Forward (FCLayer.cpp:48-53, both roundings), Sigmoid::Forward on the first n_sigmoid outputs
+ * (Sigmoid.cpp:8-12), tanh on the rest and ConvertHalfToFloat (CudaStuff.cu:174-181) as ONE launch, for heads with
+ * few rows (one block per row): x [rows][in_c], W [in_c][n_out], bias [n_out] or null; out_half / out_f32
+ * [rows][n_out] (out_f32 may be null). */
+int aig_fc_head_forward(aig_ctx* ctx, const aig_half* x, const aig_half* w_in_out, const aig_half* bias, aig_half* out_half,
+                        float* out_f32, int rows, int in_c, int n_out, int n_sigmoid);
 /* Not in the reference: adaptive average pool of channels-last [batch][d][h][w][c] over d and
  * ph x pw spatial cells -> [batch][c*ph*pw] in (c, ph, pw) order. */
 int aig_adaptive_avgpool3d_ndhwc(aig_ctx* ctx, const aig_half* x, aig_half* y, int batch, int d, int h,

@@ -280,3 +280,26 @@ def test_mask_attention_and_pools(env):
     c.call("aig_adaptive_avgpool3d_ndhwc", U.p(d3), U.p(dq), 2, 3, 6, 10, 16, 2, 2)
     U.assert_close16(U.host(dq).reshape(2, 64), O.adaptive_avgpool3d(x3, 2, 2), max_ulp=1, frac_exact=0.98, what="adaptive pool")
     c.sync()
+
+
+@gpu
+def test_fc_head_one_launch(env):
+    """FCLayer + Sigmoid (+ tanh tail) + ConvertHalfToFloat as one launch against the oracle's chain of the three."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    rng = np.random.default_rng(12)
+    for rows, in_c, n_out, n_sig in ((16, 512, 18, 16), (3, 256, 16, 14), (1, 1000, 7, 7)):
+        x = rng.standard_normal((rows, in_c)).astype(np.float16)
+        W = (rng.standard_normal((in_c, n_out)) / np.sqrt(in_c)).astype(np.float16)
+        b = rng.uniform(-0.2, 0.2, n_out).astype(np.float16)
+        want = O.tanh_tail(O.sigmoid_head(O.fc(x, W, b), n_out, n_sig), n_out, n_sig)
+        oh = torch.zeros(rows * n_out, dtype=torch.float16, device="cuda")
+        of = torch.zeros(rows * n_out, dtype=torch.float32, device="cuda")
+        dx, dW, db = U.dev(x), U.dev(W), U.dev(b)
+        c.call("aig_fc_head_forward", U.p(dx), U.p(dW), U.p(db), U.p(oh), U.p(of), rows, in_c, n_out, n_sig)
+        c.sync()
+        got = U.host(oh).reshape(rows, n_out)
+        U.assert_close16(got, want, max_ulp=2, frac_exact=0.9, what="fc head")
+        assert np.array_equal(U.host(of).reshape(rows, n_out), got.astype(np.float32))
