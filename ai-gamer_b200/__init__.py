@@ -44,6 +44,9 @@ SIGNATURES = {
     "aig_preprocess_bgra": [P, P, P, c_int, c_int],
     "aig_unconvert_unnormalize": [P, P, P, c_size_t],
     "aig_half_to_float": [P, P, P, c_size_t],
+    "aig_resize_box": [P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int],
+    "aig_process_output": [P, P, P, c_int],
+    "aig_process_output_to": [P, P, P, P],
     "aig_float_to_half": [P, P, P, c_size_t],
     "aig_nchw_to_nhwc": [P, P, P, c_int, c_int, c_int],
     "aig_nhwc_to_nchw": [P, P, P, c_int, c_int, c_int],

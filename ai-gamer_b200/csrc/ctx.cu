@@ -182,4 +182,27 @@ int aig_actions_from_outputs(const float* p, int* actions, int frames, int n_ctr
   return AIG_OK;
 }
 
+// Infer.cpp:8-57 without the Win32 call: the INPUT array the reference hands to SendInput, as portable events
+int aig_process_output(const float* p, const unsigned char* key_map, aig_input_event* events, int capacity) {
+  if (!p || !key_map || (!events && capacity > 0) || capacity < 0) return AIG_ERR_INVALID;
+  int n = 0;
+  auto put = [&](int type, int code, int down, int dx, int dy) {
+    if (n < capacity) events[n] = aig_input_event{type, code, down, dx, dy};
+    ++n;
+  };
+  for (int i = 0; i < 11; ++i) put(AIG_EVENT_KEY, key_map[i], p[i] > 0.5f ? 1 : 0, 0, 0);
+  for (int b = 0; b < 3; ++b) put(AIG_EVENT_MOUSE_BUTTON, b, p[11 + b] > 0.5f ? 1 : 0, 0, 0);
+  const int mx = static_cast<int>(p[14] * 256.0f), my = static_cast<int>(p[15] * 256.0f);
+  if (mx != 0 || my != 0) put(AIG_EVENT_MOUSE_MOVE, 0, 0, mx, my);
+  return n;
+}
+
+int aig_process_output_to(const float* p, const unsigned char* key_map, aig_event_sink sink, void* user) {
+  if (!sink) return AIG_ERR_INVALID;
+  aig_input_event ev[16];
+  const int n = aig_process_output(p, key_map, ev, 16);
+  for (int i = 0; i < n; ++i) sink(&ev[i], user);
+  return n;
+}
+
 }  // extern "C"

@@ -106,6 +106,39 @@ __global__ void unconvert_kernel(uint8_t* __restrict__ out, const __half* __rest
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = static_cast<unsigned char>(__half2float(in[i]) * 255.0f);
 }
+// Box-filter down-scaling of uint8 frames (ConvScale.cpp:41-52 = ConvertAndNormalize + k x k stride-k convolution with
+// an all-half(1/k^2) filter + UnConvertAndUnNormalize), with the colour split of ARGBtoRGBplanar fused in when the
+// source is BGRA.  One thread per output pixel (x fastest).  fp32 accumulation in a fixed order (channel, row,
+// column), one fused multiply-add per tap: the same order as the oracle, hence bit-exact.
+template <bool BGRA>
+__global__ void resize_box_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ out_u8, __half* __restrict__ out_half, int frames, int C,
+                                  int H, int W, int k, int cross) {
+  const int Ho = H / k, Wo = W / k;
+  const long long total = (long long)frames * C * Ho * Wo;
+  const float wk = __half2float(__float2half(1.0f / (float)(k * k)));
+  const float inv255 = __uint_as_float(0x3B808081u);  // half(b * fl(1/255)) == half(b / 255.0f) for every byte b
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int ox = (int)(i % Wo);
+    long long t = i / Wo;
+    const int oy = (int)(t % Ho);
+    t /= Ho;
+    const int c = (int)(t % C), n = (int)(t / C);
+    float acc = 0.f;
+    for (int ci = cross ? 0 : c; ci < (cross ? C : c + 1); ++ci)
+      for (int dy = 0; dy < k; ++dy) {
+        const int y = oy * k + dy;
+        for (int dx = 0; dx < k; ++dx) {
+          const int x = ox * k + dx;
+          const uint8_t b = BGRA ? src[(((size_t)n * H + y) * W + x) * 4 + (2 - ci)] : src[(((size_t)n * C + ci) * H + y) * W + x];
+          acc = fmaf(__half2float(__float2half(__fmul_rn((float)b, inv255))), wk, acc);
+        }
+      }
+    const __half hv = __float2half(acc);
+    if (out_half) out_half[i] = hv;
+    if (out_u8) out_u8[i] = static_cast<unsigned char>(__half2float(hv) * 255.0f);
+  }
+}
+
 __global__ void half_to_float_kernel(const __half* __restrict__ src, float* __restrict__ dst, size_t n) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     dst[i] = __half2float(src[i]);
@@ -631,6 +664,22 @@ int aig_unconvert_unnormalize(aig_ctx* ctx, uint8_t* out, const aig_half* in, si
   AIG_REQUIRE(ctx, out && in, "aig_unconvert_unnormalize: null pointer");
   if (n == 0) return AIG_OK;
   unconvert_kernel<<<grid_for(ctx, (long long)n), kThreads, 0, ctx->stream>>>(out, (const __half*)in, n);
+  AIG_LAUNCH_OK(ctx);
+  return AIG_OK;
+}
+
+int aig_resize_box(aig_ctx* ctx, const uint8_t* src, int src_is_bgra, uint8_t* out_u8, aig_half* out_half, int frames, int channels, int h,
+                   int w, int k, int cross_channel_sum) {
+  AIG_ENTER(ctx);
+  AIG_REQUIRE(ctx, src && (out_u8 || out_half) && frames >= 0 && channels > 0 && h > 0 && w > 0 && k > 0 && k <= h && k <= w,
+              "aig_resize_box: bad arguments");
+  AIG_REQUIRE(ctx, !src_is_bgra || channels == 3, "aig_resize_box: BGRA frames have three colour channels");
+  const long long total = (long long)frames * channels * (h / k) * (w / k);
+  if (total == 0) return AIG_OK;
+  if (src_is_bgra)
+    resize_box_kernel<true><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(src, out_u8, (__half*)out_half, frames, channels, h, w, k, cross_channel_sum);
+  else
+    resize_box_kernel<false><<<grid_for(ctx, total), kThreads, 0, ctx->stream>>>(src, out_u8, (__half*)out_half, frames, channels, h, w, k, cross_channel_sum);
   AIG_LAUNCH_OK(ctx);
   return AIG_OK;
 }

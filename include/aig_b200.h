@@ -77,6 +77,17 @@ int aig_convert_normalize(aig_ctx* ctx, aig_half* out, const uint8_t* in, size_t
 int aig_preprocess_bgra(aig_ctx* ctx, const uint8_t* bgra, aig_half* out_nchw, int frames, int hw);
 /* UnConvertAndUnNormalize (CudaStuff.cu:158-165). */
 int aig_unconvert_unnormalize(aig_ctx* ctx, uint8_t* out, const aig_half* in, size_t n);
+/* ConvScale::ScaleInPlace / ScaleToHalf (ConvScale.cpp:41-52) and GrabFrameScaleInt8 / GrabFrameScaleFP16
+ * (NvDisplayCap.h:91-119): k x k box-filter down-scaling of uint8 frames -- ConvertAndNormalize, a stride-k
+ * convolution with an all-half(1/k^2) filter, fp16 result, UnConvertAndUnNormalize -- as one kernel.  src: planar
+ * [frames][channels][h][w] bytes, or with src_is_bgra BGRA pixels [frames][h][w][4] (the colour split of
+ * ARGBtoRGBplanar, CudaStuff.cu:63-74, is then fused in; channels = 3).  out_u8 and/or out_half: planar
+ * [frames][channels][h/k][w/k].  The reference leaves the accumulation order to cuDNN; here it is fixed (fp32,
+ * channel-major then row-major, one fused multiply-add per tap), identical in the CPU oracle, so results are
+ * bit-exact.  cross_channel_sum = 1 reproduces the reference's filter, which adds the box means of all three
+ * channels into every output channel (ConvScale.cpp:10,17-18); 0 keeps channels apart. */
+int aig_resize_box(aig_ctx* ctx, const uint8_t* src, int src_is_bgra, uint8_t* out_u8, aig_half* out_half, int frames,
+                   int channels, int h, int w, int k, int cross_channel_sum);
 /* ConvertHalfToFloat / ConvertFloatToHalf (CudaStuff.cu:166-181). */
 int aig_half_to_float(aig_ctx* ctx, const aig_half* src, float* dst, size_t n);
 int aig_float_to_half(aig_ctx* ctx, const float* src, aig_half* dst, size_t n);
@@ -322,6 +333,23 @@ int aig_mha_reset(aig_mha_plan* plan);
 /* Output decisions of Infer::ProcessOutput (Infer.cpp:8-57) as a pure function on host values:
  * actions[i] = p[i] > 0.5 for i < n_buttons, (int)(p[i]*256.0f) otherwise. */
 int aig_actions_from_outputs(const float* p, int* actions, int frames, int n_ctrls, int n_buttons);
+
+/* Infer::ProcessOutput (Infer.cpp:8-57) as a portable event list instead of Win32 SendInput: the same events in the
+ * same order -- a key event for each of the 11 keyboard outputs (scan code key_map[i], down iff p[i] > 0.5), a
+ * button event for outputs 11, 12, 13 (left, right, middle; down iff > 0.5) and, when either is non-zero, one
+ * relative mouse move by ((int)(p[14]*256.0f), (int)(p[15]*256.0f)).  `predictions` are the 16 values of one frame. */
+enum { AIG_EVENT_KEY = 0, AIG_EVENT_MOUSE_BUTTON = 1, AIG_EVENT_MOUSE_MOVE = 2 };
+typedef struct aig_input_event {
+  int type;   /* AIG_EVENT_* */
+  int code;   /* scan code (key) or 0/1/2 = left/right/middle (button) */
+  int down;   /* 1 = press, 0 = release */
+  int dx, dy; /* mouse move */
+} aig_input_event;
+/* Writes at most `capacity` events (15 suffice) and returns how many the frame produces. */
+int aig_process_output(const float* predictions, const unsigned char* key_map, aig_input_event* events, int capacity);
+/* The same, handing every event to `sink` (a uinput writer, a network sender, a test recorder ...). */
+typedef void (*aig_event_sink)(const aig_input_event* event, void* user);
+int aig_process_output_to(const float* predictions, const unsigned char* key_map, aig_event_sink sink, void* user);
 
 #ifdef __cplusplus
 }

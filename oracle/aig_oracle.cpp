@@ -74,6 +74,35 @@ void orc_convert_normalize(f16* out, const uint8_t* in, size_t n) {
 void orc_unconvert_unnormalize(uint8_t* out, const f16* in, size_t n) {
   for (size_t i = 0; i < n; ++i) out[i] = (uint8_t)(h2f(in[i]) * 255.0f);
 }
+// ConvScale::ScaleInPlace / ScaleToHalf (ConvScale.cpp:41-52): ConvertAndNormalize, a k x k stride-k convolution whose
+// filter holds half(1/k^2) everywhere (ConvScale.cpp:17-18), fp16 result, and for ScaleInPlace
+// UnConvertAndUnNormalize.  cuDNN's accumulation order is not specified, so the order is fixed here: fp32, one fused
+// multiply-add per tap, channel-major, then row-major inside the k x k window.  cross_channel = 1 reproduces the
+// reference's filter, which sums the box means of all three channels into every output channel (its filter is
+// [3][3][k][k], all equal); 0 keeps the channels apart (a plain box filter).
+// src: planar [frames][C][H][W] bytes or, bgra = 1, BGRA pixels [frames][H][W][4] read as planes R, G, B (C = 3).
+// out_u8 / out_half: planar [frames][C][H/k][W/k]; either may be null.
+void orc_resize_box(const uint8_t* src, uint8_t* out_u8, f16* out_half, int frames, int C, int H, int W, int k, int cross_channel, int bgra) {
+  const int Ho = H / k, Wo = W / k;
+  const float wk = h2f(f2h(1.0f / (float)(k * k)));
+  auto px = [&](int n, int c, int y, int x) -> float {
+    const uint8_t b = bgra ? src[(((size_t)n * H + y) * W + x) * 4 + (2 - c)] : src[(((size_t)n * C + c) * H + y) * W + x];
+    return h2f(f2h((float)b / 255.0f));
+  };
+  for (int n = 0; n < frames; ++n)
+    for (int c = 0; c < C; ++c)
+      for (int oy = 0; oy < Ho; ++oy)
+        for (int ox = 0; ox < Wo; ++ox) {
+          float acc = 0.f;
+          for (int ci = cross_channel ? 0 : c; ci < (cross_channel ? C : c + 1); ++ci)
+            for (int dy = 0; dy < k; ++dy)
+              for (int dx = 0; dx < k; ++dx) acc = fmaf(px(n, ci, oy * k + dy, ox * k + dx), wk, acc);
+          const f16 hv = f2h(acc);
+          const size_t o = (((size_t)n * C + c) * Ho + oy) * Wo + ox;
+          if (out_half) out_half[o] = hv;
+          if (out_u8) out_u8[o] = (uint8_t)(h2f(hv) * 255.0f);
+        }
+}
 // CudaStuff.cu:174-177 / 166-169.
 void orc_half_to_float(const f16* src, float* dst, size_t n) {
   for (size_t i = 0; i < n; ++i) dst[i] = h2f(src[i]);

@@ -87,6 +87,21 @@ def unconvert_unnormalize(hf):
     return out
 
 
+def resize_box(src, k, cross_channel=False, bgra=False):
+    """ConvScale.cpp:41-52 with the fixed summation order.  src: planar uint8 [N][C][H][W], or BGRA [N][H][W][4];
+    returns (uint8, float16) planar [N][C][H//k][W//k]."""
+    src = np.ascontiguousarray(src, dtype=np.uint8)
+    if bgra:
+        N, H, W, _ = src.shape
+        C = 3
+    else:
+        N, C, H, W = src.shape
+    o8 = np.empty((N, C, H // k, W // k), np.uint8)
+    oh = np.empty((N, C, H // k, W // k), np.float16)
+    lib().orc_resize_box(_p(src), _p(o8), _p(oh), *map(_c_int, (N, C, H, W, k, 1 if cross_channel else 0, 1 if bgra else 0)))
+    return o8, oh
+
+
 def half_to_float(hf):
     hf = _h(hf)
     out = np.empty(hf.shape, np.float32)

@@ -104,3 +104,32 @@ def test_checkpoint_size_matches_writer(pkg):
     blob = SY.serialize_cnn_checkpoint(SY.make_cnn_params(0, widths=widths), 256, 144)
     assert pkg.lib().aig_cnn_checkpoint_bytes(ctypes.byref(cfg)) == len(blob)
     assert np.frombuffer(blob[:8], np.int32).tolist() == [256, 144]  # NN.cpp:118-119: width then height
+
+
+def test_process_output_event_list(pkg):
+    """Infer::ProcessOutput (Infer.cpp:8-57) as a portable event list: 11 key events, 3 mouse-button events, one
+    relative move when it is non-zero, in the reference's order; the callback form delivers the same events."""
+    import ctypes
+
+    class Event(ctypes.Structure):
+        _fields_ = [(n, ctypes.c_int) for n in ("type", "code", "down", "dx", "dy")]
+
+    lib = pkg.lib()
+    key_map = (ctypes.c_ubyte * 14)(*range(30, 44))
+    p = np.array([0.9, 0.1, 0.5, 0.51, 0, 1, 0, 0, 0, 0.7, 0.2, 0.6, 0.4, 0.99, 0.25, -0.031], np.float32)
+    ev = (Event * 16)()
+    n = lib.aig_process_output(pkg.ptr(p), key_map, ev, 16)
+    assert n == 15
+    keys = [(e.type, e.code, e.down) for e in ev[:11]]
+    assert keys == [(0, 30 + i, int(p[i] > 0.5)) for i in range(11)]          # p == 0.5 is a release (Infer.cpp:15)
+    assert [(e.type, e.code, e.down) for e in ev[11:14]] == [(1, 0, 1), (1, 1, 0), (1, 2, 1)]
+    assert (ev[14].type, ev[14].dx, ev[14].dy) == (2, 64, -7)                  # (int)(p*256.0f): truncation toward zero
+    p[14:] = [0.003, -0.003]                                                   # both truncate to zero: no move event
+    assert lib.aig_process_output(pkg.ptr(p), key_map, ev, 16) == 14
+    assert lib.aig_process_output(pkg.ptr(p), key_map, ev, 3) == 14            # count returned even when capacity is short
+    got = []
+    SINK = ctypes.CFUNCTYPE(None, ctypes.POINTER(Event), ctypes.c_void_p)
+    sink = SINK(lambda e, user: got.append((e.contents.type, e.contents.code, e.contents.down)))
+    assert lib.aig_process_output_to(pkg.ptr(p), key_map, sink, None) == 14
+    assert got[:11] == keys and len(got) == 14
+    assert lib.aig_process_output(None, key_map, ev, 16) == -1

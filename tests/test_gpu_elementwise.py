@@ -303,3 +303,30 @@ def test_fc_head_one_launch(env):
         got = U.host(oh).reshape(rows, n_out)
         U.assert_close16(got, want, max_ulp=2, frac_exact=0.9, what="fc head")
         assert np.array_equal(U.host(of).reshape(rows, n_out), got.astype(np.float32))
+
+
+@gpu
+@pytest.mark.parametrize("k", [2, 3, 4])
+def test_resize_box_bit_exact(env, k):
+    """ConvScale::ScaleInPlace / ScaleToHalf (ConvScale.cpp:41-52) and GrabFrameScale* (NvDisplayCap.h:91-119) as one
+    kernel: bit-exact against the oracle on odd sizes, from planar frames and from BGRA pixels, with the reference's
+    cross-channel filter and with the per-channel box filter."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    rng = np.random.default_rng(40 + k)
+    N, H, W = 3, 37, 53
+    planar = rng.integers(0, 256, (N, 3, H, W), dtype=np.uint8)
+    bgra = np.zeros((N, H, W, 4), np.uint8)
+    bgra[..., 2], bgra[..., 1], bgra[..., 0], bgra[..., 3] = planar[:, 0], planar[:, 1], planar[:, 2], 255
+    for cross in (0, 1):
+        w8, wh = O.resize_box(planar, k, cross_channel=bool(cross))
+        for src, is_bgra in ((planar, 0), (bgra, 1)):
+            o8 = torch.zeros(w8.size, dtype=torch.uint8, device="cuda")
+            oh = torch.zeros(wh.size, dtype=torch.float16, device="cuda")
+            dsrc = U.dev(src)
+            c.call("aig_resize_box", U.p(dsrc), is_bgra, U.p(o8), U.p(oh), N, 3, H, W, k, cross)
+            c.sync()
+            assert np.array_equal(U.host(o8).reshape(w8.shape), w8)
+            assert np.array_equal(U.host(oh).reshape(wh.shape).view(np.uint16), wh.view(np.uint16))

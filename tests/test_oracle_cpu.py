@@ -296,3 +296,34 @@ def test_oracle_matches_outputs_of_the_reference_kernels():
     d = _ulp_diff(y.reshape(-1).view(np.uint16), g["ln_y"].reshape(-1))
     big = np.abs(y.reshape(-1).astype(np.float32)) > 2e-3
     assert d[big].max() <= 2 and (d == 0).mean() > 0.97
+
+
+def test_resize_box_definition(oracle):
+    """The oracle's box-filter resize (ConvScale.cpp:41-52 with a fixed summation order) against a direct numpy
+    restatement: fp32 fused multiply-adds in (channel, row, column) order are reproduced here with float64 products
+    of fp16-exact operands, which are exact, so every partial sum can be rounded to fp32 explicitly."""
+    O = oracle
+    rng = np.random.default_rng(4)
+    for (N, C, H, W, k, cross) in ((2, 3, 9, 14, 2, False), (1, 3, 10, 11, 3, True), (1, 3, 8, 8, 4, False)):
+        src = rng.integers(0, 256, (N, C, H, W), dtype=np.uint8)
+        o8, oh = O.resize_box(src, k, cross_channel=cross)
+        wk = np.float64(np.float16(np.float32(1.0) / np.float32(k * k)))
+        xn = O.convert_normalize(src).astype(np.float64)
+        want = np.zeros((N, C, H // k, W // k), np.float16)
+        for n in range(N):
+            for c in range(C):
+                for oy in range(H // k):
+                    for ox in range(W // k):
+                        acc = np.float32(0.0)
+                        for ci in (range(C) if cross else [c]):
+                            for dy in range(k):
+                                for dx in range(k):
+                                    acc = np.float32(np.float64(acc) + xn[n, ci, oy * k + dy, ox * k + dx] * wk)   # one rounding = fmaf
+                        want[n, c, oy, ox] = np.float16(acc)
+        assert np.array_equal(oh.view(np.uint16), want.view(np.uint16))
+        assert np.array_equal(o8, (want.astype(np.float32) * np.float32(255.0)).astype(np.uint8))
+        # BGRA source = the same planes read from interleaved pixels
+        bgra = np.zeros((N, H, W, 4), np.uint8)
+        bgra[..., 2], bgra[..., 1], bgra[..., 0], bgra[..., 3] = src[:, 0], src[:, 1], src[:, 2], 255
+        o8b, ohb = O.resize_box(bgra, k, cross_channel=cross, bgra=True)
+        assert np.array_equal(o8b, o8) and np.array_equal(ohb.view(np.uint16), oh.view(np.uint16))
