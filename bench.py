@@ -223,7 +223,8 @@ def cpu_baseline_block(workload, repeats=3):
             "sample": "%s, median of %d runs (%.2f s each), OpenMP over all host threads" % (what, len(times), float(np.median(times)))}
 
 
-METRICS = {"cnn2d": ("frames/s per GPU-batch of 256, summed over the GPUs", "frames/s", "cnn2d_encoder_144x256_b256"),
+METRICS = {"agent_stream": ("frames/s of one sequence, one frame per step (device-resident frames)", "frames/s", "streaming_agent_b1_window64"),
+           "cnn2d": ("frames/s per GPU-batch of 256, summed over the GPUs", "frames/s", "cnn2d_encoder_144x256_b256"),
            "conv3d": ("clips/s (16 clips of 8x144x256 per GPU), summed over the GPUs", "clips/s", "conv3d_clip_encoder_8x144x256_b16"),
            "seqhead": ("frame-steps/s (128 sequences x 64 steps per GPU), summed over the GPUs", "frame-steps/s", "seqhead_lstm2x512_mha8x64_b128_t64"),
            "agent_batched": ("frames/s (128 sequences per GPU, one frame each per step), summed over the GPUs", "frames/s",
@@ -620,8 +621,21 @@ def reference_call_pattern(env):
                     "46 library launches per step, planar fp16 input already on the device, no head", "layers": layers}
 
 
-LEGS = {"cnn2d": leg_cnn2d, "conv3d": leg_conv3d, "seqhead": leg_seqhead, "agent_batched": leg_agent_batched}
-GLOBAL_BATCH = {"cnn2d": None, "conv3d": 16, "seqhead": SEQ_B, "agent_batched": 128}
+def leg_agent_stream(env, full):
+    """Profiler captures only: the batch-1 streaming agent on device-resident frames (encoder graph, bridge FC, the
+    one-kernel sequence-head step); the timed form of this workload is the `latency` block."""
+    torch, SY, R, args = env.torch, env.SY, env.R, env.args
+    agent = R.Agent(env.ctx, 1, HEIGHT, WIDTH, widths=WIDTHS, d=512, layers=2, heads=8, n_out=N_OUT, n_sigmoid=N_SIG, window=64)
+    agent.load_bytes(SY.serialize_agent_params(SY.make_agent_params(0, widths=WIDTHS), WIDTH, HEIGHT))
+    frames = [torch.randint(0, 256, (1, HEIGHT, WIDTH, 4), dtype=torch.uint8, device="cuda") for _ in range(4)]
+    res = env.timer.regions(lambda i: agent.step(frames[i % 4]), args.steps, args.warmup)
+    agent.close()
+    return {"value": 1.0 / (res["ms_per_step"] * 1e-3), "unit": "frames/s", **res, "l2": "batch 1: weights stay in L2 by design",
+            "roofline": {"bound": "hbm", "kernel": "seq_step_kernel", "achieved": None}}
+
+
+LEGS = {"agent_stream": leg_agent_stream, "cnn2d": leg_cnn2d, "conv3d": leg_conv3d, "seqhead": leg_seqhead, "agent_batched": leg_agent_batched}
+GLOBAL_BATCH = {"agent_stream": 1, "cnn2d": None, "conv3d": 16, "seqhead": SEQ_B, "agent_batched": 128}
 
 
 def main():
@@ -659,7 +673,7 @@ def main():
         return
     head = LEGS[wl](env, True)
     extra = {}
-    others = [w for w in LEGS if w != wl] if args.legs == "all" else ([] if args.legs == "none" else [w for w in args.legs.split(",") if w in LEGS and w != wl])
+    others = [w for w in LEGS if w != wl and w != "agent_stream"] if args.legs == "all" else ([] if args.legs == "none" else [w for w in args.legs.split(",") if w in LEGS and w != wl])
     for w in others:
         extra[w] = LEGS[w](env, env.world == 1)
     latency = streaming_latency(env, args.latency_frames) if env.rank == 0 and not args.no_latency else None

@@ -302,7 +302,12 @@ int aig_lstm_forward(aig_lstm_plan* plan, const aig_half* x, aig_half* y, aig_ha
  * in_c a multiple of 8, seq_len*batch*4*hidden <= 524288 (2 MiB of fp32); larger shapes return
  * AIG_ERR_UNSUPPORTED.  All calls on a device share the array: calls that overlap on the GPU race, so
  * serialise them; each call clears what must start at zero.  The first call on a device looks up the
- * array's device address and should come before any stream capture. */
+ * array's device address and should come before any stream capture.  That first call may also be the one
+ * that makes the CUDA runtime load this library's device image (module loading is lazy by default), which is
+ * when the driver sets the array's memory aside: make one warm-up call per device at start-up, and only after it
+ * does "allocates nothing" hold.  Calls must come from one host thread at a time (the per-device address cache
+ * and the kernel's attribute set-up are not synchronised).  The input projection of this variant is a plain
+ * CUDA-core tile kernel, not the tensor-core GEMM of the plan-based path: sized for what the scratch admits. */
 int aig_lstm_forward_noalloc(aig_ctx* ctx, const aig_half* x, const aig_half* blob, aig_half* y,
                              int seq_len, int batch, int in_c, int hidden, float clip, int double_bias);
 

@@ -38,6 +38,8 @@ def test_noalloc_lstm_matches_plan_entry_point_twice(env):
     pk = U.pkg()
     from ai_gamer_b200 import synth as SY
 
+    from oracle import oracle as O
+
     lib = pk.lib()
     T, B, I, H = 12, 24, 96, 128
     rng = np.random.default_rng(4242)
@@ -47,7 +49,7 @@ def test_noalloc_lstm_matches_plan_entry_point_twice(env):
     plan = pk.LstmPlan(c, T, 1, H, B, I, clip=5.0, double_bias=True)
     plan.set_weights(d_blob)
     for call in range(2):
-        x = rng.standard_normal((T, B, I)).astype(np.float16) * (1.0 + call)
+        x = (rng.standard_normal((T, B, I)) * (1.0 + call)).astype(np.float16)
         dx = U.dev(x)
         want = torch.zeros(T * B * H, dtype=torch.float16, device="cuda")
         plan.forward(dx, want)
@@ -60,7 +62,45 @@ def test_noalloc_lstm_matches_plan_entry_point_twice(env):
         err = np.abs(a - b).max()
         assert err < TOL, "call %d: max |noalloc - plan| = %.4g" % (call, err)
         assert (a == b).mean() > 0.9  # only the projection's summation order differs
+        # and the CPU oracle of the reference's LSTM call on the same inputs
+        ref = O.lstm(x, blob, H, 1, 5.0, True).astype(np.float32).ravel()
+        assert np.abs(a - ref).max() < TOL, "call %d: max |noalloc - oracle| = %.4g" % (call, np.abs(a - ref).max())
     plan.close()
+
+
+@gpu
+@pytest.mark.parametrize("T,B,I,H,dbl", [(2, 128, 512, 512, 1), (4, 128, 40, 256, 0), (16, 3, 8, 64, 1)])
+def test_noalloc_lstm_at_the_limits_of_the_fixed_scratch(env, T, B, I, H, dbl):
+    """The largest batch and hidden size the fixed scratch admits, the single-bias blob, and an input width that is a
+    multiple of 8 but not of 32 (the projection kernel's tile edge): against the oracle and the plan-based entry point."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    pk = U.pkg()
+    from ai_gamer_b200 import synth as SY
+    from oracle import oracle as O
+
+    lib = pk.lib()
+    rng = np.random.default_rng(T * 31 + B)
+    blob = SY.make_lstm_blob(rng, I, H, 1, bool(dbl), 1.0)
+    x = rng.standard_normal((T, B, I)).astype(np.float16)
+    want = O.lstm(x, blob, H, 1, 5.0, bool(dbl)).astype(np.float32).ravel()
+    d_blob, dx = U.dev(blob), U.dev(x)
+    got = torch.full((T * B * H,), 3.0, dtype=torch.float16, device="cuda")
+    rc = lib.aig_lstm_forward_noalloc(c.handle, pk.ptr(dx), pk.ptr(d_blob), pk.ptr(got), T, B, I, H, 5.0, dbl)
+    assert rc == 0, lib.aig_last_error(c.handle).decode()
+    c.sync()
+    a = U.host(got).astype(np.float32)
+    assert np.abs(a - want).max() < TOL
+    if I % 16 == 0:
+        plan = pk.LstmPlan(c, T, 1, H, B, I, clip=5.0, double_bias=bool(dbl))
+        plan.set_weights(d_blob)
+        ref = torch.zeros(T * B * H, dtype=torch.float16, device="cuda")
+        plan.forward(dx, ref)
+        c.sync()
+        assert np.abs(a - U.host(ref).astype(np.float32)).max() < TOL
+        plan.close()
 
 
 @gpu
