@@ -652,9 +652,9 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   const uint32_t sPatch = base;
   const uint32_t sW = base + p.patch_bufs * p.patch_bytes;
   const uint32_t tail = p.patch_bufs * p.patch_bytes + p.w_stages * kWBlock;
-  float* s_scale = reinterpret_cast<float*>(sm + tail);
-  float* s_shift = s_scale + 256;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 2048);
+  float* s_scale = reinterpret_cast<float*>(sm + tail);   // scale/shift of every N tile (up to 512 columns) staged once
+  float* s_shift = s_scale + 512;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + tail + 4096);
   const uint32_t bar_pfull = smem_u32(bars);          // [4]
   const uint32_t bar_pempty = bar_pfull + 32;         // [4]
   const uint32_t bar_tfull = bar_pfull + 64;          // [4]
@@ -664,13 +664,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint32_t* s_tab = s_tmem + 4;
-  uint8_t* s_stage = sm + tail + 5120 + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;  // per-warp staging tile of the epilogue warps
+  uint8_t* s_stage = sm + tail + 7168 + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;  // per-warp staging tile of the epilogue warps
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   griddep_launch_dependents();  // the next launch may set itself up and prefetch its weights under this one
   for (int i = threadIdx.x; i < p.tab_words; i += kPconvThreads) s_tab[i] = p.tab[i];
-  if (p.n_tiles == 1) {
-    for (int i = threadIdx.x; i < NT; i += kPconvThreads) {
+  const bool staged = p.n_tiles * NT <= 512;  // else the epilogue reads scale/shift from global memory
+  if (staged) {
+    for (int i = threadIdx.x; i < p.n_tiles * NT; i += kPconvThreads) {
       s_scale[i] = p.scale[i];
       s_shift[i] = p.shift[i];
     }
@@ -889,8 +890,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const int acc = cnt % p.acc_bufs;
         const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
         const int nb = n_tile * NT;
-        const float* sc = p.n_tiles == 1 ? s_scale : p.scale + nb;
-        const float* sf = p.n_tiles == 1 ? s_shift : p.shift + nb;
+        const float* sc = staged ? s_scale + nb : p.scale + nb;
+        const float* sf = staged ? s_shift + nb : p.shift + nb;
         const OutSeg& sg = p.seg[(nb + col_lo) >= p.n_split ? 1 : 0];
         if (sg.residual) {
           // pull the residual rows of this CTA's next tile (and of its first tile) towards L2 now, so that
@@ -1253,7 +1254,7 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
 // ---- patch-resident path: host side ------------------------------------------------------
 // Shared memory behind the patches and weights: scale/shift, barriers and K schedule tables, then one 2 KB staging
 // tile per epilogue warp (the coalescing epilogue; N = 64 tiles store directly and need none).
-constexpr int pconv_tail(int ew, bool direct_store) { return 5120 + (direct_store ? 0 : ew * 2048); }
+constexpr int pconv_tail(int ew, bool direct_store) { return 7168 + (direct_store ? 0 : ew * 2048); }
 constexpr int pconv_budget(int ew, bool direct_store) { return 227 * 1024 - 1024 /*align*/ - pconv_tail(ew, direct_store); }
 
 template <int NT, int MS, bool WRES, int EW>
