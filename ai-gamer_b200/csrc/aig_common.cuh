@@ -252,6 +252,19 @@ __device__ __forceinline__ void umma_f16_ss_lo(uint32_t d_tmem, uint32_t a_lo, u
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One lane of a converged warp (the same lane on every call).  A loop that all 32 lanes run with identical values
+// and that issues tcgen05.mma / tcgen05.commit under this predicate keeps its address arithmetic in the warp's
+// uniform registers, which is where those instructions take their operands from; a loop run by a single lane
+// inside a divergent branch pays a vector-to-uniform register move for every operand of every instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 // mbarrier arrives once all previously issued tcgen05.mma of this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -83,20 +83,41 @@ __device__ __forceinline__ float act_ct(float v, float slope) {
   return v;
 }
 
+// Eight consecutive per-column scale/shift values: from arrays in the kernel's parameter block (constant bank;
+// CB) or through pointers to shared or global memory.
+struct NoConstAffine {};
+template <bool CB, typename PP>
+__device__ __forceinline__ void load_affine8(const PP& pp, int cidx, const float* __restrict__ sc, const float* __restrict__ sf, int off,
+                                             float (&sv)[8], float (&hv)[8]) {
+  if constexpr (CB) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sv[i] = pp.cscale[cidx + i];
+      hv[i] = pp.cshift[cidx + i];
+    }
+  } else {
+    const float4 s0 = reinterpret_cast<const float4*>(sc + off)[0], s1 = reinterpret_cast<const float4*>(sc + off)[1];
+    const float4 h0 = reinterpret_cast<const float4*>(sf + off)[0], h1 = reinterpret_cast<const float4*>(sf + off)[1];
+    sv[0] = s0.x; sv[1] = s0.y; sv[2] = s0.z; sv[3] = s0.w; sv[4] = s1.x; sv[5] = s1.y; sv[6] = s1.z; sv[7] = s1.w;
+    hv[0] = h0.x; hv[1] = h0.y; hv[2] = h0.z; hv[3] = h0.w; hv[4] = h1.x; hv[5] = h1.y; hv[6] = h1.z; hv[7] = h1.w;
+  }
+}
+
 // 32 accumulator columns of one TMEM lane (= one output pixel) per step: one TMEM load, the residual
 // row segment fetched as four 16-byte loads issued before the TMEM wait, 32 FMAs + activations, four
 // 16-byte stores.  Used whenever a warp's column range is a multiple of 32.
-template <int ACT, bool RES>
+template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
 __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                  const float* __restrict__ sc, const float* __restrict__ sf,
                                                  const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
-                                                 bool valid) {
+                                                 bool valid, int dbg = 0, const PP& pp = PP(), int cb = 0) {
 #pragma unroll 1
   for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
     uint32_t r[32];
     tmem_ld_32x32(t_addr + c0, r);
     const int n0 = n_base + c0;
     uint4 rv[4];
+    if (dbg & 16) { tmem_ld_wait(); continue; }
 #pragma unroll
     for (int i = 0; i < 4; ++i) rv[i] = make_uint4(0, 0, 0, 0);
     if (RES && valid) {
@@ -109,10 +130,8 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
 #pragma unroll
       for (int v8 = 0; v8 < 4; ++v8) {
         if (n0 + v8 * 8 >= out_c) break;
-        const float4 s0 = reinterpret_cast<const float4*>(sc + c0)[2 * v8], s1 = reinterpret_cast<const float4*>(sc + c0)[2 * v8 + 1];
-        const float4 h0 = reinterpret_cast<const float4*>(sf + c0)[2 * v8], h1 = reinterpret_cast<const float4*>(sf + c0)[2 * v8 + 1];
-        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-        const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        float sv[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, hv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (!(dbg & 1)) load_affine8<CB>(pp, cb + c0 + v8 * 8, sc, sf, c0 + v8 * 8, sv, hv);
         const __half2* rh = reinterpret_cast<const __half2*>(&rv[v8]);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -127,9 +146,9 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
             a0 = t.x;
             a1 = t.y;
           }
-          oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+          oh[e2] = (dbg & 8) ? __floats2half2_rn(a0, a1) : __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
         }
-        *reinterpret_cast<uint4*>(yrow + n0 + v8 * 8) = o;
+        if (!(dbg & 2) || o.x == 0x12345678u) *reinterpret_cast<uint4*>(yrow + n0 + v8 * 8) = o;
       }
     }
   }
@@ -190,11 +209,11 @@ __device__ __forceinline__ void epi_fused_cols(uint32_t t_addr, int col_lo, int 
 // of a step pass through a 2 KB per-warp staging tile in shared memory (16-byte chunks XOR-swizzled so
 // that both directions are conflict free) and leave as 8 rows x 64 contiguous bytes per instruction;
 // the residual arrives the same way.  Lane t serves row 8j + t/4, chunk t%4 on the global side.
-template <int ACT, bool RES>
+template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
 __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                    const float* __restrict__ sc, const float* __restrict__ sf,
                                                    const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
-                                                   bool valid, uint8_t* st, int lane) {
+                                                   bool valid, uint8_t* st, int lane, int dbg = 0, const PP& pp = PP(), int cb = 0) {
   const int gr = lane >> 2, gc = lane & 3;
   const int own = lane * 64, swz = (lane >> 1) & 3;
   // row pointers and validity of the four rows this lane serves on the global side
@@ -215,6 +234,7 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
     const int n0 = n_base + c0;
     const bool cok = n0 + gc * 8 < out_c;
     uint4 rv[4];
+    if (dbg & 16) { tmem_ld_wait(); continue; }
     if (RES) {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
@@ -235,10 +255,8 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
     }
 #pragma unroll
     for (int v8 = 0; v8 < 4; ++v8) {
-      const float4 s0 = reinterpret_cast<const float4*>(sc + c0)[2 * v8], s1 = reinterpret_cast<const float4*>(sc + c0)[2 * v8 + 1];
-      const float4 h0 = reinterpret_cast<const float4*>(sf + c0)[2 * v8], h1 = reinterpret_cast<const float4*>(sf + c0)[2 * v8 + 1];
-      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-      const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+      float sv[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, hv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (!(dbg & 1)) load_affine8<CB>(pp, cb + c0 + v8 * 8, sc, sf, c0 + v8 * 8, sv, hv);
       const __half2* rh = reinterpret_cast<const __half2*>(&rown[v8]);
       uint4 o;
       __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -253,10 +271,11 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
           a0 = t.x;
           a1 = t.y;
         }
-        oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+        oh[e2] = (dbg & 8) ? __floats2half2_rn(a0, a1) : __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
       }
-      *reinterpret_cast<uint4*>(st + own + ((v8 ^ swz) << 4)) = o;
+      if (!(dbg & 2) || o.x == 0x12345678u) *reinterpret_cast<uint4*>(st + own + ((v8 ^ swz) << 4)) = o;
     }
+    if (dbg & 2) continue;
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -575,9 +594,17 @@ struct PconvParams {
   int* gerr;
   const uint32_t* tab;     // K schedule tables (see PconvTab)
   int tab_words;
+  int dbg;                 // tuning builds: epilogue parts to leave out (bit flags); 0 otherwise
   int direct_store;        // epilogue stores straight from the row-owning lanes instead of through the staging tile
   long long* ts;           // tuning builds: timeline of CTA 0 (8 stamps per tile, first 16 tiles); null otherwise
+  // Per-column scale/shift of layers with at most kPconvConstCols GEMM columns, carried in the kernel's parameter
+  // block: the epilogue then takes them from the constant bank (uniform loads on the scalar path) and issues no
+  // shared-memory load for them -- the shared-memory pipe is what the MMA's operand reads compete for.
+  int use_const;
+  float cscale[512];
+  float cshift[512];
 };
+constexpr int kPconvConstCols = 512;
 
 // A operand descriptors here start on any 128-byte row of a 1024-byte swizzle atom, not only on its
 // first.  That needs nothing extra in the descriptor: TMA writes and the MMA reads the 128-byte
@@ -618,11 +645,13 @@ __device__ __forceinline__ void pconv_item(const PconvParams& p, int item, int& 
 // Per-tile clock64 stamps of CTA 0 (patch issue / patch ready / MMAs issued / accumulator ready / epilogue
 // done) exist only in a tuning build (-DAIG_TUNING); the shipped kernel carries none of it.
 #ifdef AIG_TUNING
+#define AIG_DBG p.dbg
 #define AIG_STAMP(cond, idx)                      \
   do {                                            \
     if (p.ts && (cond)) p.ts[idx] = clock64();    \
   } while (0)
 #else
+#define AIG_DBG 0
 #define AIG_STAMP(cond, idx) \
   do {                       \
   } while (0)
@@ -640,7 +669,7 @@ __host__ __device__ constexpr int pconv_threads(int ew) { return (kPconvProducer
 template <int NT, int MS, bool WRES, int EW>
 __global__ void __launch_bounds__(pconv_threads(EW), 1)
 pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapAT, const __grid_constant__ CUtensorMap tmapB,
-             const PconvParams p) {
+             const __grid_constant__ PconvParams p) {
   constexpr int kM = MS * kTileM;
   constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
   constexpr int kPconvThreads = pconv_threads(EW);
@@ -666,10 +695,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint32_t* s_tab = s_tmem + 4;
   uint8_t* s_stage = sm + tail + 7168 + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;  // per-warp staging tile of the epilogue warps
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (the shuffle tells the compiler that the warp index is the same in all lanes, so per-role branches are uniform)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   griddep_launch_dependents();  // the next launch may set itself up and prefetch its weights under this one
   for (int i = threadIdx.x; i < p.tab_words; i += kPconvThreads) s_tab[i] = p.tab[i];
-  const bool staged = p.n_tiles * NT <= 512;  // else the epilogue reads scale/shift from global memory
+  const bool staged = !p.use_const && p.n_tiles * NT <= 512;  // else the epilogue reads scale/shift from global memory
   if (staged) {
     for (int i = threadIdx.x; i < p.n_tiles * NT; i += kPconvThreads) {
       s_scale[i] = p.scale[i];
@@ -724,9 +754,10 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
         const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
-        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 0);
+        AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 0);
         for (int u = 0; u < units && ok; ++u) {
           const int g = p.groups == 1 ? 0 : u % p.groups;
+          if (AIG_DBG & 64) continue;
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
           mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
@@ -745,7 +776,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           }
           if (++buf == p.patch_bufs) { buf = 0; ph ^= 1u; }
         }
-        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 1);
+        AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 1);
       }
     }
   } else if (warp == kWeightWarp) {
@@ -767,20 +798,23 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             const uint32_t* gs = s_tab + (sparse ? 17 : 0);
             const uint32_t* ent = s_tab + kTabHead;
             for (uint32_t e = gs[0]; e < gs[p.groups]; ++e) {
+              if (AIG_DBG & 128) continue;
               if (!mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)) { ok = false; break; }
               mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
               tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
           }
-          AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 2);
+          AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 2);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // all 32 lanes run the loop with identical values; one elected lane issues the MMAs and commits
+    {
       constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
+      const bool leader = elect_one();
       bool ok = true;
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
       int it = 0, cnt = 0, stage = 0, buf = 0;
@@ -804,19 +838,20 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           for (int g = 0; g < p.groups && ok; ++g) {
             // the patch unit of this group: a new one per (N tile, group), or the M tile's only one
             const bool fresh = p.groups > 1 || n_tile == n_lo;
-            if (fresh) {
+            if (fresh && !(AIG_DBG & 64)) {
               if (!mbar_wait_bounded(bar_pfull + 8 * buf, pph, s_abort, p.gerr, 502)) { ok = false; break; }
-              AIG_STAMP(blockIdx.x == 0 && it < 16 && n_tile == n_lo && g == 0, it * 8 + 3);
+              AIG_STAMP(blockIdx.x == 0 && leader && it < 12 && n_tile == n_lo && g == 0, it * 8 + 3);
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
             const uint32_t e1 = gs[g + 1];
             for (uint32_t e = gs[g]; e < e1; ++e) {
+              AIG_STAMP(blockIdx.x == 0 && leader && it == 2 && n_tile == n_lo && e - gs[0] < 32, 96 + (e - gs[0]));
               const uint32_t en = ent[e];
               uint32_t b0;
               if (WRES) {
                 b0 = sW + (en >> 16) * kWBlock;
               } else {
-                if (!mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
+                if (!(AIG_DBG & 128) && !mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
                 b0 = sW + stage * kWBlock;
               }
               const uint32_t a_lo = umma_desc_lo(patch + (en & 0xFFFFu) * 128u), b_lo = umma_desc_lo(b0);
@@ -824,24 +859,24 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               for (int sub = 0; sub < MS; ++sub) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                  umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
+                  if (leader) umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
                                  b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
               }
               first = 1u;
               if (!WRES) {
-                umma_commit(bar_wempty + 8 * stage);
+                if (leader) umma_commit(bar_wempty + 8 * stage);
                 if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
               }
             }
             // the unit may be overwritten once these MMAs have read it
             if (ok && (p.groups > 1 || n_tile == n_hi - 1)) {
-              umma_commit(bar_pempty + 8 * buf);
+              if (leader) umma_commit(bar_pempty + 8 * buf);
               if (++buf == p.patch_bufs) { buf = 0; pph ^= 1u; }
             }
           }
-          if (ok) umma_commit(bar_tfull + 8 * acc);
+          if (ok && leader) umma_commit(bar_tfull + 8 * acc);
         }
-        AIG_STAMP(blockIdx.x == 0 && it < 16, it * 8 + 4);
+        AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 4);
       }
     }
   } else if (warp >= kPconvProducerWarps) {
@@ -915,7 +950,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
         tc_fence_after();
-        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 5);
+        AIG_STAMP(blockIdx.x == 0 && cnt < 12 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 5);
         Pos a = pos0;
 #pragma unroll 1
         for (int sub = 0; sub < MS; ++sub) {
@@ -930,14 +965,20 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             opix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
           }
           __half* yrow = sg.y + opix * sg.channels;
-          const __half* rrow = sg.residual ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
+          const __half* rrow = (sg.residual && !(AIG_DBG & 4)) ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
-  if (p.direct_store) {                                                                                                        \
-    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);  \
-    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid);      \
-  } else if (rrow) epi_fused_cols32_t<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane);  \
-  else epi_fused_cols32_t<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane)
+  if (p.use_const) {                                                                                                           \
+    if (p.direct_store) {                                                                                                      \
+      if (rrow) epi_fused_cols32<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb);  \
+      else epi_fused_cols32<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb);      \
+    } else if (rrow) epi_fused_cols32_t<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb);  \
+    else epi_fused_cols32_t<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb);             \
+  } else if (p.direct_store) {                                                                                                 \
+    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG);  \
+    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG);      \
+  } else if (rrow) epi_fused_cols32_t<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG);  \
+  else epi_fused_cols32_t<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG)
           switch (sg.act) {
             case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
             case AIG_ACT_SWISH: AIG_EPI(AIG_ACT_SWISH); break;
@@ -948,7 +989,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         }
         tc_fence_before();
         __syncwarp();
-        AIG_STAMP(blockIdx.x == 0 && cnt < 16 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 6);
+        AIG_STAMP(blockIdx.x == 0 && cnt < 12 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 6);
         if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
       }
       pos0 = pos_add(pos0, d_item);
@@ -1238,6 +1279,8 @@ int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
   return encode_B(pl);
 }
 
+int pconv_refresh_affine(aig_conv_plan* pl);
+
 int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const float* b, const float* m, const float* v,
                float eps) {
   aig_ctx* ctx = pl->ctx;
@@ -1247,9 +1290,30 @@ int set_affine(aig_conv_plan* pl, const aig_half* bias, const float* g, const fl
                                                                         pl->d.out_c, pl->Kpad);
   AIG_LAUNCH_OK(ctx);
   pl->weights_set = true;
-  return AIG_OK;
+  return pconv_refresh_affine(pl);
 }
 
+
+// Copies the folded scale/shift of a patch-resident plan into its kernel parameter block (see PconvParams::cscale).
+// Runs at parameter-load time only: one small device-to-host copy and a stream synchronisation.
+int pconv_refresh_affine(aig_conv_plan* pl) {
+  if (!pl->use_pconv) return AIG_OK;
+  aig_ctx* ctx = pl->ctx;
+  PconvParams& q = pl->pp;
+  const int cols = pl->Kpad;
+  q.use_const = 0;
+  // measured on the encoder's layers: 2-4 % faster on the stride-1 layers (residual epilogue), slower on the fused
+  // down-sampling launches (two output segments), which therefore keep the copy staged in shared memory
+  if (pl->is_down || cols > kPconvConstCols) return AIG_OK;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_NOCONST")) if (atoi(e)) return AIG_OK;
+#endif
+  AIG_CUDA_OK(ctx, cudaMemcpyAsync(q.cscale, pl->scale, cols * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  AIG_CUDA_OK(ctx, cudaMemcpyAsync(q.cshift, pl->shift, cols * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  AIG_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  q.use_const = 1;
+  return AIG_OK;
+}
 
 // ---- patch-resident path: host side ------------------------------------------------------
 // Shared memory behind the patches and weights: scale/shift, barriers and K schedule tables, then one 2 KB staging
@@ -1460,6 +1524,10 @@ int pconv_build_tables(aig_ctx* ctx, aig_conv_plan* pl) {
   AIG_CUDA_OK(ctx, cudaMemcpy(pl->pc_tab, tab.data(), tab.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
   q.tab = pl->pc_tab;
   q.tab_words = (int)tab.size();
+  q.dbg = 0;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_DBG")) q.dbg = atoi(e);
+#endif
   return AIG_OK;
 }
 
@@ -1722,7 +1790,7 @@ int aig_fc_plan_add_bias(aig_conv_plan* pl, const aig_half* bias2) {
   AIG_REQUIRE(ctx, bias2 != nullptr && pl->weights_set, "fc add_bias: set the weights first");
   add_bias_kernel<<<ceil_div(pl->d.out_c, 128), 128, 0, ctx->stream>>>(pl->shift, (const __half*)bias2, pl->d.out_c);
   AIG_LAUNCH_OK(ctx);
-  return AIG_OK;
+  return pconv_refresh_affine(pl);
 }
 
 int aig_fc_plan_set_weights_out_in(aig_conv_plan* pl, const aig_half* w_out_in, const aig_half* bias) {
@@ -1864,7 +1932,7 @@ int aig_resdown_plan_set_weights(aig_conv_plan* pl, const aig_half* w_main, cons
   fold_affine_kernel<<<ceil_div(K, 128), 128, 0, ctx->stream>>>(pl->scale + K, pl->shift + K, (const __half*)b_short, nullptr, nullptr, nullptr, nullptr, 0.f, K, K);
   AIG_LAUNCH_OK(ctx);
   pl->weights_set = true;
-  return AIG_OK;
+  return pconv_refresh_affine(pl);
 }
 
 int aig_resdown_forward(aig_conv_plan* pl, const aig_half* x_s2d, aig_half* y_main, aig_half* y_short) {
