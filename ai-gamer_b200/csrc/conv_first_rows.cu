@@ -121,7 +121,7 @@ conv_first_rows_kernel(const __grid_constant__ CUtensorMap tmapY, const __grid_c
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 24);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
   griddep_launch_dependents();  // the next layer's launch may set itself up under this one
 
   // zero everything the MMAs may read (ring, zero row) and the output staging buffers (their border slots stay zero)
@@ -155,8 +155,10 @@ conv_first_rows_kernel(const __grid_constant__ CUtensorMap tmapY, const __grid_c
 
   if (warp == 0) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
       constexpr uint32_t idesc = umma_idesc_f16(128, kN);
+      const bool leader = elect_one();
       bool ok = true;
       int y = t_begin % p.Ho;
       for (int i = 0; i < t_end - t_begin && ok; ++i) {
@@ -173,11 +175,13 @@ conv_first_rows_kernel(const __grid_constant__ CUtensorMap tmapY, const __grid_c
           for (int h = 0; h < 2; ++h) {
             const uint64_t adesc = desc_noswizzle(a_row + 32u * h, 16u, 128u);
             const uint64_t bdesc = desc_noswizzle(sB + (uint32_t)((r * 2 + h) * 2 * kN * 16), (uint32_t)(kN * 16), 128u);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (r | h) != 0 ? 1u : 0u);
+            if (leader) umma_f16_ss(d_tmem, adesc, bdesc, idesc, (r | h) != 0 ? 1u : 0u);
           }
         }
-        umma_commit(bar_tfull + 8 * acc);
-        umma_commit(bar_done + 8 * (i & 7));
+        if (leader) {
+          umma_commit(bar_tfull + 8 * acc);
+          umma_commit(bar_done + 8 * (i & 7));
+        }
         if (++y == p.Ho) y = 0;
       }
     }

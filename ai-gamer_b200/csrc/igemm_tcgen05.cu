@@ -374,7 +374,7 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
 
   if (p.n_tiles == 1) {
     for (int i = threadIdx.x; i < NT; i += kNumThreads) {
@@ -409,7 +409,9 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -432,21 +434,25 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const int fd = tap / p.taps_hw, rem = tap - fd * p.taps_hw;
           const int fr = rem / p.kw, fs = rem - fr * p.kw;
           if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, s_abort, p.gerr, 101)) { ok = false; break; }
-          mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
-          // the weight block first: every sub-tile's MMAs need it
-          tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
+          if (leader) {
+            mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
+            // the weight block first: every sub-tile's MMAs need it
+            tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
+          }
           const uint32_t a_dst = sA + stage * Cfg::kABytes;
           for (int s = 0; s < nseg; ++s)
-            tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
-                        seg_z[s] + fd, seg_n[s]);
+            if (leader)
+              tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
+                          seg_z[s] + fd, seg_n[s]);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -466,13 +472,13 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           for (int sub = 0; sub < MS; ++sub) {
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k)
-              umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * Cfg::kSubBytes + k * 32) >> 4),
+              if (leader) umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * Cfg::kSubBytes + k * 32) >> 4),
                              b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(BK * 2), idesc, k == 0 ? first : 1u);
           }
-          umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
+          if (leader) umma_commit(bar_empty + 8 * stage);  // frees the smem stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(bar_tfull + 8 * acc);
+        if (ok && leader) umma_commit(bar_tfull + 8 * acc);
       }
     }
   } else {
@@ -741,7 +747,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     // ------------------------------------------------------------------ patch producer
     // one unit = the patch rows of one channel-block group; with a single group the unit serves all N
     // tiles of the M tile, otherwise the groups are streamed again for every N tile
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       int it = 0, buf = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -754,37 +761,40 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const long long q0 = (long long)m_tile * kM;
         const int vr0 = (int)(q0 / p.P);
         const int n0 = vr0 / p.RP, yy0 = vr0 - n0 * p.RP;
-        AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 0);
+        AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 0);
         for (int u = 0; u < units && ok; ++u) {
           const int g = p.groups == 1 ? 0 : u % p.groups;
           if (AIG_DBG & 64) continue;
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
-          mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
+          if (leader) mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
           if (p.tall_ok && yy0 + p.patch_vrows - 1 < p.RP + p.pad) {
             // the patch ends inside image n0 or in the padding rows below it: one box of patch_vrows rows per channel
             // block (rows past the image are zero-filled, which is what the shared padding rows hold)
             for (int l = 0; l < p.G; ++l)
-              tma_load_5d(dst0 + l * p.region_bytes, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy0 - p.pad, 0, n0);
+              if (leader) tma_load_5d(dst0 + l * p.region_bytes, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy0 - p.pad, 0, n0);
           } else {
             int n = n0, yy = yy0;
             for (int r = 0; r < p.patch_vrows; ++r) {
               for (int l = 0; l < p.G; ++l)
-                tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
+                if (leader) tma_load_5d(dst0 + l * p.region_bytes + r * p.P * 128, &tmapA, bar_pfull + 8 * buf, (g * p.G + l) * 64, -p.pad, yy - p.pad, 0, n);
               if (++yy == p.RP) { yy = 0; ++n; }
             }
           }
           if (++buf == p.patch_bufs) { buf = 0; ph ^= 1u; }
         }
-        AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 1);
+        AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 1);
       }
     }
   } else if (warp == kWeightWarp) {
     // ------------------------------------------------------------------ weight producer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       if (WRES) {
-        mbar_expect_tx(bar_wfull, (uint32_t)(dense_kb * kWBlock));
-        for (int kb = 0; kb < dense_kb; ++kb) tma_load_2d(sW + kb * kWBlock, &tmapB, bar_wfull, kb * 64, 0);
+        if (leader) {
+          mbar_expect_tx(bar_wfull, (uint32_t)(dense_kb * kWBlock));
+          for (int kb = 0; kb < dense_kb; ++kb) tma_load_2d(sW + kb * kWBlock, &tmapB, bar_wfull, kb * 64, 0);
+        }
       } else {
         bool ok = true;
         int stage = 0, it = 0;
@@ -800,12 +810,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             for (uint32_t e = gs[0]; e < gs[p.groups]; ++e) {
               if (AIG_DBG & 128) continue;
               if (!mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)) { ok = false; break; }
-              mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
-              tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
+              if (leader) {
+                mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
+                tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
+              }
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
           }
-          AIG_STAMP(blockIdx.x == 0 && it < 12, it * 8 + 2);
+          AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 2);
         }
       }
     }

@@ -93,7 +93,7 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tmapR, const __grid_co
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
   const int group = blockIdx.x / p.NC, cta = blockIdx.x % p.NC;
   const int row0 = group * kRows;
   const int unit0 = cta * U;
@@ -153,8 +153,10 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tmapR, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
       constexpr uint32_t idesc = umma_idesc_f16(kRows, NCOL);
+      const bool leader = elect_one();
       bool ok = mbar_wait_bounded(bar_r, 0, s_abort, p.gerr, 402);
       for (int t = 0; t < p.T && ok; ++t) {
         const uint32_t ph = (uint32_t)t & 1u;
@@ -166,10 +168,10 @@ lstm_recurrent_kernel(const __grid_constant__ CUtensorMap tmapR, const __grid_co
           for (int k = 0; k < kKB / 16; ++k) {
             const uint64_t adesc = umma_smem_desc(sA + kb * kRows * 128 + k * 32, 128);
             const uint64_t bdesc = umma_smem_desc(sR + kb * NCOL * 128 + k * 32, 128);
-            umma_f16_ss(tmem_base, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (leader) umma_f16_ss(tmem_base, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
         }
-        if (ok) umma_commit(bar_tfull);
+        if (ok && leader) umma_commit(bar_tfull);
       }
     }
   } else {

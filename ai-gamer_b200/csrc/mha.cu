@@ -82,7 +82,7 @@ attention_tile_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                  bar_o = bar_load + 32, bar_free = bar_load + 40;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
 
   if (threadIdx.x == 0) {
     mbar_init(bar_load, 1);
@@ -121,9 +121,11 @@ attention_tile_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
       constexpr uint32_t idesc_s = umma_idesc_f16(kQRows, NK);
       constexpr uint32_t idesc_o = umma_idesc_f16(kQRows, kD);
+      const bool leader = elect_one();
       int it = 0;
       for (int item = blockIdx.x; item < items; item += gridDim.x, ++it) {
         const uint32_t ph = (uint32_t)it & 1u;
@@ -131,18 +133,18 @@ attention_tile_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_f16_ss(tmem_base, umma_smem_desc(smem_u32(qT) + k * 32, 128), umma_smem_desc(smem_u32(kT) + k * 32, 128), idesc_s,
+          if (leader) umma_f16_ss(tmem_base, umma_smem_desc(smem_u32(qT) + k * 32, 128), umma_smem_desc(smem_u32(kT) + k * 32, 128), idesc_s,
                       k != 0 ? 1u : 0u);
-        umma_commit(bar_s);
+        if (leader) umma_commit(bar_s);
         if (!mbar_wait_bounded(bar_p, ph, s_abort, p.gerr, 503)) break;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < kKB; ++kb)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tmem_base + NK, umma_smem_desc(smem_u32(pT) + kb * kQRows * 128 + k * 32, 128),
+            if (leader) umma_f16_ss(tmem_base + NK, umma_smem_desc(smem_u32(pT) + kb * kQRows * 128 + k * 32, 128),
                         umma_smem_desc(smem_u32(vtT) + kb * 64 * 128 + k * 32, 128), idesc_o, (kb | k) != 0 ? 1u : 0u);
-        umma_commit(bar_o);
+        if (leader) umma_commit(bar_o);
       }
     }
   } else {
