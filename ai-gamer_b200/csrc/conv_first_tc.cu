@@ -50,7 +50,7 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
   const uint32_t bar_afull = smem_u32(bars), bar_aempty = bar_afull + 16, bar_tfull = bar_afull + 32, bar_tempty = bar_afull + 48;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
   const ConvFirstGeom& g = p.g;
 
   // one-time staging: zero both A stages (the K padding is never written again), weights, scale/shift
@@ -142,8 +142,10 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
       const uint32_t idesc = umma_idesc_f16(kRows, p.NT);
+      const bool leader = elect_one();
       int it = 0;
       for (int tile = blockIdx.x; tile < p.tiles; tile += gridDim.x, ++it) {
         const int st = it & 1;
@@ -155,11 +157,13 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
 #pragma unroll
         for (int i = 0; i < KSTEPS; ++i) {
           const int kb = i >> 2, k = i & 3;
-          umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
+          if (leader) umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
                       umma_smem_desc(b0 + kb * (p.NT * 128) + k * 32, 128), idesc, i != 0 ? 1u : 0u);
         }
-        umma_commit(bar_aempty + 8 * st);
-        umma_commit(bar_tfull + 8 * st);
+        if (leader) {
+          umma_commit(bar_aempty + 8 * st);
+          umma_commit(bar_tfull + 8 * st);
+        }
       }
     }
   } else {
@@ -280,7 +284,7 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
   griddep_launch_dependents();  // the first residual-block launch may set itself up under this kernel
   uint2* s_patch = reinterpret_cast<uint2*>(bars + 16);
   uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_patch + kPatchMax);  // 4 x 2 KB, one tile per epilogue warp (16-byte aligned)
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;  // (uniform for the compiler)
   const ConvFirstGeom& g = p.g;
   const int blocks_x = (g.Wo + kBW - 1) / kBW, blocks_y = (g.Ho + kBH - 1) / kBH;
   const int tiles = g.batch * blocks_y * blocks_x;
@@ -391,8 +395,10 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
     }
   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (all lanes run the loop with identical values, one elected lane issues: see elect_one)
+    {
       const uint32_t idesc = umma_idesc_f16(kRows, p.NT);
+      const bool leader = elect_one();
       int it = 0;
       for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
         const int st = it & 1;
@@ -404,11 +410,13 @@ conv_first_patch_kernel(const uint32_t* __restrict__ xin, __half* __restrict__ y
 #pragma unroll
         for (int i = 0; i < KSTEPS; ++i) {
           const int kb = i >> 2, k = i & 3;
-          umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
+          if (leader) umma_f16_ss(tmem_base + (uint32_t)(st * p.NT), umma_smem_desc(a0 + kb * (kRows * 128) + k * 32, 128),
                       umma_smem_desc(b0 + kb * (p.NT * 128) + k * 32, 128), idesc, i != 0 ? 1u : 0u);
         }
-        umma_commit(bar_aempty + 8 * st);
-        umma_commit(bar_tfull + 8 * st);
+        if (leader) {
+          umma_commit(bar_aempty + 8 * st);
+          umma_commit(bar_tfull + 8 * st);
+        }
       }
     }
   } else {

@@ -585,6 +585,11 @@ struct PconvParams {
   int m_tiles, n_tiles;
   int patch_vrows, region_bytes, patch_bytes;
   int tall_ok;             // the patch_vrows-row tensor map exists (one box per channel block where the patch stays in one image)
+  // Flat input: every position of the flattened padded space exists in memory as one row of C channels (the
+  // space-to-depth blocks of a fused down-sampling launch; a producer that writes the padding positions as zeros),
+  // so the patch of a tile is one contiguous run of rows starting pad*(P+1) rows before the tile: flat_boxes
+  // boxes of flat_box_rows rows per channel block instead of one box per virtual row and image.
+  int flat, flat_boxes, flat_box_rows;
   int w_stages;            // ring depth (streamed) or taps*cblocks (resident)
   int acc_bufs;            // TMEM accumulator buffers of MS*NT columns: as many as fit in 512 columns, at most 4
   int patch_bufs;          // patch buffers in shared memory: 2, or 1 when only one fits beside the weight ring
@@ -766,9 +771,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           const int g = p.groups == 1 ? 0 : u % p.groups;
           if (AIG_DBG & 64) continue;
           if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
-          if (leader) mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.patch_vrows * p.P * 128 * p.G));
+          if (leader) mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.flat ? p.region_bytes * p.G : p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
-          if (p.tall_ok && yy0 + p.patch_vrows - 1 < p.RP + p.pad) {
+          if (p.flat) {
+            const int row0 = (int)(q0 - (long long)p.pad * (p.P + 1));  // may be negative: rows before the tensor read as zeros
+            for (int l = 0; l < p.G; ++l)
+              for (int b = 0; b < p.flat_boxes; ++b)
+                if (leader) tma_load_2d(dst0 + l * p.region_bytes + b * p.flat_box_rows * 128, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, row0 + b * p.flat_box_rows);
+          } else if (p.tall_ok && yy0 + p.patch_vrows - 1 < p.RP + p.pad) {
             // the patch ends inside image n0 or in the padding rows below it: one box of patch_vrows rows per channel
             // block (rows past the image are zero-filled, which is what the shared padding rows hold)
             for (int l = 0; l < p.G; ++l)
@@ -836,7 +846,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         int m_tile, n_lo, n_hi;
         pconv_item(p, item, m_tile, n_lo, n_hi);
         const long long q0 = (long long)m_tile * kM;
-        const int off0 = (int)(q0 - (q0 / p.P) * p.P);
+        const int off0 = p.flat ? 0 : (int)(q0 - (q0 / p.P) * p.P);  // (a flat patch starts at the tile's first position)
         for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
           const int acc = cnt % p.acc_bufs;
           const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
@@ -1410,6 +1420,10 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   if (const char* f = getenv("AIG_PCONV_FORCE")) sscanf(f, "%d,%d,%d,%d", &f_nt, &f_ms, &f_pb, &f_g);
 #endif
   auto vrows_of = [&](int M) { return (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1; };
+  // rows of one channel block of a patch in shared memory
+  auto flat_boxes_of = [&](int M) { return (M + (kh - 1) * q.P + (q.kw - 1) + 255) / 256; };
+  auto flat_box_rows_of = [&](int M) { return (M + (kh - 1) * q.P + (q.kw - 1) + flat_boxes_of(M) - 1) / flat_boxes_of(M); };
+  auto region_rows_of = [&](int M) { return q.flat ? flat_boxes_of(M) * flat_box_rows_of(M) : vrows_of(M) * q.P; };
   auto take = [&](int o, int ms, int pb, int G, bool res, long long stages) {
     best = 1; best_opt = o; best_ms = ms; best_pb = pb; best_G = G; best_res = res; best_stages = (int)stages;
     best_acc = 512 / (ms * opts[o].NT);
@@ -1450,24 +1464,27 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
       if (f_pb && pb != f_pb) continue;
       if (f_g && f_g != q.cblocks) continue;
       for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
-        const long long patch = (long long)vrows_of(ms * kTileM) * q.P * 128 * q.cblocks;
+        const long long patch = (long long)region_rows_of(ms * kTileM) * 128 * q.cblocks;
         if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget) take(o, ms, pb, q.cblocks, true, dense_kb);
         if (ms == 1) break;
       }
     }
-    // streamed weights: two patch units of the largest channel-block group that leaves two stages
-    for (int pb = (f_pb > 2 ? f_pb : 2); pb >= 1 && best < 0; --pb) {
-      if (f_pb && pb != f_pb) continue;
-      for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
-        const long long region = (long long)vrows_of(ms * kTileM) * q.P * 128;
-        for (int G = q.cblocks; G >= 1 && best < 0; G /= 2) {
-          if (q.cblocks % G != 0) break;
-          if (f_g && G != f_g) continue;
-          long long stages = (kPconvBudget - pb * region * G) / wblock;
-          if (stages > 32) stages = 32;
-          if (stages >= 2) take(o, ms, pb, G, false, stages);
+    // streamed weights: two patch units of the largest channel-block group that leaves three stages (a ring of two
+    // cannot cover the refill round trip: 42 -> 36 us on the 256 -> 256 down-sampling launch), else two
+    for (int min_stages = 3; min_stages >= 2 && best < 0; --min_stages) {
+      for (int pb = (f_pb > 2 ? f_pb : 2); pb >= 1 && best < 0; --pb) {
+        if (f_pb && pb != f_pb) continue;
+        for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
+          const long long region = (long long)region_rows_of(ms * kTileM) * 128;
+          for (int G = q.cblocks; G >= 1 && best < 0; G /= 2) {
+            if (q.cblocks % G != 0) break;
+            if (f_g && G != f_g) continue;
+            long long stages = (kPconvBudget - pb * region * G) / wblock;
+            if (stages > 32) stages = 32;
+            if (stages >= min_stages) take(o, ms, pb, G, false, stages);
+          }
+          if (ms == 1) break;
         }
-        if (ms == 1) break;
       }
     }
   }
@@ -1477,7 +1494,9 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   q.n_tiles = opts[best_opt].n_tiles;
   q.sparse_tile0 = opts[best_opt].sparse_tile0;
   q.patch_vrows = (q.P - 1 + M - 1 + (kh - 1) * q.P + (q.kw - 1)) / q.P + 1;
-  q.region_bytes = q.patch_vrows * q.P * 128;
+  q.flat_boxes = flat_boxes_of(M);
+  q.flat_box_rows = flat_box_rows_of(M);
+  q.region_bytes = region_rows_of(M) * 128;
   q.G = best_G;
   q.groups = q.cblocks / best_G;
   q.patch_bytes = q.region_bytes * q.G;
@@ -1561,6 +1580,21 @@ int encode_P(aig_conv_plan* pl, const void* x) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t C = pl->pc_in_c, W = pl->pc_in_w, H = pl->pc_in_h, N = pl->d.batch;
+  if (pl->pp.flat) {
+    // rows = every position of the flattened space: N * RP * P (the space-to-depth blocks, or the padded layout)
+    cuuint64_t fdims[2] = {C, (cuuint64_t)N * pl->pp.RP * pl->pp.P};
+    cuuint64_t fstrides[1] = {C * 2};
+    cuuint32_t fbox[2] = {64u, (cuuint32_t)pl->pp.flat_box_rows};
+    cuuint32_t festr[2] = {1, 1};
+    CUresult fr = enc(&pl->tmapPT, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), fdims, fstrides, fbox, festr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (fr != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(flat patch) failed: %d", (int)fr);
+    pl->tmapP = pl->tmapPT;
+    pl->pp.tall_ok = 0;
+    pl->tmapP_ptr = x;
+    return AIG_OK;
+  }
   cuuint64_t dims[5] = {C, W, H, 1, N};
   cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, H * W * C * 2};
   cuuint32_t box[5] = {64u, (cuuint32_t)pl->pp.P, 1, 1, 1};
@@ -1887,6 +1921,7 @@ int aig_resdown_plan_create(aig_ctx* ctx, int batch, int in_c, int in_h, int in_
   PconvParams& q = pl->pp;
   q = PconvParams{};
   q.P = Wb; q.RP = Hb; q.pad = 0; q.kw = 2; q.taps = 4; q.cblocks = C4 / 64;
+  q.flat = 1;  // the space-to-depth buffer holds every block position, border blocks included
   q.Ho = pl->Ho; q.Wo = pl->Wo; q.batch = batch;
   q.n_split = out_c;
   q.sub_cblocks = in_c % 64 == 0 ? in_c / 64 : 1;
