@@ -103,6 +103,9 @@ SIGNATURES = {
     "aig_resdown_plan_create": [P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, PP],
     "aig_resdown_plan_set_weights": [P, P, P, P, P, P, P, c_float, P, P],
     "aig_resdown_forward": [P, P, P, P],
+    "aig_conv_padded_rows": [c_int, c_int, c_int, c_int],
+    "aig_resdown_plan_set_output_padded": [P, c_int],
+    "aig_conv_plan_set_input_padded": [P, c_int],
     "aig_actions_from_outputs": [P, P, c_int, c_int, c_int],
     # include/aig_compat.h: the reference's launcher names (no context argument; most return void)
     "InitCUDA": [],
@@ -228,7 +231,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_compat_context": c_void_p, "aig_recording_last_error": ctypes.c_char_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_compat_context": c_void_p, "aig_recording_last_error": ctypes.c_char_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_conv_padded_rows": ctypes.c_longlong, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
@@ -350,6 +353,11 @@ class _Plan:
         return d.value, h.value, w.value
 
 
+def padded_rows(batch, h, w, pad=1):
+    """Rows of a [batch][h][w][c] tensor in the padded position layout (aig_conv_padded_rows)."""
+    return int(lib().aig_conv_padded_rows(batch, h, w, pad))
+
+
 class ConvPlan(_Plan):
     """aig_conv_plan: tcgen05 implicit-GEMM convolution on channels-last tensors."""
     _destroy = "aig_conv_plan_destroy"
@@ -371,6 +379,11 @@ class ConvPlan(_Plan):
         self.check(lib().aig_conv_forward(self.handle, ptr(x), ptr(residual), ptr(y)))
         return y
 
+    def set_input_padded(self, enable=True):
+        """x and residual of forward() in the padded position layout (see padded_rows)."""
+        self.check(lib().aig_conv_plan_set_input_padded(self.handle, 1 if enable else 0))
+
+
 
 class ResDownPlan(_Plan):
     """aig_resdown_plan: main k4 s2 p1 conv (+BN+act) and k2 s2 p0 shortcut of a residual block as one launch
@@ -389,6 +402,10 @@ class ResDownPlan(_Plan):
 
     def forward(self, x_s2d, y_main, y_short):
         self.check(lib().aig_resdown_forward(self.handle, ptr(x_s2d), ptr(y_main), ptr(y_short)))
+
+    def set_output_padded(self, enable=True):
+        """y_main / y_short in the padded position layout (rows: padded_rows(batch, Ho, Wo, 1))."""
+        self.check(lib().aig_resdown_plan_set_output_padded(self.handle, 1 if enable else 0))
 
 
 class FcPlan(_Plan):

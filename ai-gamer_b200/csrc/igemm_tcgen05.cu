@@ -110,7 +110,9 @@ template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
 __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                  const float* __restrict__ sc, const float* __restrict__ sf,
                                                  const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
-                                                 bool valid, int dbg = 0, const PP& pp = PP(), int cb = 0) {
+                                                 bool valid, int dbg = 0, const PP& pp = PP(), int cb = 0, bool store_invalid = false) {
+  // (store_invalid: rows of padding positions are stored too, as zeros)
+  const uint32_t keep = valid ? 0xffffffffu : 0u;
 #pragma unroll 1
   for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
     uint32_t r[32];
@@ -126,7 +128,7 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
         if (n0 + 8 * i < out_c) rv[i] = __ldg(reinterpret_cast<const uint4*>(rrow + n0 + 8 * i));
     }
     tmem_ld_wait();
-    if (valid) {
+    if (valid || store_invalid) {
 #pragma unroll
       for (int v8 = 0; v8 < 4; ++v8) {
         if (n0 + v8 * 8 >= out_c) break;
@@ -148,6 +150,7 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
           }
           oh[e2] = (dbg & 8) ? __floats2half2_rn(a0, a1) : __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
         }
+        o.x &= keep; o.y &= keep; o.z &= keep; o.w &= keep;
         if (!(dbg & 2) || o.x == 0x12345678u) *reinterpret_cast<uint4*>(yrow + n0 + v8 * 8) = o;
       }
     }
@@ -213,19 +216,23 @@ template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
 __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                    const float* __restrict__ sc, const float* __restrict__ sf,
                                                    const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
-                                                   bool valid, uint8_t* st, int lane, int dbg = 0, const PP& pp = PP(), int cb = 0) {
+                                                   bool valid, uint8_t* st, int lane, int dbg = 0, const PP& pp = PP(), int cb = 0,
+                                                   bool store_invalid = false) {
+  // (store_invalid: rows of padding positions are stored too, as zeros)
+  const uint32_t keep = valid ? 0xffffffffu : 0u;
   const int gr = lane >> 2, gc = lane & 3;
   const int own = lane * 64, swz = (lane >> 1) & 3;
   // row pointers and validity of the four rows this lane serves on the global side
   __half* yp[4];
   const __half* rp[4];
-  bool vj[4];
+  bool vj[4], sj[4];  // the row is a real position (residual loads) / is stored
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int row = 8 * j + gr;
     yp[j] = reinterpret_cast<__half*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(yrow), row));
     rp[j] = RES ? reinterpret_cast<const __half*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(rrow), row)) : nullptr;
     vj[j] = __shfl_sync(0xffffffffu, valid ? 1 : 0, row) != 0;
+    sj[j] = vj[j] || store_invalid;
   }
 #pragma unroll 1
   for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
@@ -273,6 +280,7 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
         }
         oh[e2] = (dbg & 8) ? __floats2half2_rn(a0, a1) : __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
       }
+      o.x &= keep; o.y &= keep; o.z &= keep; o.w &= keep;
       if (!(dbg & 2) || o.x == 0x12345678u) *reinterpret_cast<uint4*>(st + own + ((v8 ^ swz) << 4)) = o;
     }
     if (dbg & 2) continue;
@@ -281,7 +289,7 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
     for (int j = 0; j < 4; ++j) {
       const int row = 8 * j + gr;
       const uint4 o = *reinterpret_cast<const uint4*>(st + row * 64 + ((gc ^ ((row >> 1) & 3)) << 4));
-      if (vj[j] && cok) *reinterpret_cast<uint4*>(yp[j] + n0 + gc * 8) = o;
+      if (sj[j] && cok) *reinterpret_cast<uint4*>(yp[j] + n0 + gc * 8) = o;
     }
     __syncwarp();
   }
@@ -577,6 +585,11 @@ struct OutSeg {
   int act;
   int s2d;                  // 1: store into the 2x2 space-to-depth layout read by the next stride-2 block
   int Hb, Wb;               // block extents of that layout
+  // Padded position layout: row q = (n * RP + yy) * P + vc of this launch's flattened space, padding positions
+  // included and written as zeros, so that a stride-1 consumer with the same P and RP loads its patches (and its
+  // residual rows) as contiguous runs of rows.
+  int padded;               // 1: y is written in that layout
+  int res_padded;           // 1: the residual is read in that layout
 };
 
 struct PconvParams {
@@ -963,7 +976,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               a = pos_add(a, d_sub);
               if (EW == 16 && MS > 1 && (sub & 1) != team) continue;
               if (n < p.batch && yy < p.Ho && vc < p.Wo) {
-                const __half* rr = sg.residual + (((size_t)n * p.Ho + yy) * p.Wo + vc) * sg.channels + (nb - sg.c0 + col_lo);
+                const size_t rpos = sg.res_padded ? ((size_t)n * p.RP + yy) * p.P + vc : ((size_t)n * p.Ho + yy) * p.Wo + vc;
+                const __half* rr = sg.residual + rpos * sg.channels + (nb - sg.c0 + col_lo);
                 for (int b = 0; b < NT; b += 128)  // NT/2 halfs = NT bytes per row segment
                   asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t*>(rr) + b));
               }
@@ -981,26 +995,31 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           if (EW == 16 && MS > 1 && (sub & 1) != team) continue;  // the other team's sub-tile
           const bool valid = n < p.batch && yy < p.Ho && vc < p.Wo;
           const size_t pix = ((size_t)n * p.Ho + yy) * p.Wo + vc;
+          const size_t qpos = ((size_t)n * p.RP + yy) * p.P + vc;  // this row's index in the flattened padded space
           size_t opix = pix;
           if (sg.s2d) {
             const int by = (yy + 1) >> 1, bx = (vc + 1) >> 1, sp = ((yy + 1) & 1) * 2 + ((vc + 1) & 1);
             opix = (((size_t)n * sg.Hb + by) * sg.Wb + bx) * 4 + sp;
+          } else if (sg.padded) {
+            opix = qpos;
           }
+          const bool sinv = sg.padded != 0;  // (the padded layout holds every position; its buffer is rounded up to whole tiles)
           __half* yrow = sg.y + opix * sg.channels;
-          const __half* rrow = (sg.residual && !(AIG_DBG & 4)) ? sg.residual + pix * sg.channels : nullptr;  // residual is plain channels-last
+          // residual: plain channels-last, or the padded position layout
+          const __half* rrow = (sg.residual && !(AIG_DBG & 4)) ? sg.residual + (sg.res_padded ? qpos : pix) * sg.channels : nullptr;
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
 #define AIG_EPI(ACT)                                                                                                          \
   if (p.use_const) {                                                                                                           \
     if (p.direct_store) {                                                                                                      \
-      if (rrow) epi_fused_cols32<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb);  \
-      else epi_fused_cols32<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb);      \
-    } else if (rrow) epi_fused_cols32_t<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb);  \
-    else epi_fused_cols32_t<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb);             \
+      if (rrow) epi_fused_cols32<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb, sinv);  \
+      else epi_fused_cols32<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb, sinv);      \
+    } else if (rrow) epi_fused_cols32_t<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb, sinv);  \
+    else epi_fused_cols32_t<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb, sinv);             \
   } else if (p.direct_store) {                                                                                                 \
-    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG);  \
-    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG);      \
-  } else if (rrow) epi_fused_cols32_t<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG);  \
-  else epi_fused_cols32_t<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG)
+    if (rrow) epi_fused_cols32<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, NoConstAffine(), 0, sinv);  \
+    else epi_fused_cols32<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, NoConstAffine(), 0, sinv);      \
+  } else if (rrow) epi_fused_cols32_t<ACT, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, NoConstAffine(), 0, sinv);  \
+  else epi_fused_cols32_t<ACT, false>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, NoConstAffine(), 0, sinv)
           switch (sg.act) {
             case AIG_ACT_RELU: AIG_EPI(AIG_ACT_RELU); break;
             case AIG_ACT_SWISH: AIG_EPI(AIG_ACT_SWISH); break;
@@ -1154,6 +1173,7 @@ struct aig_conv_plan {
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
   bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
   bool is_down = false;                        // fused down-sampling pair (main k4 s2 p1 + shortcut k2 s2 p0)
+  bool in_padded = false;                      // input and residual arrive in the padded position layout
 };
 
 namespace {
@@ -1635,6 +1655,7 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.P = d.in_w + d.pw;
   q.RP = d.in_h + d.ph;
   q.pad = d.ph;
+  q.flat = pl->in_padded ? 1 : 0;
   q.kw = d.kw;
   q.taps = d.kh * d.kw;
   q.cblocks = d.in_c / 64;
@@ -1651,6 +1672,8 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.seg[0].c0 = 0;
   q.seg[0].act = d.act;
   q.seg[0].s2d = 0;
+  q.seg[0].padded = 0;
+  q.seg[0].res_padded = pl->in_padded ? 1 : 0;
   q.seg[1] = q.seg[0];
   // N tilings: the natural tile width, and for wide layers also half of it (more sub-tiles per CTA tile
   // then share every weight block); Kpad is a multiple of both
@@ -1887,6 +1910,43 @@ int aig_conv_plan_set_output_s2d(aig_conv_plan* pl, int enable) {
   pl->pp.seg[0].s2d = enable ? 1 : 0;
   pl->pp.seg[0].Hb = s2d_extent(pl->Ho);
   pl->pp.seg[0].Wb = s2d_extent(pl->Wo);
+  return AIG_OK;
+}
+
+long long aig_conv_padded_rows(int batch, int h, int w, int pad) {
+  const long long rows = (long long)batch * (h + pad) * (w + pad);
+  return (rows + 1023) / 1024 * 1024;
+}
+
+int aig_conv_plan_set_input_padded(aig_conv_plan* pl, int enable) {
+  if (!pl) return AIG_ERR_INVALID;
+  aig_ctx* ctx = pl->ctx;
+  DeviceGuard g(ctx->device);
+  if (pl->in_padded == (enable != 0)) return AIG_OK;
+  if (enable && !(pl->use_pconv && !pl->is_down && pl->d.ph >= 1 && pl->d.ph == pl->d.pw))
+    return aig_fail(ctx, AIG_ERR_UNSUPPORTED, "padded input layout needs the patch-resident convolution path with equal padding >= 1");
+  if (!pl->use_pconv) return AIG_OK;
+  // the patch regions change size: choose the tile again, keeping the output layout already selected
+  const OutSeg keep = pl->pp.seg[0];
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(pl->pc_tab);
+  pl->pc_tab = nullptr;
+  cudaFree(pl->pp.ts);
+  pl->use_pconv = false;
+  pl->in_padded = enable != 0;
+  pl->tmapP_ptr = nullptr;
+  int rc = pconv_try_plain(ctx, pl);
+  if (rc == AIG_OK && !pl->use_pconv) rc = aig_fail(ctx, AIG_ERR_UNSUPPORTED, "padded input layout: no tile fits shared memory");
+  if (rc != AIG_OK) return rc;
+  pl->pp.seg[0].s2d = keep.s2d; pl->pp.seg[0].Hb = keep.Hb; pl->pp.seg[0].Wb = keep.Wb;
+  if (pl->weights_set) rc = pconv_refresh_affine(pl);
+  return rc;
+}
+
+int aig_resdown_plan_set_output_padded(aig_conv_plan* pl, int enable) {
+  if (!pl) return AIG_ERR_INVALID;
+  if (!pl->is_down || !pl->use_pconv) return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "padded output layout is an option of the fused down-sampling plan");
+  pl->pp.seg[0].padded = pl->pp.seg[1].padded = enable ? 1 : 0;
   return AIG_OK;
 }
 

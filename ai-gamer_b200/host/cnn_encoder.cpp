@@ -250,7 +250,13 @@ int aig_cnn_create(aig_ctx* ctx, const aig_cnn_config* cfg, aig_cnn** out) {
     aig_conv_desc e = d;
     e.in_c = co; e.in_h = oh; e.in_w = ow; e.kh = e.kw = 3; e.sh = e.sw = 1; e.ph = e.pw = 1;
     if ((rc = aig_conv_plan_create(ctx, &e, &b.c1)) != AIG_OK) return bail(rc);
-    const size_t n = (size_t)c.batch * oh * ow * co;
+    size_t n = (size_t)c.batch * oh * ow * co;
+    // fused down-sampling launch -> 3x3 convolution: the pair passes both tensors (conv1's input and residual) in the
+    // padded position layout when both plans take it, so that conv1 loads each patch as one contiguous run of rows
+    if (b.down && aig_resdown_plan_set_output_padded(b.down, 1) == AIG_OK) {
+      if (aig_conv_plan_set_input_padded(b.c1, 1) == AIG_OK) n = (size_t)aig_conv_padded_rows(c.batch, oh, ow, 1) * co;
+      else aig_resdown_plan_set_output_padded(b.down, 0);
+    }
     if (dev_alloc(m, &b.t, n) != AIG_OK || dev_alloc(m, &b.r, n) != AIG_OK) return bail(AIG_ERR_CUDA);
     m->blocks.push_back(b);
     m->bh.push_back(oh);

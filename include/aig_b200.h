@@ -269,6 +269,21 @@ int aig_resdown_plan_set_weights(aig_conv_plan* plan, const aig_half* w_main, co
                                  const float* bn_var, float bn_eps, const aig_half* w_short, const aig_half* b_short);
 int aig_resdown_forward(aig_conv_plan* plan, const aig_half* x_s2d, aig_half* y_main, aig_half* y_short);
 
+/* Padded position layout between a fused down-sampling launch and the stride-1 convolution that follows it
+ * (ResConvLayer.cpp:28-36: conv0 -> conv1, with the shortcut as conv1's residual).  A [batch][h][w][c] tensor is
+ * stored as [batch][h + pad][w + pad][c]: row q = (n * (h + pad) + y) * (w + pad) + x, the extra row and column of
+ * every image written as zeros.  One zero column is the right padding of its row and the left padding of the next,
+ * one zero row the bottom padding of its image and the top padding of the next, so a convolution with that
+ * padding finds every input position of a tile, padding included, in ONE contiguous run of rows (rows before the
+ * tensor read as zeros).  aig_conv_padded_rows gives the rows to allocate (rounded up to whole tiles).
+ *   aig_resdown_plan_set_output_padded: y_main and y_short of aig_resdown_forward are written in this layout
+ *     (pad = 1: the geometry of the 3x3 convolution that follows);
+ *   aig_conv_plan_set_input_padded: x AND residual of aig_conv_forward are read in this layout (pad = the plan's
+ *     padding); the output layout is unchanged.  Patch-resident plans only (AIG_ERR_UNSUPPORTED otherwise). */
+long long aig_conv_padded_rows(int batch, int h, int w, int pad);
+int aig_resdown_plan_set_output_padded(aig_conv_plan* plan, int enable);
+int aig_conv_plan_set_input_padded(aig_conv_plan* plan, int enable);
+
 /* ---------------------------------------------------------------------------------------------
  * LSTM.  Replaces LSTMLayer (LSTMLayer.cpp:4-40 constructor, :75-104 Forward: cudnnRNNForwardInference,
  * seq-major x [T][B][in] -> y [T][B][hidden], cell clip +-5, two bias vectors) and the cuDNN-8 variant

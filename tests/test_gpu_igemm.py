@@ -355,6 +355,74 @@ def test_conv_output_in_space_to_depth_layout(env):
 
 
 @gpu
+@pytest.mark.parametrize("B,C,H,W,K", [(2, 32, 24, 32, 64), (3, 64, 18, 32, 128), (4, 128, 18, 32, 256), (5, 256, 9, 16, 256), (37, 64, 10, 12, 128)])
+def test_padded_position_layout_between_down_sampling_and_conv1(env, B, C, H, W, K):
+    """The fused down-sampling launch writes both outputs in the padded position layout (every image with one extra
+    zero row and column) and the 3x3 convolution reads its input and its residual from it: the padding positions
+    hold zeros, the real positions hold exactly what the channels-last outputs hold, and the convolution's result
+    equals the one computed from the channels-last tensors bit for bit."""
+    U = env
+    import torch
+
+    c = U.ctx()
+    pk = U.pkg()
+    x = h(RNG.standard_normal((B, C, H, W)))
+    w0, b0 = PL.he_normal(RNG, (K, C, 4, 4)), h(RNG.uniform(-0.2, 0.2, K))
+    bn = PL.bn_params(RNG, K, trivial=False)
+    ws, bs = PL.he_normal(RNG, (K, C, 2, 2)), h(RNG.uniform(-0.2, 0.2, K))
+    w1, b1 = PL.he_normal(RNG, (K, K, 3, 3)), h(RNG.uniform(-0.2, 0.2, K))
+    bn1 = PL.bn_params(RNG, K, trivial=False)
+    down = pk.ResDownPlan(c, B, C, H, W, K, act=pk.ACT_SWISH)
+    _, Ho, Wo = down.out_dims()
+    keep = [U.dev(a) for a in (w0, b0, ws, bs, w1, b1)] + [U.dev(q) for q in bn] + [U.dev(q) for q in bn1]
+    down.set_weights(keep[0], keep[1], keep[6:10], keep[2], keep[3], eps=1e-6)
+    conv = pk.ConvPlan(c, B, K, Ho, Wo, K, 3, 1, 1, act=pk.ACT_SWISH)
+    conv.set_weights(keep[4], keep[5], bn=keep[10:14])
+    ds = torch.zeros(pk.lib().aig_s2d_elems(B, H, W, C), dtype=torch.float16, device="cuda")
+    c.call("aig_nhwc_to_s2d", U.p(U.dev(U.nhwc(x))), U.p(ds), B, H, W, C)
+    # channels-last link
+    n = B * Ho * Wo * K
+    m0, s0, y0 = (torch.zeros(n, dtype=torch.float16, device="cuda") for _ in range(3))
+    down.forward(ds, m0, s0)
+    conv.forward(m0, y0, residual=s0)
+    c.sync()
+    # padded link (buffers start as garbage: the launch must write every row itself)
+    rows = pk.padded_rows(B, Ho, Wo, 1)
+    assert rows % 1024 == 0 and rows >= B * (Ho + 1) * (Wo + 1)
+    m1 = torch.full((rows * K,), 7.0, dtype=torch.float16, device="cuda")
+    s1 = torch.full((rows * K,), -3.0, dtype=torch.float16, device="cuda")
+    y1 = torch.zeros(n, dtype=torch.float16, device="cuda")
+    down.set_output_padded(True)
+    conv.set_input_padded(True)
+    down.forward(ds, m1, s1)
+    conv.forward(m1, y1, residual=s1)
+    c.sync()
+    real = B * (Ho + 1) * (Wo + 1)
+    for got, want in ((m1, m0), (s1, s0)):
+        g = U.host(got).reshape(rows, K)
+        # (rows past the last image belong to the allocation only: the consumer's tensor map ends at `real`)
+        g = g[:real].reshape(B, Ho + 1, Wo + 1, K)
+        assert not g[:, Ho].any() and not g[:, :, Wo].any(), "padding positions must be zeros"
+        assert np.array_equal(g[:, :Ho, :Wo], U.host(want).reshape(B, Ho, Wo, K))
+    assert np.array_equal(U.host(y1), U.host(y0)), "conv1 over the padded layout differs from the channels-last result"
+    # and against the oracle
+    main = O.activate(O.batchnorm(O.conv2d(x, w0, b0, 2, 1), *bn), 2, 0.01)
+    short = O.conv2d(x, ws, bs, 2, 0)
+    want = O.activate(O.add(O.batchnorm(O.conv2d(main, w1, b1, 1, 1), *bn1), short), 2, 0.01)
+    assert U.scaled_err(U.nchw(U.host(y1).reshape(B, Ho, Wo, K)), want) < 8e-3
+    # switching back restores the channels-last link
+    down.set_output_padded(False)
+    conv.set_input_padded(False)
+    y2 = torch.zeros(n, dtype=torch.float16, device="cuda")
+    down.forward(ds, m0, s0)
+    conv.forward(m0, y2, residual=s0)
+    c.sync()
+    assert torch.equal(y2, y0)
+    down.close()
+    conv.close()
+
+
+@gpu
 def test_fused_downsampling_refuses_unsupported_channel_counts(env):
     """Channel counts the space-to-depth GEMM cannot tile are refused with a clear status (callers then
     use the two separate convolutions)."""
