@@ -60,7 +60,6 @@ __device__ __forceinline__ uint64_t desc_noswizzle(uint32_t saddr, uint32_t lbo_
   // descriptor version 1 at [46,48), layout type 0 = no swizzle at [61,64)
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) | ((uint64_t)1 << 46);
 }
-__device__ __forceinline__ void named_bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ void tma_store_5d(const void* desc, uint32_t src, int c0, int c1, int c2, int c3, int c4) {
   asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];" ::"l"(reinterpret_cast<uint64_t>(desc)),
                "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)

@@ -83,6 +83,43 @@ __device__ __forceinline__ float act_ct(float v, float slope) {
   return v;
 }
 
+// Residual rows delivered by TMA (residual in the padded position layout, where the rows of a sub-tile are 128
+// consecutive rows): every step's 128 rows x 32 channels land in the team's 8 KB tile (64-byte rows, 64-byte
+// swizzle); a lane reads its own row from there, and once the four warps of the team have read (named barrier) one
+// thread requests the tile of the following step, which lands while this step's values are computed and stored.
+struct ResTma {
+  uint32_t tile;        // shared-memory address of the team's tile (1024-byte aligned)
+  uint32_t bar;         // mbarrier the loads complete on
+  uint32_t* phase;      // steps taken so far (its low bit is the parity to wait for)
+  bool issuer;          // this thread requests the loads
+  int bar_id;           // named barrier of the team
+  const void* map;      // tensor map of the residual [rows][channels], box 32 x 128
+  int ch0, row0;        // channel of col_lo and first row of this sub-tile in the residual
+  int next_row0;        // first row of the sub-tile processed after this one (-1: none)
+  volatile int* abort_flag;
+  int* gerr;
+};
+struct NoResTma {};
+// Waits for the step's tile, returns this lane's 64 bytes, and requests the next tile.  `row` = row inside the sub-tile.
+__device__ __forceinline__ void res_tma_take(const ResTma& rt, int row, int c0, int col_lo, int col_hi, uint4 (&rown)[4]) {
+  mbar_wait_bounded(rt.bar, *rt.phase & 1u, rt.abort_flag, rt.gerr, 602);
+  ++*rt.phase;
+  const uint32_t src = rt.tile + (uint32_t)row * 64u, swz = (uint32_t)((row >> 1) & 3);
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rown[c].x), "=r"(rown[c].y), "=r"(rown[c].z), "=r"(rown[c].w)
+                 : "r"(src + (((uint32_t)c ^ swz) << 4)));
+  named_bar_sync(rt.bar_id, 128);  // the team has read this tile
+  if (rt.issuer) {
+    const bool more = c0 + 32 < col_hi;
+    const int nrow = more ? rt.row0 : rt.next_row0;
+    if (nrow >= 0) {
+      mbar_expect_tx(rt.bar, 128u * 64u);
+      tma_load_2d(rt.tile, rt.map, rt.bar, more ? rt.ch0 + (c0 + 32 - col_lo) : rt.ch0, nrow);
+    }
+  }
+}
+
 // Eight consecutive per-column scale/shift values: from arrays in the kernel's parameter block (constant bank;
 // CB) or through pointers to shared or global memory.
 struct NoConstAffine {};
@@ -106,11 +143,12 @@ __device__ __forceinline__ void load_affine8(const PP& pp, int cidx, const float
 // 32 accumulator columns of one TMEM lane (= one output pixel) per step: one TMEM load, the residual
 // row segment fetched as four 16-byte loads issued before the TMEM wait, 32 FMAs + activations, four
 // 16-byte stores.  Used whenever a warp's column range is a multiple of 32.
-template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
+template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine, bool RT = false, typename RTT = NoResTma>
 __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                  const float* __restrict__ sc, const float* __restrict__ sf,
                                                  const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
-                                                 bool valid, int dbg = 0, const PP& pp = PP(), int cb = 0, bool store_invalid = false) {
+                                                 bool valid, int dbg = 0, const PP& pp = PP(), int cb = 0, bool store_invalid = false,
+                                                 const RTT& rt = RTT(), int row = 0) {
   // (store_invalid: rows of padding positions are stored too, as zeros)
   const uint32_t keep = valid ? 0xffffffffu : 0u;
 #pragma unroll 1
@@ -122,7 +160,9 @@ __device__ __forceinline__ void epi_fused_cols32(uint32_t t_addr, int col_lo, in
     if (dbg & 16) { tmem_ld_wait(); continue; }
 #pragma unroll
     for (int i = 0; i < 4; ++i) rv[i] = make_uint4(0, 0, 0, 0);
-    if (RES && valid) {
+    if constexpr (RES && RT) {
+      res_tma_take(rt, row, c0, col_lo, col_hi, rv);
+    } else if (RES && valid) {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
         if (n0 + 8 * i < out_c) rv[i] = __ldg(reinterpret_cast<const uint4*>(rrow + n0 + 8 * i));
@@ -212,12 +252,12 @@ __device__ __forceinline__ void epi_fused_cols(uint32_t t_addr, int col_lo, int 
 // of a step pass through a 2 KB per-warp staging tile in shared memory (16-byte chunks XOR-swizzled so
 // that both directions are conflict free) and leave as 8 rows x 64 contiguous bytes per instruction;
 // the residual arrives the same way.  Lane t serves row 8j + t/4, chunk t%4 on the global side.
-template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine>
+template <int ACT, bool RES, bool CB = false, typename PP = NoConstAffine, bool RT = false, typename RTT = NoResTma>
 __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, int col_hi, int n_base, int out_c,
                                                    const float* __restrict__ sc, const float* __restrict__ sf,
                                                    const __half* __restrict__ rrow, __half* __restrict__ yrow, float slope,
                                                    bool valid, uint8_t* st, int lane, int dbg = 0, const PP& pp = PP(), int cb = 0,
-                                                   bool store_invalid = false) {
+                                                   bool store_invalid = false, const RTT& rt = RTT(), int row_in_sub = 0) {
   // (store_invalid: rows of padding positions are stored too, as zeros)
   const uint32_t keep = valid ? 0xffffffffu : 0u;
   const int gr = lane >> 2, gc = lane & 3;
@@ -242,14 +282,15 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
     const bool cok = n0 + gc * 8 < out_c;
     uint4 rv[4];
     if (dbg & 16) { tmem_ld_wait(); continue; }
-    if (RES) {
+    if (RES && !RT) {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         rv[j] = (vj[j] && cok) ? __ldg(reinterpret_cast<const uint4*>(rp[j] + n0 + gc * 8)) : make_uint4(0, 0, 0, 0);
     }
-    tmem_ld_wait();
     uint4 rown[4];
-    if (RES) {
+    if constexpr (RES && RT) res_tma_take(rt, row_in_sub, c0, col_lo, col_hi, rown);
+    tmem_ld_wait();
+    if (RES && !RT) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int row = 8 * j + gr;
@@ -292,6 +333,57 @@ __device__ __forceinline__ void epi_fused_cols32_t(uint32_t t_addr, int col_lo, 
       if (sj[j] && cok) *reinterpret_cast<uint4*>(yp[j] + n0 + gc * 8) = o;
     }
     __syncwarp();
+  }
+}
+
+// The same step for a destination in the padded position layout, stored by TMA.  The rows of a sub-tile are 128
+// consecutive rows of the destination there, so the four warps that share a column half (a team: one warp per TMEM
+// lane quarter) put their 32 rows x 64 bytes side by side into the team's 8 KB staging tile (64-byte rows, 16-byte
+// chunks in the 64-byte swizzle order) and one thread hands the 128 x 32 box to the TMA unit: no shared-memory
+// read-back and no global store instruction in the warps.  Padding positions are stored as zeros.  Two named
+// barriers per step order the hand-over: staging free (the issuing thread has waited for the last store to have
+// read it) -> rows written -> store issued.
+template <int ACT, bool CB = false, typename PP = NoConstAffine>
+__device__ __forceinline__ void epi_cols32_tma(uint32_t t_addr, int col_lo, int col_hi, int ch0, const float* __restrict__ sc,
+                                               const float* __restrict__ sf, float slope, bool valid, uint32_t st_team, int row,
+                                               bool issuer, int bar_id, const void* ymap, int y_row0, const PP& pp = PP(),
+                                               int cb = 0) {
+  const uint32_t keep = valid ? 0xffffffffu : 0u;
+  // 64-byte swizzle: chunk index ^= address bits [7,9); the staging tile is 1024-byte aligned
+  const uint32_t dst = st_team + (uint32_t)row * 64u, swz = (uint32_t)((row >> 1) & 3);
+#pragma unroll 1
+  for (int c0 = col_lo; c0 < col_hi; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld_32x32(t_addr + c0, r);
+    tmem_ld_wait();
+    uint4 o[4];
+#pragma unroll
+    for (int v8 = 0; v8 < 4; ++v8) {
+      float sv[8], hv[8];
+      load_affine8<CB>(pp, cb + c0 + v8 * 8, sc, sf, c0 + v8 * 8, sv, hv);
+      __half2* oh = reinterpret_cast<__half2*>(&o[v8]);
+#pragma unroll
+      for (int e2 = 0; e2 < 4; ++e2) {
+        const int e = v8 * 8 + e2 * 2;
+        const float a0 = fmaf(__uint_as_float(r[e]), sv[e2 * 2], hv[e2 * 2]);
+        const float a1 = fmaf(__uint_as_float(r[e + 1]), sv[e2 * 2 + 1], hv[e2 * 2 + 1]);
+        oh[e2] = __floats2half2_rn(act_ct<ACT>(a0, slope), act_ct<ACT>(a1, slope));
+      }
+      o[v8].x &= keep; o[v8].y &= keep; o[v8].z &= keep; o[v8].w &= keep;
+    }
+    if (issuer) bulk_wait_group_read0();  // the previous store has read the staging tile
+    named_bar_sync(bar_id, 128);
+#pragma unroll
+    for (int v8 = 0; v8 < 4; ++v8)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (((uint32_t)v8 ^ swz) << 4)), "r"(o[v8].x), "r"(o[v8].y),
+                   "r"(o[v8].z), "r"(o[v8].w)
+                   : "memory");
+    fence_proxy_async_smem();  // the rows are read by the TMA store (async proxy)
+    named_bar_sync(bar_id, 128);
+    if (issuer) {
+      tma_store_2d(ymap, st_team, ch0 + (c0 - col_lo), y_row0);
+      bulk_commit_group();
+    }
   }
 }
 
@@ -625,6 +717,7 @@ struct PconvParams {
   // block: the epilogue then takes them from the constant bank (uniform loads on the scalar path) and issues no
   // shared-memory load for them -- the shared-memory pipe is what the MMA's operand reads compete for.
   int use_const;
+  int res_tma;             // the residual (padded position layout) arrives by TMA: see ResTma; its two 8 KB tiles follow the staging tiles
   float cscale[512];
   float cshift[512];
 };
@@ -693,7 +786,7 @@ __host__ __device__ constexpr int pconv_threads(int ew) { return (kPconvProducer
 template <int NT, int MS, bool WRES, int EW>
 __global__ void __launch_bounds__(pconv_threads(EW), 1)
 pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapAT, const __grid_constant__ CUtensorMap tmapB,
-             const __grid_constant__ PconvParams p) {
+             const __grid_constant__ CUtensorMap tmapY0, const __grid_constant__ CUtensorMap tmapY1, const __grid_constant__ PconvParams p) {
   constexpr int kM = MS * kTileM;
   constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
   constexpr int kPconvThreads = pconv_threads(EW);
@@ -714,10 +807,13 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   const uint32_t bar_tempty = bar_pfull + 96;         // [4]
   const uint32_t bar_wfull = bar_pfull + 128;         // [w_stages] (resident: [0] only)
   const uint32_t bar_wempty = bar_wfull + 8 * 32;     // [w_stages]
+  const uint32_t bar_res = bar_wempty + 8 * 30;       // [2]: residual tile of each epilogue team has landed
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(bars + 16 + 64);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   uint32_t* s_tab = s_tmem + 4;
-  uint8_t* s_stage = sm + tail + 7168 + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;  // per-warp staging tile of the epilogue warps
+  // staging tiles of the epilogue: 2 KB per warp, or 8 KB per team of four warps (TMA-stored outputs); 1024-byte aligned
+  const uint32_t stage_off = ((base + tail + 7168u + 1023u) & ~1023u) - base;
+  uint8_t* s_stage = sm + stage_off + ((int)(threadIdx.x >> 5) - kPconvProducerWarps) * 2048;
 
   // (the shuffle tells the compiler that the warp index is the same in all lanes, so per-role branches are uniform)
   const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -744,6 +840,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       mbar_init(bar_wfull + 8 * s, 1);
       mbar_init(bar_wempty + 8 * s, 1);
     }
+    mbar_init(bar_res, 1);
+    mbar_init(bar_res + 8, 1);
     *s_abort = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmapA);
@@ -951,6 +1049,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     const Pos d_item = pos_of((long long)gridDim.x * kM);
     Pos pos0 = pos_of((long long)blockIdx.x * kM + row_in_tile);  // (work items are whole M tiles unless dist_n)
     griddep_wait();  // residual rows come from, and outputs may overwrite what was read by, earlier launches
+    // residual by TMA (see ResTma): the first tile of this CTA is requested here, every later one by the step before it
+    const bool rtma = EW == 8 && p.res_tma != 0;
+    const uint32_t res_tile = base + stage_off + (p.direct_store ? 0u : (uint32_t)(EW * 2048)) + (uint32_t)half * 8192u;
+    uint32_t res_phase = 0;
+    if (rtma && q4 == 0 && lane == 0 && (int)blockIdx.x < n_items) {
+      mbar_expect_tx(bar_res + 8 * half, 128u * 64u);
+      tma_load_2d(res_tile, &tmapY0, bar_res + 8 * half, col_lo, (int)((long long)blockIdx.x * kM));
+    }
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       int m_tile, n_lo, n_hi;
       pconv_item(p, item, m_tile, n_lo, n_hi);
@@ -963,7 +1069,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const float* sc = staged ? s_scale + nb : p.scale + nb;
         const float* sf = staged ? s_shift + nb : p.shift + nb;
         const OutSeg& sg = p.seg[(nb + col_lo) >= p.n_split ? 1 : 0];
-        if (sg.residual) {
+        if (sg.residual && !rtma) {
           // pull the residual rows of this CTA's next tile (and of its first tile) towards L2 now, so that
           // the loads in the epilogue steps below find them there instead of waiting on HBM
           for (int which = ((item == (int)blockIdx.x || p.dist_n) ? 0 : 1); which < (p.dist_n ? 1 : 2); ++which) {
@@ -984,7 +1090,14 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             }
           }
         }
-        if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) { ok = false; break; }
+        if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) ok = false;
+        if (EW == 8 && sg.padded && !p.direct_store) {
+          // the TMA-stored steps below meet at named barriers: the four warps of a team take the decision to go on
+          // together (every warp arrives here, its wait being bounded, and reads the flag after the barrier)
+          named_bar_sync(1 + half, 128);
+          if (*s_abort) ok = false;
+        }
+        if (!ok) break;
         tc_fence_after();
         AIG_STAMP(blockIdx.x == 0 && cnt < 12 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 5);
         Pos a = pos0;
@@ -1008,8 +1121,31 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           // residual: plain channels-last, or the padded position layout
           const __half* rrow = (sg.residual && !(AIG_DBG & 4)) ? sg.residual + (sg.res_padded ? qpos : pix) * sg.channels : nullptr;
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
+          if (EW == 8 && sg.padded && !p.direct_store) {
+            // padded destination: the team's 128 rows x 32 columns leave through one TMA store per step
+            const uint32_t st_team = base + stage_off + (uint32_t)half * 8192u;
+            const void* ymap = (nb + col_lo) >= p.n_split ? static_cast<const void*>(&tmapY1) : static_cast<const void*>(&tmapY0);
+            const int y_row0 = (int)((long long)m_tile * kM) + sub * kTileM;
+            const bool issuer = q4 == 0 && lane == 0;
+#define AIG_EPI_TMA(ACT) \
+  epi_cols32_tma<ACT>(t_addr, col_lo, col_hi, nb - sg.c0 + col_lo, sc, sf, p.slope, valid, st_team, row_in_tile, issuer, 1 + half, ymap, y_row0)
+            switch (sg.act) {
+              case AIG_ACT_RELU: AIG_EPI_TMA(AIG_ACT_RELU); break;
+              case AIG_ACT_SWISH: AIG_EPI_TMA(AIG_ACT_SWISH); break;
+              case AIG_ACT_LEAKY: AIG_EPI_TMA(AIG_ACT_LEAKY); break;
+              default: AIG_EPI_TMA(AIG_ACT_NONE); break;
+            }
+#undef AIG_EPI_TMA
+            continue;
+          }
 #define AIG_EPI(ACT)                                                                                                          \
-  if (p.use_const) {                                                                                                           \
+  if (rtma && rrow) {                                                                                                          \
+    const int r0 = (int)((long long)m_tile * kM) + sub * kTileM;                                                               \
+    const int nx = sub + 1 < MS ? r0 + kTileM : (item + (int)gridDim.x < n_items ? (int)((long long)(item + (int)gridDim.x) * kM) : -1);  \
+    const ResTma rt{res_tile, bar_res + 8u * half, &res_phase, q4 == 0 && lane == 0, 1 + half, &tmapY0, col_lo, r0, nx, s_abort, p.gerr};  \
+    if (p.direct_store) epi_fused_cols32<ACT, true, true, PconvParams, true, ResTma>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb, sinv, rt, row_in_tile);  \
+    else epi_fused_cols32_t<ACT, true, true, PconvParams, true, ResTma>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, s_stage, lane, AIG_DBG, p, nb, sinv, rt, row_in_tile);  \
+  } else if (p.use_const) {                                                                                                    \
     if (p.direct_store) {                                                                                                      \
       if (rrow) epi_fused_cols32<ACT, true, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb, sinv);  \
       else epi_fused_cols32<ACT, false, true>(t_addr, col_lo, col_hi, nb - sg.c0, sg.channels, sc, sf, rrow, yrow, p.slope, valid, AIG_DBG, p, nb, sinv);      \
@@ -1035,6 +1171,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       }
       pos0 = pos_add(pos0, d_item);
     }
+    if (q4 == 0 && lane == 0) bulk_wait_group0();  // TMA stores of this team (if any) have completed
   }
 
   if (*s_abort) {
@@ -1167,6 +1304,8 @@ struct aig_conv_plan {
   PconvParams pp{};
   uint32_t* pc_tab = nullptr;
   CUtensorMap tmapP{}, tmapPT{}, tmapBp{};  // patch rows one per box / patch_vrows per box, weights
+  CUtensorMap tmapY[2]{};                   // destinations in the padded position layout (TMA-stored): main, shortcut
+  const void* tmapY_ptr[2] = {nullptr, nullptr};
   const void* tmapP_ptr = nullptr;
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1, pc_EW = 8;
   bool pc_wres = false;
@@ -1174,6 +1313,7 @@ struct aig_conv_plan {
   bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
   bool is_down = false;                        // fused down-sampling pair (main k4 s2 p1 + shortcut k2 s2 p0)
   bool in_padded = false;                      // input and residual arrive in the padded position layout
+  bool res_tiles = false;                      // ... and the residual is delivered by TMA into two 8 KB tiles of shared memory
 };
 
 namespace {
@@ -1360,8 +1500,8 @@ int pconv_refresh_affine(aig_conv_plan* pl) {
 // ---- patch-resident path: host side ------------------------------------------------------
 // Shared memory behind the patches and weights: scale/shift, barriers and K schedule tables, then one 2 KB staging
 // tile per epilogue warp (the coalescing epilogue; N = 64 tiles store directly and need none).
-constexpr int pconv_tail(int ew, bool direct_store) { return 7168 + (direct_store ? 0 : ew * 2048); }
-constexpr int pconv_budget(int ew, bool direct_store) { return 227 * 1024 - 1024 /*align*/ - pconv_tail(ew, direct_store); }
+constexpr int pconv_tail(int ew, bool direct_store, bool res_tiles) { return 7168 + 1024 + (direct_store ? 0 : ew * 2048) + (res_tiles ? 16384 : 0); }
+constexpr int pconv_budget(int ew, bool direct_store, bool res_tiles) { return 227 * 1024 - 1024 /*align*/ - pconv_tail(ew, direct_store, res_tiles); }
 
 template <int NT, int MS, bool WRES, int EW>
 int launch_pconv(aig_conv_plan* pl) {
@@ -1382,7 +1522,7 @@ int launch_pconv(aig_conv_plan* pl) {
   attr[0].val.programmaticStreamSerializationAllowed = pl->pc_pdl ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES, EW>, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->pp));
+  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, pconv_kernel<NT, MS, WRES, EW>, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->tmapY[0], pl->tmapY[1], pl->pp));
   return AIG_OK;
 }
 
@@ -1468,7 +1608,7 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
     const int o = small ? n_opts - 1 - oo : oo;
     const int NT = opts[o].NT, wblock = NT * 128;
     const int dense_kb = q.taps * q.cblocks;
-    const int kPconvBudget = pconv_budget(ew, NT == 64);
+    const int kPconvBudget = pconv_budget(ew, NT == 64, pl->res_tiles);
     if (f_nt && NT != f_nt) continue;
     if (!small && NT == 64 && o > 0) continue;  // the 64-wide tiling of a wider layer is for the small regime only
     int ms_top = 256 / NT < 1 ? 1 : 256 / NT;
@@ -1500,7 +1640,7 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
             if (q.cblocks % G != 0) break;
             if (f_g && G != f_g) continue;
             long long stages = (kPconvBudget - pb * region * G) / wblock;
-            if (stages > 32) stages = 32;
+            if (stages > 30) stages = 30;  // (32 barrier slots per direction; the last two serve the residual tiles)
             if (stages >= min_stages) take(o, ms, pb, G, false, stages);
           }
           if (ms == 1) break;
@@ -1531,7 +1671,7 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
-  pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + pconv_tail(ew, NT == 64);
+  pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + pconv_tail(ew, NT == 64, pl->res_tiles);
   const long long items = (long long)q.m_tiles * (q.dist_n ? q.n_tiles : 1);
   pl->pc_grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
   return true;
@@ -1641,6 +1781,24 @@ int encode_P(aig_conv_plan* pl, const void* x) {
   return AIG_OK;
 }
 
+// Destination in the padded position layout as a 2-D tensor [rows][channels]; box = 32 channels x 128 rows (one
+// team step of the epilogue), 64-byte swizzle.  Rows: the allocation, rounded up to whole tiles.
+int encode_Y(aig_conv_plan* pl, int idx, const void* y, int channels) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const long long rows = aig_conv_padded_rows(pl->d.batch, pl->Ho, pl->Wo, pl->is_down ? 1 : pl->d.ph);
+  cuuint64_t dims[2] = {(cuuint64_t)channels, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)channels * 2};
+  cuuint32_t box[2] = {32u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&pl->tmapY[idx], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(y), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled(padded output) failed: %d", (int)r);
+  pl->tmapY_ptr[idx] = y;
+  return AIG_OK;
+}
+
 // Stride-1 2-D convolutions with in_c % 64 == 0 take the patch-resident kernel when a tile fits.
 int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   const aig_conv_desc& d = pl->d;
@@ -1656,6 +1814,9 @@ int pconv_try_plain(aig_ctx* ctx, aig_conv_plan* pl) {
   q.RP = d.in_h + d.ph;
   q.pad = d.ph;
   q.flat = pl->in_padded ? 1 : 0;
+  // residual by TMA where the epilogue bounds the launch (up to 128 output channels: 89 -> 77 us on the 64-channel
+  // layer); the 256-channel layers are bound by their weight stream and keep the 16 KB for its ring
+  pl->res_tiles = pl->in_padded && d.out_c <= 128 && d.out_c % 64 == 0;
   q.kw = d.kw;
   q.taps = d.kh * d.kw;
   q.cblocks = d.in_c / 64;
@@ -1796,6 +1957,11 @@ int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* resid
     }
     pl->pp.seg[0].y = (__half*)y;
     pl->pp.seg[0].residual = (const __half*)residual;
+    pl->pp.res_tma = residual && pl->res_tiles && pl->pp.n_tiles == 1 && !pl->pp.dist_n && pl->pp.use_const && pl->pc_EW == 8 && pl->d.out_c % 64 == 0 && pl->pp.dbg == 0;
+    if (pl->pp.res_tma && pl->tmapY_ptr[0] != residual) {
+      const int rc = encode_Y(pl, 0, residual, pl->d.out_c);
+      if (rc != AIG_OK) return rc;
+    }
     return dispatch_pconv(pl);
   }
   if (pl->tmapA_ptr != x) {
@@ -2048,6 +2214,7 @@ int aig_resdown_forward(aig_conv_plan* pl, const aig_half* x_s2d, aig_half* y_ma
   DeviceGuard g(ctx->device);
   AIG_REQUIRE(ctx, pl->is_down && x_s2d && y_main && y_short && pl->weights_set, "resdown forward: bad arguments or weights not set");
   AIG_REQUIRE(ctx, ((uintptr_t)x_s2d & 15) == 0 && ((uintptr_t)y_main & 15) == 0 && ((uintptr_t)y_short & 15) == 0, "resdown forward: tensors must be 16-byte aligned");
+  int rc0 = AIG_OK;
   if (pl->tmapP_ptr != x_s2d) {
     const int rc = encode_P(pl, x_s2d);
     if (rc != AIG_OK) return rc;
@@ -2056,6 +2223,10 @@ int aig_resdown_forward(aig_conv_plan* pl, const aig_half* x_s2d, aig_half* y_ma
   pl->pp.seg[0].residual = nullptr;
   pl->pp.seg[1].y = (__half*)y_short;
   pl->pp.seg[1].residual = nullptr;
+  if (pl->pp.seg[0].padded) {
+    if (pl->tmapY_ptr[0] != y_main && (rc0 = encode_Y(pl, 0, y_main, pl->d.out_c)) != AIG_OK) return rc0;
+    if (pl->tmapY_ptr[1] != y_short && (rc0 = encode_Y(pl, 1, y_short, pl->d.out_c)) != AIG_OK) return rc0;
+  }
   return dispatch_pconv(pl);
 }
 
