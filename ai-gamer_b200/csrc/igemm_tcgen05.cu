@@ -1619,15 +1619,24 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
     if (f_ms) ms_top = f_ms;
     if (ms_top * NT > 512) continue;
     while (!f_ms && ms_top > 1 && ceil_div_ll(total_q, ms_top * kTileM) < ctx->sm_count) ms_top /= 2;
-    // resident weights beside two whole patches (then one), largest tile first
-    for (int pb = (f_pb ? f_pb : 2); pb >= 2 && best < 0; --pb) {
-      if (f_pb && pb != f_pb) continue;
-      if (f_g && f_g != q.cblocks) continue;
-      for (int ms = ms_top; ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
-        const long long patch = (long long)region_rows_of(ms * kTileM) * 128 * q.cblocks;
-        if (opts[o].n_tiles == 1 && pb * patch + (long long)dense_kb * wblock <= kPconvBudget) take(o, ms, pb, q.cblocks, true, dense_kb);
-        if (ms == 1) break;
+    // resident weights beside two patch units, largest tile and largest channel-block group first
+    bool try_resident = opts[o].n_tiles == 1;
+#ifdef AIG_TUNING
+    if (const char* e = getenv("AIG_PCONV_NORES")) if (atoi(e) == 1) try_resident = false;
+    const char* e2 = getenv("AIG_PCONV_NORES");
+    const bool grouped_resident = !(e2 && atoi(e2) == 2);
+#else
+    const bool grouped_resident = true;
+#endif
+    for (int ms = ms_top; try_resident && ms >= (f_ms ? ms_top : 1) && best < 0; ms /= 2) {
+      const long long region = (long long)region_rows_of(ms * kTileM) * 128;
+      for (int G = q.cblocks; G >= 1 && best < 0; G /= 2) {
+        if (q.cblocks % G != 0) break;
+        if (f_g && G != f_g) continue;
+        if ((!f_pb || f_pb == 2) && 2 * region * G + (long long)dense_kb * wblock <= kPconvBudget) take(o, ms, 2, G, true, dense_kb);
+        if (!grouped_resident) break;
       }
+      if (ms == 1) break;
     }
     // streamed weights: two patch units of the largest channel-block group that leaves three stages (a ring of two
     // cannot cover the refill round trip: 42 -> 36 us on the 256 -> 256 down-sampling launch), else two
@@ -1667,6 +1676,9 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   // at N = 64 a warp's column half is 64 bytes of a 128-byte output row: the staging tile of the coalescing
   // epilogue costs more there than the scattered stores it saves (measured: 95 vs 93 us on a 64 -> 64 layer)
   q.direct_store = NT == 64 ? 1 : 0;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_DIRECT")) if (atoi(e)) q.direct_store = 1;  // (the staging tiles stay allocated)
+#endif
   if (const char* e = getenv("AIG_NO_PDL")) pl->pc_pdl = !atoi(e);
   pl->pc_NT = NT;
   pl->pc_MS = best_ms;
