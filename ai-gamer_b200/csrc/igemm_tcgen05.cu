@@ -709,6 +709,7 @@ struct PconvParams {
   OutSeg seg[2];
   int* gerr;
   const uint32_t* tab;     // K schedule tables (see PconvTab)
+  const int* sched;        // per-CTA item lists (see PconvItemIter), or null
   int tab_words;
   int dbg;                 // tuning builds: epilogue parts to leave out (bit flags); 0 otherwise
   int direct_store;        // epilogue stores straight from the row-owning lanes instead of through the staging tile
@@ -756,6 +757,33 @@ __device__ __forceinline__ void pconv_item(const PconvParams& p, int item, int& 
     m_tile = item;
     n_lo = 0;
     n_hi = p.n_tiles;
+  }
+}
+// The items of a CTA in order: every gridDim.x-th item from blockIdx.x on, or, with a schedule table (dist_n == 2:
+// a fused down-sampling launch whose main and shortcut N tiles differ fourfold in length and whose M tiles do not
+// fill the SMs evenly), the list the host computed for this CTA (longest-processing-time-first assignment of the
+// (M tile, N tile) pairs).  sched[c] .. sched[c + 1] index the items of CTA c behind the gridDim.x + 1 offsets.
+struct PconvItemIter {
+  int item, si, se;
+};
+__device__ __forceinline__ PconvItemIter pconv_item_begin(const PconvParams& p) {
+  PconvItemIter it;
+  if (p.sched) {
+    it.si = p.sched[blockIdx.x];
+    it.se = p.sched[blockIdx.x + 1];
+    it.item = it.si < it.se ? p.sched[it.si] : (1 << 30);
+  } else {
+    it.si = it.se = 0;
+    it.item = (int)blockIdx.x;
+  }
+  return it;
+}
+__device__ __forceinline__ void pconv_item_next(const PconvParams& p, PconvItemIter& it) {
+  if (p.sched) {
+    ++it.si;
+    it.item = it.si < it.se ? p.sched[it.si] : (1 << 30);
+  } else {
+    it.item += (int)gridDim.x;
   }
 }
 
@@ -870,7 +898,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       bool ok = true;
       const int n_items = pconv_items(p);
       griddep_wait();  // activations come from the previous launch
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      for (PconvItemIter itr = pconv_item_begin(p); itr.item < n_items && ok; pconv_item_next(p, itr), ++it) {
+        const int item = itr.item;
         int m_tile, n_lo, n_hi;
         pconv_item(p, item, m_tile, n_lo, n_hi);
         const int units = p.groups == 1 ? 1 : (n_hi - n_lo) * p.groups;
@@ -921,7 +950,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         int stage = 0, it = 0;
         uint32_t wphase = 0;
         const int n_items = pconv_items(p);
-        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+        for (PconvItemIter itr = pconv_item_begin(p); itr.item < n_items && ok; pconv_item_next(p, itr), ++it) {
+        const int item = itr.item;
           int m_tile, n_lo, n_hi;
           pconv_item(p, item, m_tile, n_lo, n_hi);
           for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile) {
@@ -953,7 +983,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       int it = 0, cnt = 0, stage = 0, buf = 0;
       uint32_t wphase = 0, pph = 0;
       const int n_items = pconv_items(p);
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+      for (PconvItemIter itr = pconv_item_begin(p); itr.item < n_items && ok; pconv_item_next(p, itr), ++it) {
+        const int item = itr.item;
         int m_tile, n_lo, n_hi;
         pconv_item(p, item, m_tile, n_lo, n_hi);
         const long long q0 = (long long)m_tile * kM;
@@ -1057,7 +1088,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       mbar_expect_tx(bar_res + 8 * half, 128u * 64u);
       tma_load_2d(res_tile, &tmapY0, bar_res + 8 * half, col_lo, (int)((long long)blockIdx.x * kM));
     }
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (PconvItemIter itr = pconv_item_begin(p); itr.item < n_items && ok; pconv_item_next(p, itr)) {
+      const int item = itr.item;
       int m_tile, n_lo, n_hi;
       pconv_item(p, item, m_tile, n_lo, n_hi);
       if (p.dist_n) pos0 = pos_of((long long)m_tile * kM + row_in_tile);
@@ -1308,6 +1340,7 @@ struct aig_conv_plan {
   const void* tmapY_ptr[2] = {nullptr, nullptr};
   const void* tmapP_ptr = nullptr;
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1, pc_EW = 8;
+  int* pc_sched = nullptr;                     // per-CTA item lists of the patch-resident launch (device), or null
   bool pc_wres = false;
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
   bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
@@ -1684,8 +1717,44 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
   pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + pconv_tail(ew, NT == 64, pl->res_tiles);
-  const long long items = (long long)q.m_tiles * (q.dist_n ? q.n_tiles : 1);
+  // a launch with a main and a (sparse) shortcut N tile whose M tiles do not fill the SMs evenly: the (M tile,
+  // N tile) pairs become the work items, assigned to the CTAs longest first
+  bool lpt = !q.dist_n && q.n_tiles == 2 && q.sparse_tile0 == 1 && q.m_tiles % ctx->sm_count != 0;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_NODIST2")) if (atoi(e)) lpt = false;
+#endif
+  cudaFree(pl->pc_sched);
+  pl->pc_sched = nullptr;
+  q.sched = nullptr;
+  const long long items = (long long)q.m_tiles * ((q.dist_n || lpt) ? q.n_tiles : 1);
   pl->pc_grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
+  if (lpt) {
+    q.dist_n = 2;
+    const int G = pl->pc_grid;
+    const long long w_main = (long long)q.taps * q.cblocks, w_short = (long long)q.taps * q.sub_cblocks;
+    std::vector<long long> load(G, 0);
+    std::vector<std::vector<int>> lists(G);
+    auto place = [&](int item, long long w) {
+      int best_c = 0;
+      for (int c = 1; c < G; ++c)
+        if (load[c] < load[best_c]) best_c = c;
+      load[best_c] += w;
+      lists[best_c].push_back(item);
+    };
+    for (int m = 0; m < q.m_tiles; ++m) place(2 * m, w_main);       // item = m_tile * n_tiles + n_tile
+    for (int m = 0; m < q.m_tiles; ++m) place(2 * m + 1, w_short);
+    std::vector<int> tab(G + 1);
+    int off = G + 1;
+    for (int c = 0; c < G; ++c) {
+      tab[c] = off;
+      off += (int)lists[c].size();
+    }
+    tab[G] = off;
+    for (int c = 0; c < G; ++c) tab.insert(tab.end(), lists[c].begin(), lists[c].end());
+    if (cudaMalloc(&pl->pc_sched, tab.size() * sizeof(int)) != cudaSuccess) return false;
+    cudaMemcpy(pl->pc_sched, tab.data(), tab.size() * sizeof(int), cudaMemcpyHostToDevice);
+    q.sched = pl->pc_sched;
+  }
   return true;
 }
 
@@ -1913,6 +1982,7 @@ int aig_conv_plan_destroy(aig_conv_plan* pl) {
   cudaFree(pl->shift);
   cudaFree(pl->pp.ts);
   cudaFree(pl->pc_tab);
+  cudaFree(pl->pc_sched);
   delete pl;
   return AIG_OK;
 }

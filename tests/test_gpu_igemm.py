@@ -275,6 +275,7 @@ RESDOWN = [
     (5, 32, 72, 128, 64),    # several M tiles per CTA, resident weights
     (1, 256, 10, 12, 256),   # 1024 space-to-depth channels: the patch streams in channel-block groups
     (4, 256, 9, 16, 256),    # the same with odd height and several M tiles
+    (230, 128, 9, 16, 256),  # 81 M tiles on 148 SMs: main and shortcut tiles of an M tile go to different CTAs
 ]
 
 
