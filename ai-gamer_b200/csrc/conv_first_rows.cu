@@ -94,12 +94,7 @@ __device__ __forceinline__ uint2 pixel_rgb(uint32_t r, uint32_t g, uint32_t b, u
 template <int ACT>
 __device__ __forceinline__ float act_rows(float v, float slope) {
   if (ACT == AIG_ACT_RELU) return fmaxf(v, 0.f);
-  if (ACT == AIG_ACT_SWISH) {
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-    return v * r;
-  }
+  if (ACT == AIG_ACT_SWISH) return swish_sfu(v);
   if (ACT == AIG_ACT_LEAKY) return v < 0.f ? v * slope : v;
   return v;
 }

@@ -71,14 +71,7 @@ struct IgemmCfg {
 template <int ACT>
 __device__ __forceinline__ float act_ct(float v, float slope) {
   if (ACT == AIG_ACT_RELU) return fmaxf(v, 0.f);
-  if (ACT == AIG_ACT_SWISH) {
-    // v * sigmoid(v) with the SFU's ex2 and rcp approximations (about 2 ulp of fp32 each, far below
-    // the fp16 rounding of the result); an IEEE reciprocal here costs several times the rest of the epilogue
-    float e, r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-    return v * r;
-  }
+  if (ACT == AIG_ACT_SWISH) return swish_sfu(v);  // one special-function operation per value
   if (ACT == AIG_ACT_LEAKY) return v < 0.f ? v * slope : v;
   return v;
 }
@@ -718,6 +711,7 @@ struct PconvParams {
   // block: the epilogue then takes them from the constant bank (uniform loads on the scalar path) and issues no
   // shared-memory load for them -- the shared-memory pipe is what the MMA's operand reads compete for.
   int use_const;
+  int tma_store;           // padded destinations leave through TMA stores (see epi_cols32_tma)
   int res_tma;             // the residual (padded position layout) arrives by TMA: see ResTma; its two 8 KB tiles follow the staging tiles
   float cscale[512];
   float cshift[512];
@@ -1123,7 +1117,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           }
         }
         if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) ok = false;
-        if (EW == 8 && sg.padded && !p.direct_store) {
+        if (EW == 8 && sg.padded && p.tma_store && !p.direct_store) {
           // the TMA-stored steps below meet at named barriers: the four warps of a team take the decision to go on
           // together (every warp arrives here, its wait being bounded, and reads the flag after the barrier)
           named_bar_sync(1 + half, 128);
@@ -1153,7 +1147,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
           // residual: plain channels-last, or the padded position layout
           const __half* rrow = (sg.residual && !(AIG_DBG & 4)) ? sg.residual + (sg.res_padded ? qpos : pix) * sg.channels : nullptr;
           const uint32_t t_addr = tmem_base + (uint32_t)((acc * MS + sub) * NT) + ((uint32_t)(q4 * 32) << 16);
-          if (EW == 8 && sg.padded && !p.direct_store) {
+          if (EW == 8 && sg.padded && p.tma_store && !p.direct_store) {
             // padded destination: the team's 128 rows x 32 columns leave through one TMA store per step
             const uint32_t st_team = base + stage_off + (uint32_t)half * 8192u;
             const void* ymap = (nb + col_lo) >= p.n_split ? static_cast<const void*>(&tmapY1) : static_cast<const void*>(&tmapY0);
@@ -2040,6 +2034,9 @@ int aig_conv_forward(aig_conv_plan* pl, const aig_half* x, const aig_half* resid
     pl->pp.seg[0].y = (__half*)y;
     pl->pp.seg[0].residual = (const __half*)residual;
     pl->pp.res_tma = residual && pl->res_tiles && pl->pp.n_tiles == 1 && !pl->pp.dist_n && pl->pp.use_const && pl->pc_EW == 8 && pl->d.out_c % 64 == 0 && pl->pp.dbg == 0;
+#ifdef AIG_TUNING
+    if (const char* e = getenv("AIG_PCONV_NORTMA")) if (atoi(e)) pl->pp.res_tma = 0;
+#endif
     if (pl->pp.res_tma && pl->tmapY_ptr[0] != residual) {
       const int rc = encode_Y(pl, 0, residual, pl->d.out_c);
       if (rc != AIG_OK) return rc;
@@ -2195,6 +2192,10 @@ int aig_resdown_plan_set_output_padded(aig_conv_plan* pl, int enable) {
   if (!pl) return AIG_ERR_INVALID;
   if (!pl->is_down || !pl->use_pconv) return aig_fail(pl->ctx, AIG_ERR_UNSUPPORTED, "padded output layout is an option of the fused down-sampling plan");
   pl->pp.seg[0].padded = pl->pp.seg[1].padded = enable ? 1 : 0;
+  pl->pp.tma_store = enable ? 1 : 0;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_NOTMASTORE")) if (atoi(e)) pl->pp.tma_store = 0;
+#endif
   return AIG_OK;
 }
 

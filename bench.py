@@ -422,6 +422,7 @@ def leg_conv3d(env, full):
             plan = pkg.ConvPlan(env.ctx, B, ci, h, w, co, 3, 2, 1, act=pkg.ACT_LEAKY, in_d=D, kd=3, sd=1, pd=1)
             wt = (torch.randn(co * ci * 27, device="cuda") * 0.05).half()
             bs = torch.zeros(co, device="cuda").half()
+            torch.cuda.synchronize()   # (torch fills these on its own stream; the library's context has another)
             plan.set_weights(wt, bs)
             n_in, n_out = B * D * h * w * ci, B * D * (h // 2) * (w // 2) * co
             rot = max(2, -(-140_000_000 // (n_in * 2)))
@@ -463,6 +464,7 @@ def leg_seqhead(env, full):
         sp = SY.make_seq_params(0)
         lp = pkg.LstmPlan(env.ctx, T, 2, d, B, d, batch_major=True)
         blob = torch.from_numpy(sp["lstm"]).cuda()
+        torch.cuda.synchronize()
         lp.set_weights(blob)
         yy = torch.empty(B * T * d, device="cuda", dtype=torch.float16)
         r_l = env.timer.regions(lambda i: lp.forward(embs[i % n_rot], yy), 10, 3)
@@ -470,12 +472,14 @@ def leg_seqhead(env, full):
         fp = pkg.FcPlan(env.ctx, B * T, d, 4 * d)
         pkg.lib().aig_fc_plan_set_output_f32(fp.handle, 1)
         wfc, bfc = torch.randn(4 * d * d, device="cuda").half(), torch.zeros(4 * d, device="cuda").half()
+        torch.cuda.synchronize()
         fp.set_weights_out_in(wfc, bfc)
         gx = torch.empty(B * T * 4 * d, device="cuda", dtype=torch.float32)
         r_p = env.timer.regions(lambda i: fp.forward(embs[i % n_rot], gx), 10, 3)
         fp.close()
         mp = pkg.MhaPlan(env.ctx, B, T, d, 8, rope_base=10000.0)
         ws = [torch.from_numpy(sp[k]).cuda() for k in ("wq", "wk", "wv", "wo")]
+        torch.cuda.synchronize()
         mp.set_weights(*ws)
         r_m = env.timer.regions(lambda i: mp.forward(embs[i % n_rot], yy), 10, 3)
         mp.close()

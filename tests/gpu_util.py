@@ -32,9 +32,14 @@ def ctx():
 
 
 def dev(a):
+    """Host array -> device tensor, complete on return.  The copy runs on torch's stream and the library's context
+    has a stream of its own (non-blocking), so the copy is waited for here: a copy from pageable memory may return
+    while its last chunk is still on the way."""
     import torch
 
-    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    torch.cuda.synchronize()
+    return t
 
 
 def host(t):
