@@ -805,13 +805,23 @@ constexpr int kPconvProducerWarps = 4;
 constexpr int kWeightWarp = 2;
 __host__ __device__ constexpr int pconv_threads(int ew) { return (kPconvProducerWarps + ew) * 32; }
 
-template <int NT, int MS, bool WRES, int EW>
+// PAIR: two CTAs of a cluster share every weight block.  One tcgen05.mma.cta_group::2 computes 256 positions x NT
+// channels: each CTA supplies its own 128 positions (its own patch, at the same shared-memory offset in both: a flat
+// patch starts at its tile's first position) and HALF of the weight rows, and receives its 128 rows of the result in
+// its own TMEM at the same address.  A CTA thereby writes and reads half of the weight bytes per MMA, which is
+// what bounds the 256-channel layers (shared-memory bandwidth).  The first CTA's MMA warp issues for the pair; all
+// loads of both CTAs count on the first CTA's barriers (cp.async.bulk.tensor ... cta_group::2), its commits release
+// the stages, patch units and accumulators of both, and both CTAs' epilogue warps arrive at its accumulator-free
+// barriers.  M tiles 2j and 2j + 1 form a pair; flat inputs, streamed weights, MS = 1, 8 epilogue warps only.
+template <int NT, int MS, bool WRES, int EW, bool PAIR = false>
 __global__ void __launch_bounds__(pconv_threads(EW), 1)
 pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapAT, const __grid_constant__ CUtensorMap tmapB,
              const __grid_constant__ CUtensorMap tmapY0, const __grid_constant__ CUtensorMap tmapY1, const __grid_constant__ PconvParams p) {
+  static_assert(!PAIR || (MS == 1 && !WRES && EW == 8), "pair kernel: MS = 1, streamed weights, 8 epilogue warps");
   constexpr int kM = MS * kTileM;
-  constexpr int kWBlock = NT * 128;  // one (tap, channel block) of weights
+  constexpr int kWBlock = (PAIR ? NT / 2 : NT) * 128;  // one (tap, channel block) of weights: this CTA's rows of it
   constexpr int kPconvThreads = pconv_threads(EW);
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
   constexpr int kArrivals = (EW == 16 && MS == 1) ? 8 : EW;  // epilogue warps that drain one accumulator buffer
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -855,7 +865,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
     }
     for (int a = 0; a < 4; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, kArrivals);
+      mbar_init(bar_tempty + 8 * a, PAIR ? 2 * kArrivals : kArrivals);  // (pair: both CTAs' epilogue warps arrive at the first CTA's)
     }
     const int nw = WRES ? 1 : p.w_stages;
     for (int s = 0; s < nw; ++s) {
@@ -872,14 +882,24 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   }
   constexpr uint32_t kTmemCols = 512u;  // acc_bufs buffers of MS * NT columns each
   if (warp == 1) {
-    tmem_alloc(smem_u32(s_tmem), kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(s_tmem), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(s_tmem), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised and their TMEM allocated before anything crosses
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
   const int dense_kb = p.taps * p.cblocks;
+  // barriers the pair's loads count on and its epilogues arrive at: the first CTA's (cluster-window addresses)
+  const uint32_t pfull_first = PAIR ? mapa_shared(bar_pfull, 0) : bar_pfull;
+  const uint32_t wfull_first = PAIR ? mapa_shared(bar_wfull, 0) : bar_wfull;
+  const uint32_t tempty_first = PAIR ? mapa_shared(bar_tempty, 0) : bar_tempty;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ patch producer
@@ -904,14 +924,19 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         for (int u = 0; u < units && ok; ++u) {
           const int g = p.groups == 1 ? 0 : u % p.groups;
           if (AIG_DBG & 64) continue;
-          if (!mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)) { ok = false; break; }
-          if (leader) mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(p.flat ? p.region_bytes * p.G : p.patch_vrows * p.P * 128 * p.G));
+          if (!(PAIR ? mbar_wait_bounded_cl(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401)
+                     : mbar_wait_bounded(bar_pempty + 8 * buf, ph ^ 1u, s_abort, p.gerr, 401))) { ok = false; break; }
+          if (leader && rank == 0)
+            mbar_expect_tx(bar_pfull + 8 * buf, (uint32_t)(PAIR ? 2 : 1) * (uint32_t)(p.flat ? p.region_bytes * p.G : p.patch_vrows * p.P * 128 * p.G));
           const uint32_t dst0 = sPatch + buf * p.patch_bytes;
           if (p.flat) {
             const int row0 = (int)(q0 - (long long)p.pad * (p.P + 1));  // may be negative: rows before the tensor read as zeros
             for (int l = 0; l < p.G; ++l)
               for (int b = 0; b < p.flat_boxes; ++b)
-                if (leader) tma_load_2d(dst0 + l * p.region_bytes + b * p.flat_box_rows * 128, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, row0 + b * p.flat_box_rows);
+                if (leader) {
+                  if constexpr (PAIR) tma_load_2d_pair(dst0 + l * p.region_bytes + b * p.flat_box_rows * 128, &tmapAT, pfull_first + 8 * buf, (g * p.G + l) * 64, row0 + b * p.flat_box_rows);
+                  else tma_load_2d(dst0 + l * p.region_bytes + b * p.flat_box_rows * 128, &tmapAT, bar_pfull + 8 * buf, (g * p.G + l) * 64, row0 + b * p.flat_box_rows);
+                }
           } else if (p.tall_ok && yy0 + p.patch_vrows - 1 < p.RP + p.pad) {
             // the patch ends inside image n0 or in the padding rows below it: one box of patch_vrows rows per channel
             // block (rows past the image are zero-filled, which is what the shared padding rows hold)
@@ -954,10 +979,16 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             const uint32_t* ent = s_tab + kTabHead;
             for (uint32_t e = gs[0]; e < gs[p.groups]; ++e) {
               if (AIG_DBG & 128) continue;
-              if (!mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)) { ok = false; break; }
+              if (!(PAIR ? mbar_wait_bounded_cl(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402)
+                         : mbar_wait_bounded(bar_wempty + 8 * stage, wphase ^ 1u, s_abort, p.gerr, 402))) { ok = false; break; }
               if (leader) {
-                mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
-                tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
+                if constexpr (PAIR) {
+                  if (rank == 0) mbar_expect_tx(bar_wfull + 8 * stage, 2u * (uint32_t)kWBlock);
+                  tma_load_2d_pair(sW + stage * kWBlock, &tmapB, wfull_first + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT + (int)rank * (NT / 2));
+                } else {
+                  mbar_expect_tx(bar_wfull + 8 * stage, (uint32_t)kWBlock);
+                  tma_load_2d(sW + stage * kWBlock, &tmapB, bar_wfull + 8 * stage, (int)(ent[e] >> 16) * 64, n_tile * NT);
+                }
               }
               if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
             }
@@ -969,9 +1000,22 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     // all 32 lanes run the loop with identical values; one elected lane issues the MMAs and commits
-    {
-      constexpr uint32_t idesc = umma_idesc_f16(kTileM, NT);
+    // (pair: the first CTA's warp issues for both CTAs, the other CTA's warp has nothing to do)
+    if (!PAIR || rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(PAIR ? 2 * kTileM : kTileM, NT);
       const bool leader = elect_one();
+      // a commit arrives at this CTA's barrier and, in a pair, at the same barrier of the other CTA
+      auto commit = [&](uint32_t bar) {
+        if constexpr (PAIR) {
+          umma_commit_pair(bar);
+          umma_commit_pair(mapa_shared(bar, 1));
+        } else {
+          umma_commit(bar);
+        }
+      };
+      auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+        return PAIR ? mbar_wait_bounded_cl(bar, parity, s_abort, p.gerr, code) : mbar_wait_bounded(bar, parity, s_abort, p.gerr, code);
+      };
       bool ok = true;
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
       int it = 0, cnt = 0, stage = 0, buf = 0;
@@ -986,7 +1030,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
           const int acc = cnt % p.acc_bufs;
           const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
-          if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1u, s_abort, p.gerr, 503)) { ok = false; break; }
+          if (!wait(bar_tempty + 8 * acc, acc_phase ^ 1u, 503)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
           const bool sparse = n_tile >= p.sparse_tile0;
@@ -997,7 +1041,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             // the patch unit of this group: a new one per (N tile, group), or the M tile's only one
             const bool fresh = p.groups > 1 || n_tile == n_lo;
             if (fresh && !(AIG_DBG & 64)) {
-              if (!mbar_wait_bounded(bar_pfull + 8 * buf, pph, s_abort, p.gerr, 502)) { ok = false; break; }
+              if (!wait(bar_pfull + 8 * buf, pph, 502)) { ok = false; break; }
               AIG_STAMP(blockIdx.x == 0 && leader && it < 12 && n_tile == n_lo && g == 0, it * 8 + 3);
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
@@ -1009,7 +1053,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               if (WRES) {
                 b0 = sW + (en >> 16) * kWBlock;
               } else {
-                if (!(AIG_DBG & 128) && !mbar_wait_bounded(bar_wfull + 8 * stage, wphase, s_abort, p.gerr, 504)) { ok = false; break; }
+                if (!(AIG_DBG & 128) && !wait(bar_wfull + 8 * stage, wphase, 504)) { ok = false; break; }
                 b0 = sW + stage * kWBlock;
               }
               const uint32_t a_lo = umma_desc_lo(patch + (en & 0xFFFFu) * 128u), b_lo = umma_desc_lo(b0);
@@ -1017,22 +1061,27 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
               for (int sub = 0; sub < MS; ++sub) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k)
-                  if (leader) umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
-                                 b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+                  if (leader) {
+                    if constexpr (PAIR)
+                      umma_f16_ss_lo_pair(d_tmem, a_lo + (uint32_t)((k * 32) >> 4), b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+                    else
+                      umma_f16_ss_lo(d_tmem + (uint32_t)(sub * NT), a_lo + (uint32_t)((sub * (kTileM * 128) + k * 32) >> 4),
+                                     b_lo + (uint32_t)((k * 32) >> 4), umma_desc_hi(128), idesc, k == 0 ? first : 1u);
+                  }
               }
               first = 1u;
               if (!WRES) {
-                if (leader) umma_commit(bar_wempty + 8 * stage);
+                if (leader) commit(bar_wempty + 8 * stage);
                 if (++stage == p.w_stages) { stage = 0; wphase ^= 1u; }
               }
             }
             // the unit may be overwritten once these MMAs have read it
             if (ok && (p.groups > 1 || n_tile == n_hi - 1)) {
-              if (leader) umma_commit(bar_pempty + 8 * buf);
+              if (leader) commit(bar_pempty + 8 * buf);
               if (++buf == p.patch_bufs) { buf = 0; pph ^= 1u; }
             }
           }
-          if (ok && leader) umma_commit(bar_tfull + 8 * acc);
+          if (ok && leader) commit(bar_tfull + 8 * acc);
         }
         AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 4);
       }
@@ -1116,7 +1165,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             }
           }
         }
-        if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601)) ok = false;
+        if (!(PAIR ? mbar_wait_bounded_cl(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601) : mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase, s_abort, p.gerr, 601))) ok = false;
         if (EW == 8 && sg.padded && p.tma_store && !p.direct_store) {
           // the TMA-stored steps below meet at named barriers: the four warps of a team take the decision to go on
           // together (every warp arrives here, its wait being bounded, and reads the flag after the barrier)
@@ -1193,7 +1242,10 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         AIG_STAMP(blockIdx.x == 0 && cnt < 12 && threadIdx.x == kPconvProducerWarps * 32, cnt * 8 + 6);
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(tempty_first + 8 * acc);
+          else mbar_arrive(bar_tempty + 8 * acc);
+        }
       }
       pos0 = pos_add(pos0, d_item);
     }
@@ -1205,9 +1257,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // neither CTA frees TMEM or exits while the other may still read it or arrive at its barriers
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -1335,6 +1389,7 @@ struct aig_conv_plan {
   const void* tmapP_ptr = nullptr;
   int pc_NT = 0, pc_MS = 0, pc_smem = 0, pc_grid = 1, pc_EW = 8;
   int* pc_sched = nullptr;                     // per-CTA item lists of the patch-resident launch (device), or null
+  bool pc_pair = false;                        // CTA pairs (clusters of two, tcgen05 cta_group::2): see pconv_kernel, PAIR
   bool pc_wres = false;
   int pc_in_h = 0, pc_in_w = 0, pc_in_c = 0;  // extents of the tensor the patch rows are read from
   bool pc_pdl = true;                          // launch with programmatic stream serialization (AIG_NO_PDL=1 turns it off)
@@ -1553,6 +1608,55 @@ int launch_pconv(aig_conv_plan* pl) {
   return AIG_OK;
 }
 
+// CTA-pair launch: clusters of two CTAs.
+int launch_pconv_pair256(aig_conv_plan* pl) {
+  static bool attr_set[64] = {};
+  aig_ctx* ctx = pl->ctx;
+  auto kern = pconv_kernel<256, 1, false, 8, true>;
+  if (!attr_set[ctx->device & 63]) {
+    AIG_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr_set[ctx->device & 63] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl->pc_grid);
+  cfg.blockDim = dim3(pconv_threads(8));
+  cfg.dynamicSmemBytes = (size_t)pl->pc_smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pl->pc_pdl ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  AIG_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, pl->tmapP, pl->tmapPT, pl->tmapBp, pl->tmapY[0], pl->tmapY[1], pl->pp));
+  return AIG_OK;
+}
+// Clusters of two CTAs of the pair kernel that can be resident at once with `smem` bytes of dynamic shared memory.
+int pconv_pair_max_clusters(aig_ctx* ctx, int smem) {
+  auto kern = pconv_kernel<256, 1, false, 8, true>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(ctx->sm_count & ~1));
+  cfg.blockDim = dim3(pconv_threads(8));
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
 template <int NT, int MS>
 int dispatch_pconv_w(aig_conv_plan* pl) {
 #ifdef AIG_TUNING
@@ -1562,6 +1666,7 @@ int dispatch_pconv_w(aig_conv_plan* pl) {
 }
 
 int dispatch_pconv(aig_conv_plan* pl) {
+  if (pl->pc_pair) return launch_pconv_pair256(pl);
   switch (pl->pc_NT * 10 + pl->pc_MS) {
     case 641: return dispatch_pconv_w<64, 1>(pl);
     case 642: return dispatch_pconv_w<64, 2>(pl);
@@ -1711,9 +1816,31 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   pl->pc_MS = best_ms;
   pl->pc_wres = best_res;
   pl->pc_smem = 1024 + q.patch_bufs * q.patch_bytes + q.w_stages * NT * 128 + pconv_tail(ew, NT == 64, pl->res_tiles);
+  // CTA pairs for the 256-wide streamed layers with flat inputs: every CTA keeps half of each weight block, so the
+  // same shared memory holds twice the stages
+  pl->pc_pair = false;
+  // (launches with a separate shortcut N tile keep the longest-first item table, launches with fewer M tiles than SMs
+  //  gain nothing from pairing: both measured)
+  bool want_pair = q.flat && !best_res && best_ms == 1 && NT == 256 && !q.dist_n && ew == 8 && q.n_tiles == 1 && q.m_tiles >= ctx->sm_count && !f_nt;
+#ifdef AIG_TUNING
+  if (const char* e = getenv("AIG_PCONV_PAIR_ALL")) if (atoi(e)) want_pair = q.flat && !best_res && best_ms == 1 && NT == 256 && !q.dist_n && ew == 8 && q.m_tiles >= 2;
+#endif
+  if (const char* e = getenv("AIG_PCONV_NO_PAIR")) if (atoi(e)) want_pair = false;
+  if (want_pair) {
+    long long stages = (pconv_budget(ew, false, pl->res_tiles) - (long long)q.patch_bufs * q.patch_bytes) / (NT * 64);
+    if (stages > 30) stages = 30;
+    const int smem = 1024 + q.patch_bufs * q.patch_bytes + (int)stages * NT * 64 + pconv_tail(ew, false, pl->res_tiles);
+    const int clusters = stages >= 4 ? pconv_pair_max_clusters(ctx, smem) : 0;
+    if (clusters >= 32) {
+      pl->pc_pair = true;
+      q.w_stages = (int)stages;
+      q.m_tiles = (q.m_tiles + 1) & ~1;  // whole pairs: the odd tile's partner runs on rows past the end (zero-filled, not stored)
+      pl->pc_smem = smem;
+    }
+  }
   // a launch with a main and a (sparse) shortcut N tile whose M tiles do not fill the SMs evenly: the (M tile,
   // N tile) pairs become the work items, assigned to the CTAs longest first
-  bool lpt = !q.dist_n && q.n_tiles == 2 && q.sparse_tile0 == 1 && q.m_tiles % ctx->sm_count != 0;
+  bool lpt = !pl->pc_pair && !q.dist_n && q.n_tiles == 2 && q.sparse_tile0 == 1 && q.m_tiles % ctx->sm_count != 0;
 #ifdef AIG_TUNING
   if (const char* e = getenv("AIG_PCONV_NODIST2")) if (atoi(e)) lpt = false;
 #endif
@@ -1722,6 +1849,13 @@ bool pconv_choose_tile(aig_ctx* ctx, aig_conv_plan* pl, const PconvNtOption* opt
   q.sched = nullptr;
   const long long items = (long long)q.m_tiles * ((q.dist_n || lpt) ? q.n_tiles : 1);
   pl->pc_grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
+  if (pl->pc_pair) {
+    // whole clusters, no more than can be resident at once (the CTAs of a pair wait for each other)
+    const int cap = 2 * pconv_pair_max_clusters(ctx, pl->pc_smem);
+    int g = q.m_tiles < (ctx->sm_count & ~1) ? q.m_tiles : (ctx->sm_count & ~1);
+    if (g > cap) g = cap;
+    pl->pc_grid = g;
+  }
   if (lpt) {
     q.dist_n = 2;
     const int G = pl->pc_grid;
@@ -1802,7 +1936,7 @@ int encode_Bp(aig_conv_plan* pl) {
   if (!enc) return aig_fail(pl->ctx, AIG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t dims[2] = {(cuuint64_t)pl->Ktot, (cuuint64_t)pl->Kpad};
   cuuint64_t strides[1] = {(cuuint64_t)pl->Ktot * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)pl->pc_NT};
+  cuuint32_t box[2] = {64u, (cuuint32_t)(pl->pc_pair ? pl->pc_NT / 2 : pl->pc_NT)};  // (a CTA of a pair loads its half of the rows)
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&pl->tmapBp, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pl->w_packed, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
