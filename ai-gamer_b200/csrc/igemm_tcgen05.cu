@@ -1019,6 +1019,8 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       bool ok = true;
       if (WRES) ok = mbar_wait_bounded(bar_wfull, 0, s_abort, p.gerr, 501);
       int it = 0, cnt = 0, stage = 0, buf = 0;
+      int acc = 0;            // accumulator buffer of the current (M tile, N tile) and its parity: advanced by hand, the
+      uint32_t acc_phase = 0; // loop of the issuing warp holds no division
       uint32_t wphase = 0, pph = 0;
       const int n_items = pconv_items(p);
       for (PconvItemIter itr = pconv_item_begin(p); itr.item < n_items && ok; pconv_item_next(p, itr), ++it) {
@@ -1028,8 +1030,6 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const long long q0 = (long long)m_tile * kM;
         const int off0 = p.flat ? 0 : (int)(q0 - (q0 / p.P) * p.P);  // (a flat patch starts at the tile's first position)
         for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
-          const int acc = cnt % p.acc_bufs;
-          const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
           if (!wait(bar_tempty + 8 * acc, acc_phase ^ 1u, 503)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * MS * NT);
@@ -1046,9 +1046,11 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             }
             const uint32_t patch = sPatch + buf * p.patch_bytes + (uint32_t)off0 * 128u;
             const uint32_t e1 = gs[g + 1];
+            uint32_t en_next = ent[gs[g]];  // (table entries are fetched one step ahead: the load's latency is off the issue path)
             for (uint32_t e = gs[g]; e < e1; ++e) {
               AIG_STAMP(blockIdx.x == 0 && leader && it == 2 && n_tile == n_lo && e - gs[0] < 32, 96 + (e - gs[0]));
-              const uint32_t en = ent[e];
+              const uint32_t en = en_next;
+              en_next = ent[e + 1];  // (one word past the last entry of the table is allocated)
               uint32_t b0;
               if (WRES) {
                 b0 = sW + (en >> 16) * kWBlock;
@@ -1082,6 +1084,7 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             }
           }
           if (ok && leader) commit(bar_tfull + 8 * acc);
+          if (++acc == p.acc_bufs) { acc = 0; acc_phase ^= 1u; }
         }
         AIG_STAMP(blockIdx.x == 0 && leader && it < 12, it * 8 + 4);
       }
@@ -1138,8 +1141,9 @@ pconv_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
       if (p.dist_n) pos0 = pos_of((long long)m_tile * kM + row_in_tile);
       for (int n_tile = n_lo; n_tile < n_hi && ok; ++n_tile, ++cnt) {
         if (EW == 16 && MS == 1 && (cnt & 1) != team) continue;  // the other team's tile
-        const int acc = cnt % p.acc_bufs;
-        const uint32_t acc_phase = (uint32_t)(cnt / p.acc_bufs) & 1u;
+        const int acc_shift = p.acc_bufs == 4 ? 2 : (p.acc_bufs == 2 ? 1 : 0);  // (1, 2 or 4 buffers)
+        const int acc = cnt & (p.acc_bufs - 1);
+        const uint32_t acc_phase = (uint32_t)(cnt >> acc_shift) & 1u;
         const int nb = n_tile * NT;
         const float* sc = staged ? s_scale + nb : p.scale + nb;
         const float* sf = staged ? s_shift + nb : p.shift + nb;
