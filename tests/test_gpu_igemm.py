@@ -356,7 +356,9 @@ def test_conv_output_in_space_to_depth_layout(env):
 
 
 @gpu
-@pytest.mark.parametrize("B,C,H,W,K", [(2, 32, 24, 32, 64), (3, 64, 18, 32, 128), (4, 128, 18, 32, 256), (5, 256, 9, 16, 256), (37, 64, 10, 12, 128)])
+@pytest.mark.parametrize("B,C,H,W,K", [(2, 32, 24, 32, 64), (3, 64, 18, 32, 128), (4, 128, 18, 32, 256), (5, 256, 9, 16, 256), (37, 64, 10, 12, 128),
+                                       (800, 64, 8, 8, 128),    # 157 M tiles: the down-sampling launch runs as CTA pairs, the odd tile's partner past the end
+                                       (1210, 128, 6, 6, 256)]) # 152 M tiles of a 256-channel 3x3 convolution: CTA pairs on the stride-1 side
 def test_padded_position_layout_between_down_sampling_and_conv1(env, B, C, H, W, K):
     """The fused down-sampling launch writes both outputs in the padded position layout (every image with one extra
     zero row and column) and the 3x3 convolution reads its input and its residual from it: the padding positions
