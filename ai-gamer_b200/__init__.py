@@ -45,6 +45,17 @@ SIGNATURES = {
     "aig_unconvert_unnormalize": [P, P, P, c_size_t],
     "aig_half_to_float": [P, P, P, c_size_t],
     "aig_resize_box": [P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int],
+    "aig_mse_loss2": [P, P, P, c_int, c_int, c_int, ctypes.POINTER(c_float), ctypes.POINTER(c_float)],
+    "aig_loss_gradient": [P, P, P, P, ctypes.c_longlong],
+    "aig_any_nan_half": [P, P, ctypes.c_longlong, ctypes.POINTER(c_int)],
+    "aig_swish_backward": [P, P, P, ctypes.c_longlong],
+    "aig_leaky_relu_backward": [P, P, P, ctypes.c_longlong, c_float],
+    "aig_sigmoid_backward": [P, P, P, c_int, c_int, ctypes.c_longlong],
+    "aig_bias_gradient": [P, P, P, c_int, c_int],
+    "aig_sgd_step_f16": [P, P, P, ctypes.c_longlong, c_float, c_float],
+    "aig_sgd_step_f32": [P, P, P, ctypes.c_longlong, c_float, c_float],
+    "aig_adamw_step_f32": [P, P, P, P, P, ctypes.c_longlong, c_float, c_int, c_float],
+    "aig_adamw_step_f16": [P, P, P, P, P, ctypes.c_longlong, c_float, c_int, c_float],
     "aig_process_output": [P, P, P, c_int],
     "aig_process_output_to": [P, P, P, P],
     "aig_float_to_half": [P, P, P, c_size_t],

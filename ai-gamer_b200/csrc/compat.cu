@@ -83,6 +83,44 @@ void HeInit(__half* weightHalf, int numWeights, float fanIn) {
 
 void LeakyReluForward(__half* data, int size, float negativeSlope) { note(aig_leaky_relu_forward(ctx(), (aig_half*)data, size, negativeSlope)); }
 void SwishForward(__half* data, int size) { note(aig_swish_forward(ctx(), (aig_half*)data, size)); }
+float MseLoss(const __half* dPredictions, const float* dTargets, int size) {
+  float loss = 0.f;
+  note(aig_mse_loss2(ctx(), (const aig_half*)dPredictions, dTargets, 1, 1, size, &loss, nullptr));
+  return loss;
+}
+void MseLoss2(const __half* dPredictions, const float* dTargets, int numButs, int numCtrls, int batchSize, float* butLoss, float* axesLoss) {
+  note(aig_mse_loss2(ctx(), (const aig_half*)dPredictions, dTargets, numButs, numCtrls, batchSize, butLoss, axesLoss));
+}
+void Gradient(__half* dGradient, const __half* dPredictions, const __half* dTargets, int size) {
+  note(aig_loss_gradient(ctx(), (aig_half*)dGradient, (const aig_half*)dPredictions, (const aig_half*)dTargets, size));
+}
+bool IsnanHalf(const __half* data, int size) {
+  int found = 0;
+  note(aig_any_nan_half(ctx(), (const aig_half*)data, size, &found));
+  return found != 0;
+}
+void LeakyReluBackward(__half* grad, const __half* data, int size, float negativeSlope) {
+  note(aig_leaky_relu_backward(ctx(), (aig_half*)grad, (const aig_half*)data, size, negativeSlope));
+}
+void SwishBackward(__half* grad, const __half* data, int size) { note(aig_swish_backward(ctx(), (aig_half*)grad, (const aig_half*)data, size)); }
+void SigmoidBackward(__half* grad, const __half* data, int numCtrls, int numButs, int size) {
+  note(aig_sigmoid_backward(ctx(), (aig_half*)grad, (const aig_half*)data, numCtrls, numButs, size));
+}
+void BiasGradient(const __half* gradInput, __half* gradBias, int c, int batchSize) {
+  note(aig_bias_gradient(ctx(), (const aig_half*)gradInput, (aig_half*)gradBias, c, batchSize));
+}
+void SGDHalf(__half* params, const __half* grads, int size, float learningRate, float weightDecay) {
+  note(aig_sgd_step_f16(ctx(), (aig_half*)params, (const aig_half*)grads, size, learningRate, weightDecay));
+}
+void SGDFloat(float* params, const float* grads, int size, float learningRate, float weightDecay) {
+  note(aig_sgd_step_f32(ctx(), params, grads, size, learningRate, weightDecay));
+}
+void AdamWFloat(float* params, const float* grads, float* m, float* v, float learningRate, int t, float weightDecay, int size) {
+  note(aig_adamw_step_f32(ctx(), params, grads, m, v, size, learningRate, t, weightDecay));
+}
+void AdamWHalf(__half* params, const __half* grads, __half* m, __half* v, float lr, int t, float weightDecay, int size) {
+  note(aig_adamw_step_f16(ctx(), (aig_half*)params, (const aig_half*)grads, (aig_half*)m, (aig_half*)v, size, lr, t, weightDecay));
+}
 void SigmoidForward(__half* data, int numCtrls, int numButs, int size) {
   note(aig_sigmoid_forward(ctx(), (aig_half*)data, numCtrls, numButs, size));
 }

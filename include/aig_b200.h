@@ -88,6 +88,34 @@ int aig_unconvert_unnormalize(aig_ctx* ctx, uint8_t* out, const aig_half* in, si
  * channels into every output channel (ConvScale.cpp:10,17-18); 0 keeps channels apart. */
 int aig_resize_box(aig_ctx* ctx, const uint8_t* src, int src_is_bgra, uint8_t* out_u8, aig_half* out_half, int frames,
                    int channels, int h, int w, int k, int cross_channel_sum);
+
+/* ---------------------------------------------------------------------------------------------
+ * Training step, the part outside the layers' own Backward (Train.cpp:60-109): losses, loss gradient, NaN check,
+ * activation backward passes, bias gradient and parameter updates (CudaStuff.cu:76-153, 194-252, 298-307, 372-459,
+ * 571-586).  Per element every kernel performs the arithmetic of the reference's kernel in the same types and
+ * order, so gradients, parameters and moments are bit-identical with it; the losses are reduced in a fixed order
+ * (the reference adds block sums with float atomics).  Convolution / GEMM / LSTM backward passes are not provided.
+ *   aig_mse_loss2        MseLoss2: mean squared error over the buttons (control index % n_ctrls < n_buttons) and over
+ *                        the mouse axes of a batch; host results; synchronises the context's stream
+ *   aig_loss_gradient    Gradient: prediction - target in half arithmetic
+ *   aig_any_nan_half     IsnanHalf: *found = 1 if any element is NaN; synchronises
+ *   aig_swish_backward   SwishBackward: from the layer's OUTPUT s, d = s + s/(1+s) * (1 - s)   (the reference's form)
+ *   aig_leaky_relu_backward, aig_sigmoid_backward: in place on the gradient, as the reference's kernels
+ *   aig_bias_gradient    per-channel sum of grad_in [batch][channels] over the batch in fp32 (the reference's kernel,
+ *                        CudaStuff.cu:372-394, reduces ACROSS channels after summing: a defect not reproduced)
+ *   aig_sgd_step_*       SGDHalf / SGDFloat: decoupled weight decay, gradient clipped to +-128
+ *   aig_adamw_step_*     AdamWFloat / AdamWHalf: beta1 0.9, beta2 0.999, eps 1e-7, clip 128, step count t from 1 */
+int aig_mse_loss2(aig_ctx* ctx, const aig_half* pred, const float* targets, int n_buttons, int n_ctrls, int batch, float* button_loss, float* axes_loss);
+int aig_loss_gradient(aig_ctx* ctx, aig_half* grad, const aig_half* pred, const aig_half* targets, long long n);
+int aig_any_nan_half(aig_ctx* ctx, const aig_half* data, long long n, int* found);
+int aig_swish_backward(aig_ctx* ctx, aig_half* grad, const aig_half* output, long long n);
+int aig_leaky_relu_backward(aig_ctx* ctx, aig_half* grad, const aig_half* input, long long n, float slope);
+int aig_sigmoid_backward(aig_ctx* ctx, aig_half* grad, const aig_half* output, int n_ctrls, int n_buttons, long long n);
+int aig_bias_gradient(aig_ctx* ctx, const aig_half* grad_in, aig_half* grad_bias, int channels, int batch);
+int aig_sgd_step_f16(aig_ctx* ctx, aig_half* params, const aig_half* grads, long long n, float lr, float weight_decay);
+int aig_sgd_step_f32(aig_ctx* ctx, float* params, const float* grads, long long n, float lr, float weight_decay);
+int aig_adamw_step_f32(aig_ctx* ctx, float* params, const float* grads, float* m, float* v, long long n, float lr, int t, float weight_decay);
+int aig_adamw_step_f16(aig_ctx* ctx, aig_half* params, const aig_half* grads, aig_half* m, aig_half* v, long long n, float lr, int t, float weight_decay);
 /* ConvertHalfToFloat / ConvertFloatToHalf (CudaStuff.cu:166-181). */
 int aig_half_to_float(aig_ctx* ctx, const aig_half* src, float* dst, size_t n);
 int aig_float_to_half(aig_ctx* ctx, const float* src, aig_half* dst, size_t n);

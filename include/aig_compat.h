@@ -34,6 +34,20 @@ void SpatialAttentionForward(const __half* inData, const __half* keyWeights, con
                              int inW);                                                 /* CudaStuff.cu:673-760 */
 cudaError_t ARGBtoRGB(unsigned char* src, unsigned char* dst, int n);                  /* CudaStuff.cu:52-62 */
 cudaError_t ARGBtoRGBplanar(unsigned char* src, unsigned char* dst, int n);            /* CudaStuff.cu:63-74 */
+/* training step (see aig_b200.h: losses, gradient, NaN check, activation backward, optimisers) */
+float MseLoss(const __half* dPredictions, const float* dTargets, int size);            /* CudaStuff.cu:97-105 */
+void MseLoss2(const __half* dPredictions, const float* dTargets, int numButs, int numCtrls, int batchSize, float* butLoss,
+              float* axesLoss);                                                        /* CudaStuff.cu:138-151 */
+void Gradient(__half* dGradient, const __half* dPredictions, const __half* dTargets, int size);   /* CudaStuff.cu:304-307 */
+bool IsnanHalf(const __half* data, int size);                                          /* CudaStuff.cu:576-583 */
+void LeakyReluBackward(__half* grad, const __half* data, int size, float negativeSlope);          /* CudaStuff.cu:412-415 */
+void SwishBackward(__half* grad, const __half* data, int size);                        /* CudaStuff.cu:433-436 */
+void SigmoidBackward(__half* grad, const __half* data, int numCtrls, int numButs, int size);      /* CudaStuff.cu:453-456 */
+void BiasGradient(const __half* gradInput, __half* gradBias, int c, int batchSize);    /* CudaStuff.cu:396-399 */
+void SGDHalf(__half* params, const __half* grads, int size, float learningRate, float weightDecay);           /* CudaStuff.cu:207-210 */
+void SGDFloat(float* params, const float* grads, int size, float learningRate, float weightDecay);            /* CudaStuff.cu:219-222 */
+void AdamWFloat(float* params, const float* grads, float* m, float* v, float learningRate, int t, float weightDecay, int size);   /* CudaStuff.cu:233-236 */
+void AdamWHalf(__half* params, const __half* grads, __half* m, __half* v, float lr, int t, float weightDecay, int size);          /* CudaStuff.cu:249-252 */
 
 /* Not in the reference: the context behind these wrappers (for mixing them with aig_* calls), the
  * status of the last wrapped call (AIG_OK or a negative code), and the pixel-group size that
