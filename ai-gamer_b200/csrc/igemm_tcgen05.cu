@@ -38,6 +38,7 @@ struct IgemmParams {
   int sd, sh, sw, pd, ph, pw;
   int DoHo, Ho, Wo;
   int tw, segs, segs_per_row, total_rows;
+  int rows_per_box;                           // consecutive output rows fetched by one TMA box (whole-row runs only; else 1)
   int m_super, n_tiles;                       // CTA tiles along M (MS sub-tiles each) and along N
   int out_c;
   int act, two_step;
@@ -102,6 +103,11 @@ __device__ __forceinline__ void res_tma_take(const ResTma& rt, int row, int c0, 
   for (int c = 0; c < 4; ++c)
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rown[c].x), "=r"(rown[c].y), "=r"(rown[c].z), "=r"(rown[c].w)
                  : "r"(src + (((uint32_t)c ^ swz) << 4)));
+  // The tile is overwritten next by the TMA unit (async proxy).  The reads above are ordinary loads whose data may
+  // still be on its way when this thread reaches the barrier (it does not wait for them, and under the MMAs' operand
+  // traffic a shared-memory load can take long): the proxy fence orders them before any later async-proxy access,
+  // the barrier extends that to the thread that requests the next tile.
+  fence_proxy_async_smem();
   named_bar_sync(rt.bar_id, 128);  // the team has read this tile
   if (rt.issuer) {
     const bool more = c0 + 32 < col_hi;
@@ -533,7 +539,8 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
             tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
           }
           const uint32_t a_dst = sA + stage * Cfg::kABytes;
-          for (int s = 0; s < nseg; ++s)
+          // one box per run of tw pixels, or per rows_per_box consecutive whole rows of one image plane
+          for (int s = 0; s < nseg; s += p.rows_per_box)
             if (leader)
               tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
                           seg_z[s] + fd, seg_n[s]);
@@ -1469,8 +1476,9 @@ int encode_A(aig_conv_plan* pl, const void* x) {
   cuuint64_t C = d.in_c, W = d.in_w, H = d.in_h, D = d.in_d, N = d.batch;
   cuuint64_t dims[5] = {C, W, H, D, N};
   cuuint64_t strides[4] = {C * 2, W * C * 2, H * W * C * 2, D * H * W * C * 2};
-  cuuint32_t box[5] = {(cuuint32_t)pl->BK, (cuuint32_t)(pl->prm.tw * d.sw), 1, 1, 1};
-  cuuint32_t estr[5] = {1, (cuuint32_t)d.sw, 1, 1, 1};
+  cuuint32_t box[5] = {(cuuint32_t)pl->BK, (cuuint32_t)(pl->prm.tw * d.sw), (cuuint32_t)(pl->prm.rows_per_box * d.sh), 1, 1};
+  cuuint32_t estr[5] = {1, (cuuint32_t)d.sw, (cuuint32_t)(pl->prm.rows_per_box > 1 ? d.sh : 1), 1, 1};
+  if (pl->prm.rows_per_box == 1) box[2] = 1;
   CUresult r = enc(&pl->tmapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(x), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(pl->BK), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1510,6 +1518,16 @@ int plan_finish(aig_ctx* ctx, aig_conv_plan* pl) {
   p.segs = kTileM / best_tw;
   p.segs_per_row = ceil_div(pl->Wo, best_tw);
   p.total_rows = d.batch * pl->Do * pl->Ho;
+  // Runs that are whole output rows: the rows of a sub-tile are consecutive rows of one image plane when the plane's
+  // height is a multiple of the group, so one TMA box (strided along H like along W) fetches the group.  The
+  // streamed kernel is bound by the number of its TMA operations on small images, not by their bytes.
+  p.rows_per_box = 1;
+  if (p.segs_per_row == 1 && best_tw == pl->Wo)
+    for (int r = 8; r >= 2; r /= 2)
+      if (p.segs % r == 0 && pl->Ho % r == 0 && r * d.sh <= 256) {
+        p.rows_per_box = r;
+        break;
+      }
   const long long total_segs = (long long)p.total_rows * p.segs_per_row;
   const int m_tiles = (int)ceil_div_ll(total_segs, p.segs);
   // few M tiles (small spatial extents): split N so that more SMs stream the weights in parallel

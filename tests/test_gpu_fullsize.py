@@ -80,6 +80,29 @@ def test_frame_encoder_all_256_frames_against_the_oracle(env):
 
 
 @gpu
+def test_frame_encoder_same_bits_on_every_run(env):
+    """200 forwards of the 256-frame batch give the same bits every time.  (A hand-over of a shared-memory tile from
+    ordinary loads to the TMA unit without a proxy fence once changed single frames in about one run in ten.)"""
+    U = env
+    c, pk = U.ctx(), U.pkg()
+    B, H, W = 256, 144, 256
+    params = PL.make_cnn_params(4, widths=WIDTHS, trivial=False)
+    d_frames = U.dev(PL.make_frames(11, B, H, W))
+    enc = pk.CnnEncoder(c, B, H, W, widths=WIDTHS)
+    enc.load_bytes(PL.serialize_cnn_checkpoint(params, W, H))
+    enc.forward(d_frames)
+    c.sync()
+    first = U.host(enc.outputs_f32()).copy()
+    differing = 0
+    for _ in range(200):
+        enc.forward(d_frames)
+        c.sync()
+        differing += 0 if np.array_equal(U.host(enc.outputs_f32()), first) else 1
+    enc.close()
+    assert differing == 0, "%d of 200 runs differ from the first" % differing
+
+
+@gpu
 def test_clip_encoder_full_size(env):
     """Temporal encoder at its configuration: 16 clips of 8 x 144 x 256 (ConvLayer3D.cpp:106-111 three times,
     channels 3 -> 32 -> 64 -> 128); the oracle on the first and the last clip."""
