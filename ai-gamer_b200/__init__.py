@@ -56,6 +56,11 @@ SIGNATURES = {
     "aig_sgd_step_f32": [P, P, P, ctypes.c_longlong, c_float, c_float],
     "aig_adamw_step_f32": [P, P, P, P, P, ctypes.c_longlong, c_float, c_int, c_float],
     "aig_adamw_step_f16": [P, P, P, P, P, ctypes.c_longlong, c_float, c_int, c_float],
+    "aig_fc_backward_plan_create": [P, c_int, c_int, c_int, P],
+    "aig_fc_backward": [P, P, P, P, P, P, P],
+    "aig_fc_backward_plan_destroy": [P],
+    "aig_fc_backward_weight_storage": [P],
+    "aig_fc_adamw_update": [P, P, c_int, c_int, P, P, P, P, P, P, P, P, c_float, c_int, c_float],
     "aig_process_output": [P, P, P, c_int],
     "aig_process_output_to": [P, P, P, P],
     "aig_float_to_half": [P, P, P, c_size_t],
@@ -209,6 +214,8 @@ SIGNATURES.update({
     "aig_layers_last_error": [],
     "aig_layer_create": [P, ctypes.c_char_p, PI, c_int, PP],
     "aig_layer_forward": [P, P, PP],
+    "aig_layer_backward": [P, P, PP],
+    "aig_layer_update": [P, c_float],
     "aig_layer_load_file": [P, ctypes.c_char_p],
     "aig_layer_save_file": [P, ctypes.c_char_p],
     "aig_layer_param_bytes": [P],
@@ -242,7 +249,7 @@ SIGNATURES.update({
     "aig_c3d_outputs_f32": [P],
     "aig_c3d_features": [P],
 })
-_RESTYPES = {"aig_compat_context": c_void_p, "aig_recording_last_error": ctypes.c_char_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_conv_padded_rows": ctypes.c_longlong, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
+_RESTYPES = {"aig_compat_context": c_void_p, "aig_fc_backward_weight_storage": c_void_p, "aig_recording_last_error": ctypes.c_char_p, "aig_layer_param_bytes": c_size_t, "aig_s2d_elems": c_size_t, "aig_conv_padded_rows": ctypes.c_longlong, "aig_c3d_last_error": ctypes.c_char_p, "aig_c3d_param_bytes": c_size_t, "aig_c3d_outputs_f32": c_void_p,
              "aig_c3d_features": c_void_p, "aig_ctx_stream": c_void_p, "aig_last_error": ctypes.c_char_p, "aig_cnn_last_error": ctypes.c_char_p,
              "aig_cnn_checkpoint_bytes": c_size_t, "aig_cnn_outputs_half": c_void_p, "aig_cnn_outputs_f32": c_void_p,
              "aig_cnn_features": c_void_p, "aig_cnn_stage_output": c_void_p, "aig_cnn_site_name": ctypes.c_char_p,
@@ -439,6 +446,18 @@ class FcPlan(_Plan):
     def forward(self, x, y, residual=None):
         self.check(lib().aig_conv_forward(self.handle, ptr(x), ptr(residual), ptr(y)))
         return y
+
+
+class FcBackwardPlan(_Plan):
+    """aig_fc_backward_*: weight, bias and input gradients of a fully connected layer (FCLayer.cpp:54-59)."""
+    _destroy = "aig_fc_backward_plan_destroy"
+
+    def __init__(self, ctx, batch, in_c, out_c):
+        super().__init__(ctx)
+        self.check(lib().aig_fc_backward_plan_create(ctx.handle, batch, in_c, out_c, ctypes.byref(self.handle)))
+
+    def backward(self, x, grad, w_in_out, grad_w=None, grad_b=None, grad_x=None):
+        self.check(lib().aig_fc_backward(self.handle, ptr(x), ptr(grad), ptr(w_in_out), ptr(grad_w), ptr(grad_b), ptr(grad_x)))
 
 
 class Conv0Plan(_Plan):

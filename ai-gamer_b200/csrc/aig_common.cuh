@@ -28,6 +28,13 @@ struct aig_graph {
 
 int aig_fail(aig_ctx* ctx, int code, const char* fmt, ...);
 
+// FC plans whose weight operand is produced inside the library (igemm_tcgen05.cu): the K-major buffer
+// [out_c][in_c] to write in place, the epilogue's fp32 shift [out_c] (the bias), and the identity epilogue folded once.
+struct aig_conv_plan;
+__half* fc_plan_weight_buffer(aig_conv_plan* plan);
+float* fc_plan_shift_buffer(aig_conv_plan* plan);
+int fc_plan_identity_affine(aig_conv_plan* plan);
+
 #define AIG_CUDA_OK(ctx, expr)                                                             \
   do {                                                                                     \
     cudaError_t e__ = (expr);                                                              \

@@ -2279,6 +2279,19 @@ int aig_fc_plan_set_weights_out_in(aig_conv_plan* pl, const aig_half* w_out_in, 
   return set_affine(pl, bias, nullptr, nullptr, nullptr, nullptr, 0.f);
 }
 
+// Library-internal (C++ linkage, declared in aig_common.cuh): producers inside the library that write an FC plan's
+// K-major weight operand [out_c][in_c] in place, once the identity epilogue (scale 1, shift 0) has been folded, and
+// the fp32 per-column shift (= the bias of a plain FC layer) of a plan whose weights were set.
+extern "C++" {
+__half* fc_plan_weight_buffer(aig_conv_plan* pl) { return pl && pl->is_fc ? pl->w_packed : nullptr; }
+float* fc_plan_shift_buffer(aig_conv_plan* pl) { return pl && pl->is_fc && pl->weights_set ? pl->shift : nullptr; }
+int fc_plan_identity_affine(aig_conv_plan* pl) {
+  if (!pl || !pl->is_fc) return AIG_ERR_INVALID;
+  DeviceGuard g(pl->ctx->device);
+  return set_affine(pl, nullptr, nullptr, nullptr, nullptr, nullptr, 0.f);
+}
+}  // extern "C++"
+
 // ---- fused down-sampling pair and space-to-depth plumbing ---------------------------------
 static inline int s2d_extent(int v) { return (v - 2) / 2 + 2; }  // blocks along an axis of v pixels
 

@@ -256,8 +256,8 @@ __half* Sigmoid::Forward(__half* data) {
 
 // ------------------------------------------------------------------------------------------ FCLayer
 FCLayer::FCLayer(cudnnHandle_t cudnnHandle, cublasHandle_t, int batchSize, int inputSize, int outputSize, const char* layerName,
-                 bool train, float)
-    : batchSize_(batchSize), inC_(inputSize), outC_(outputSize), ctx_(cudnnHandle) {
+                 bool train, float weightDecay)
+    : weightDecay_(weightDecay), batchSize_(batchSize), inC_(inputSize), outC_(outputSize), ctx_(cudnnHandle) {
   g_default_ctx = ctx_;
   layerName_ = layerName;
   train_ = train;
@@ -265,21 +265,66 @@ FCLayer::FCLayer(cudnnHandle_t cudnnHandle, cublasHandle_t, int batchSize, int i
   outDesc_ = {batchSize_, outC_, 1, 1};
   weightCount_ = (size_t)inC_ * outC_;
   check(ctx_, aig_fc_plan_create(ctx_, batchSize_, inC_, outC_, AIG_ACT_NONE, 0.f, /*two_step*/ 1, &plan_), layerName);
-  mallocZero(&weights_, weightCount_);
+  if (train_) {
+    check(ctx_, aig_fc_backward_plan_create(ctx_, batchSize_, inC_, outC_, &backward_), layerName);
+    // the master weights live in the input-gradient GEMM's operand where its layout is the reference's (no copy per step)
+    weights_ = reinterpret_cast<__half*>(aig_fc_backward_weight_storage(backward_));
+    weightsInPlan_ = weights_ != nullptr;
+  }
+  if (!weightsInPlan_) mallocZero(&weights_, weightCount_);
   mallocZero(&bias_, (size_t)outC_);
   mallocZero(&outData_, (size_t)outNCHW_);
+  if (train_) {
+    mallocZero(&gradWeights_, weightCount_);
+    mallocZero(&gradBias_, (size_t)outC_);
+    mallocZero(&gradOut_, (size_t)batchSize_ * inC_);
+    mallocZero(&m_Weights_, weightCount_);
+    mallocZero(&v_Weights_, weightCount_);
+    mallocZero(&m_Bias_, (size_t)outC_);
+    mallocZero(&v_Bias_, (size_t)outC_);
+  }
   SyncWeights();
 }
 FCLayer::~FCLayer() {
   aig_conv_plan_destroy(plan_);
-  cudaFree(weights_); cudaFree(bias_); cudaFree(outData_);
+  if (!weightsInPlan_) cudaFree(weights_);
+  aig_fc_backward_plan_destroy(backward_);
+  cudaFree(bias_); cudaFree(outData_);
+  cudaFree(gradWeights_); cudaFree(gradBias_); cudaFree(gradOut_);
+  cudaFree(m_Weights_); cudaFree(v_Weights_); cudaFree(m_Bias_); cudaFree(v_Bias_);
 }
 void FCLayer::SyncWeights() {
   check(ctx_, aig_fc_plan_set_weights(plan_, H(weights_), H(bias_), nullptr, nullptr, nullptr, nullptr, 0.f), layerName_);
 }
 __half* FCLayer::Forward(__half* data) {
+  inData_ = data;
   check(ctx_, aig_conv_forward(plan_, H(data), nullptr, H(outData_)), layerName_);
   return outData_;
+}
+__half* FCLayer::Backward(__half* grad) {
+  if (!backward_ || !inData_) throw std::runtime_error(std::string(layerName_) + ": Backward needs train = true and a Forward before it");
+  check(ctx_, aig_fc_backward(backward_, H(inData_), H(grad), H(weights_), H(gradWeights_), H(gradBias_), H(gradOut_)), layerName_);
+  return gradOut_;
+}
+void FCLayer::UpdateParameters(float learningRate) {
+  if (!backward_) throw std::runtime_error(std::string(layerName_) + ": UpdateParameters needs train = true");
+  check(ctx_, aig_fc_adamw_update(ctx_, plan_, inC_, outC_, H(weights_), H(gradWeights_), H(m_Weights_), H(v_Weights_), H(bias_), H(gradBias_),
+                                  H(m_Bias_), H(v_Bias_), learningRate, t_, weightDecay_), layerName_);
+  ++t_;
+}
+void FCLayer::SaveOptimizerState(std::ofstream& file, unsigned char* buffer) {
+  if (!backward_) return;
+  saveArray(ctx_, file, buffer, m_Weights_, weightCount_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, v_Weights_, weightCount_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, m_Bias_, outC_ * sizeof(__half));
+  saveArray(ctx_, file, buffer, v_Bias_, outC_ * sizeof(__half));
+}
+void FCLayer::LoadOptimizerState(std::ifstream& file, unsigned char* buffer) {
+  if (!backward_) return;
+  loadArray(file, buffer, m_Weights_, weightCount_ * sizeof(__half));
+  loadArray(file, buffer, v_Weights_, weightCount_ * sizeof(__half));
+  loadArray(file, buffer, m_Bias_, outC_ * sizeof(__half));
+  loadArray(file, buffer, v_Bias_, outC_ * sizeof(__half));
 }
 void FCLayer::LoadParameters(std::ifstream& file, unsigned char* buffer) {
   loadArray(file, buffer, weights_, weightCount_ * sizeof(__half));
@@ -635,6 +680,7 @@ int aig_layer_create(aig_ctx* ctx, const char* kind, const int* a, int n, void**
     else if (k == "LeakyReLU") { need(1); L = new LeakyReLU(a[0], "LeakyReLU"); }
     else if (k == "Sigmoid") { need(3); L = new Sigmoid(a[0], a[1], a[2], "Sigmoid"); }
     else if (k == "FCLayer") { need(3); L = new FCLayer(ctx, ctx, a[0], a[1], a[2], "FCLayer", false, wd); }
+    else if (k == "FCLayerTrain") { need(3); L = new FCLayer(ctx, ctx, a[0], a[1], a[2], "FCLayer", true, wd); }
     else if (k == "ResConvLayer") { need(5); int h = a[3], w = a[4]; L = new ResConvLayer(ctx, a[0], a[1], a[2], &h, &w, "ResConvLayer", false); }
     else if (k == "LayerNorm") { need(4); L = new LayerNorm(a[0], a[1], a[2], a[3], "LayerNorm", wd); }
     else if (k == "SpatialAttentionLayer") { need(5); L = new SpatialAttentionLayer(ctx, a[0], a[1], a[2], a[3], a[4], "SpatialAttention", false, wd); }
@@ -655,6 +701,28 @@ int aig_layer_forward(void* layer, aig_half* x, const aig_half** out_dev) {
   if (!layer || !x || !out_dev) return AIG_ERR_INVALID;
   try {
     *out_dev = reinterpret_cast<const aig_half*>(static_cast<Layer*>(layer)->Forward(reinterpret_cast<__half*>(x)));
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_CUDA;
+  }
+}
+// Layer::Backward / Layer::UpdateParameters (Layer.h:8-9); of the classes here FCLayer created as "FCLayerTrain"
+// implements them, the others return a null gradient as the base class does
+int aig_layer_backward(void* layer, aig_half* grad, const aig_half** grad_in_dev) {
+  if (!layer || !grad || !grad_in_dev) return AIG_ERR_INVALID;
+  try {
+    *grad_in_dev = reinterpret_cast<const aig_half*>(static_cast<Layer*>(layer)->Backward(reinterpret_cast<__half*>(grad)));
+    return AIG_OK;
+  } catch (const std::exception& e) {
+    g_layers_error = e.what();
+    return AIG_ERR_CUDA;
+  }
+}
+int aig_layer_update(void* layer, float learning_rate) {
+  if (!layer) return AIG_ERR_INVALID;
+  try {
+    static_cast<Layer*>(layer)->UpdateParameters(learning_rate);
     return AIG_OK;
   } catch (const std::exception& e) {
     g_layers_error = e.what();

@@ -151,13 +151,27 @@ class FCLayer final : public Layer {
   void LoadParameters(std::ifstream& file, unsigned char* buffer) override;
   void SaveParameters(std::ofstream& file, unsigned char* buffer) override;
   size_t GetParameterSize() override { return (weightCount_ + outC_) * sizeof(__half); }
+  // training mode (train = true in the constructor), FCLayer.cpp:54-70 and :83-104: Backward returns the gradient
+  // with respect to the last Forward's input; UpdateParameters is the AdamW step on weights and bias
+  __half* Backward(__half* grad) override;
+  void UpdateParameters(float learningRate) override;
+  void SaveOptimizerState(std::ofstream& file, unsigned char* buffer) override;
+  void LoadOptimizerState(std::ifstream& file, unsigned char* buffer) override;
+  size_t GetOptimizerStateSize() override { return weightCount_ * sizeof(__half); }
   void SyncWeights();
   __half *weights_ = nullptr, *bias_ = nullptr, *outData_ = nullptr;
+  __half *gradOut_ = nullptr, *gradWeights_ = nullptr, *gradBias_ = nullptr;
+  __half *m_Weights_ = nullptr, *v_Weights_ = nullptr, *m_Bias_ = nullptr, *v_Bias_ = nullptr;
+  const __half* inData_ = nullptr;
+  int t_ = 1;
+  float weightDecay_;
   int batchSize_, inC_, outC_;
 
  private:
   aig_ctx* ctx_;
   aig_conv_plan* plan_ = nullptr;
+  aig_fc_backward_plan* backward_ = nullptr;
+  bool weightsInPlan_ = false;
 };
 
 // ResConvLayer.h:12 / ResConvLayer.cpp:8-37

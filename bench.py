@@ -625,6 +625,77 @@ def reference_call_pattern(env):
                     "46 library launches per step, planar fp16 input already on the device, no head", "layers": layers}
 
 
+def fc_training_round(env):
+    """One Forward / Backward / UpdateParameters round of FCLayer in training mode (FCLayer.cpp:48-70) on the
+    reference's own CPU-runnable shape, 64 x 1024 -> 1024: this library's class (`aig_layer_*` hooks, kind
+    "FCLayerTrain": tcgen05 GEMMs for the three products, AdamW on fp16 parameters) and, where it was built, the
+    reference's class on cuBLAS beside it.  The 2 MB of weights live in L2 in both; the round is launch-bound."""
+    import ctypes
+
+    torch, lib, ctx = env.torch, env.pkg.lib(), env.ctx
+    B, I, N, steps = 64, 1024, 1024, 200
+    P = ctypes.c_void_p
+    arr = (ctypes.c_int * 3)(B, I, N)
+    gen = torch.Generator("cuda").manual_seed(5)
+    xs = [torch.randn((B, I), device="cuda", generator=gen).half() for _ in range(4)]
+    gs = [(0.1 * torch.randn((B, N), device="cuda", generator=gen)).half() for _ in range(4)]
+    torch.cuda.synchronize()
+    layer = P()
+    env.ctx.check(lib.aig_layer_create(ctx.handle, b"FCLayerTrain", arr, 3, ctypes.byref(layer)))
+    out, gx = P(), P()
+
+    def ours(i):
+        lib.aig_layer_forward(layer, P(xs[i % 4].data_ptr()), ctypes.byref(out))
+        lib.aig_layer_backward(layer, P(gs[i % 4].data_ptr()), ctypes.byref(gx))
+        env.ctx.check(lib.aig_layer_update(layer, 1e-3))
+
+    res = env.timer.regions(ours, steps, 10)
+    lib.aig_layer_destroy(layer)
+    flop = 3 * 2.0 * B * I * N
+    block = {"shape": "batch %d, %d -> %d" % (B, I, N), "value": 1.0 / (res["ms_per_step"] * 1e-3), "unit": "rounds/s", "us_per_round": res["ms_per_step"] * 1e3,
+             "repeats": res["repeats"], "steps": steps, "tflops": flop / (res["ms_per_step"] * 1e-3) / 1e12}
+    path = os.path.join(ROOT, "oracle", "_ref", "libaig_reflayers.so")
+    if not os.path.exists(path):
+        block["reference_class"] = {"unavailable": "oracle/_ref/libaig_reflayers.so was not built (reference tree absent at build time)"}
+        return block
+    ref = ctypes.CDLL(path)
+    ref.ref_layer_create.restype, ref.ref_layer_create.argtypes = P, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    ref.ref_layer_forward.restype, ref.ref_layer_forward.argtypes = P, [P, P]
+    ref.ref_fc_backward.restype, ref.ref_fc_backward.argtypes = P, [P, P, P, P]
+    ref.ref_layer_update.argtypes = [P, ctypes.c_float]
+    ref.ref_layer_destroy.argtypes = [P]
+    ref.ref_last_error.restype = ctypes.c_char_p
+    torch.cuda.synchronize()
+    rl = ref.ref_layer_create(b"FCLayerTrain", arr, 3) if ref.ref_init() == 0 else None
+    if not rl:
+        block["reference_class"] = {"unavailable": ref.ref_last_error().decode()}
+        return block
+    legacy = torch.cuda.default_stream()
+
+    def theirs(i):
+        ref.ref_layer_forward(rl, P(xs[i % 4].data_ptr()))
+        ref.ref_fc_backward(rl, P(gs[i % 4].data_ptr()), None, None)
+        ref.ref_layer_update(rl, 1e-3)
+
+    for i in range(10):
+        theirs(i)
+    torch.cuda.synchronize()
+    times = []
+    for r in range(25):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(legacy)
+        for i in range(steps):
+            theirs(i)
+        e1.record(legacy)
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / steps)
+    ref.ref_layer_destroy(rl)
+    ms = float(np.median(times))
+    block["reference_class"] = {"value": 1.0 / (ms * 1e-3), "unit": "rounds/s", "us_per_round": ms * 1e3,
+                                "what": "the reference's FCLayer (cublasGemmEx x3, cudnnAddTensor, BiasGradient, AdamWHalf x2) on the legacy default stream"}
+    return block
+
+
 def leg_agent_stream(env, full):
     """Profiler captures only: the batch-1 streaming agent on device-resident frames (encoder graph, bridge FC, the
     one-kernel sequence-head step); the timed form of this workload is the `latency` block."""
@@ -701,6 +772,7 @@ def main():
         line["workloads"] = extra
         if env.world == 1 and wl == "cnn2d" and args.legs == "all":
             line["reference_call_pattern"] = reference_call_pattern(env)
+            line["fc_training_round"] = fc_training_round(env)
         if not args.no_cpu_baseline and env.world == 1:
             line["cpu_baseline"] = cpu_baseline_block(wl, 5 if wl == "cnn2d" else 3)
             for w in extra:

@@ -94,7 +94,8 @@ int aig_resize_box(aig_ctx* ctx, const uint8_t* src, int src_is_bgra, uint8_t* o
  * activation backward passes, bias gradient and parameter updates (CudaStuff.cu:76-153, 194-252, 298-307, 372-459,
  * 571-586).  Per element every kernel performs the arithmetic of the reference's kernel in the same types and
  * order, so gradients, parameters and moments are bit-identical with it; the losses are reduced in a fixed order
- * (the reference adds block sums with float atomics).  Convolution / GEMM / LSTM backward passes are not provided.
+ * (the reference adds block sums with float atomics).  Of the layers' own Backward passes the fully connected one is
+ * provided (aig_fc_backward, declared with the FC plans below); convolution, normalisation and LSTM backward passes are not.
  *   aig_mse_loss2        MseLoss2: mean squared error over the buttons (control index % n_ctrls < n_buttons) and over
  *                        the mouse axes of a batch; host results; synchronises the context's stream
  *   aig_loss_gradient    Gradient: prediction - target in half arithmetic
@@ -243,6 +244,29 @@ int aig_fc_plan_set_output_f32(aig_conv_plan* plan, int enable);
 /* Add a second bias vector (cuDNN's LSTM keeps separate input and recurrent biases,
  * LSTMLayer.cpp:9-40 default bias mode); call after the set_weights function. */
 int aig_fc_plan_add_bias(aig_conv_plan* plan, const aig_half* bias2);
+
+/* FCLayer::Backward (FCLayer.cpp:54-59): from the layer's input x [batch][in_c], the incoming gradient grad
+ * [batch][out_c] and the weights w_in_out [in_c][out_c] (the reference's layout),
+ *   grad_w [in_c][out_c] = x^T . grad,   grad_b [out_c] = aig_bias_gradient(grad),   grad_x [batch][in_c] = grad . W^T,
+ * each product accumulated in fp32 on the tensor cores and rounded to fp16 once, like the reference's two
+ * cublasGemmEx calls (CUDA_R_32F compute).  Any of the three outputs may be null (then x or w_in_out may be too).
+ * The plan holds two GEMM plans and the transposed / zero-padded operand copies; nothing is allocated per call. */
+typedef struct aig_fc_backward_plan aig_fc_backward_plan;
+int aig_fc_backward_plan_create(aig_ctx* ctx, int batch, int in_c, int out_c, aig_fc_backward_plan** out);
+int aig_fc_backward(aig_fc_backward_plan* plan, const aig_half* x, const aig_half* grad, const aig_half* w_in_out, aig_half* grad_w,
+                    aig_half* grad_b, aig_half* grad_x);
+int aig_fc_backward_plan_destroy(aig_fc_backward_plan* plan);
+/* Device storage for [in_c][out_c] weights inside the plan (the input-gradient GEMM's own operand), or null when
+ * out_c is not a multiple of 16: a caller that keeps its master weights there and passes this pointer as w_in_out
+ * saves aig_fc_backward its copy of the weights.  Owned by the plan. */
+aig_half* aig_fc_backward_weight_storage(aig_fc_backward_plan* plan);
+/* FCLayer::UpdateParameters, AdamW branch (FCLayer.cpp:60-65): AdamWHalf on weights [in_c][out_c] and bias [out_c]
+ * (element for element the arithmetic of aig_adamw_step_f16) in two launches that also refresh what `forward_plan`
+ * (an aig_fc_plan_create plan of the same layer whose weights were set once) reads -- its K-major weight operand
+ * and its fp32 bias -- so no aig_fc_plan_set_weights call is needed after the step.  t counts steps from 1. */
+int aig_fc_adamw_update(aig_ctx* ctx, aig_conv_plan* forward_plan, int in_c, int out_c, aig_half* weights, const aig_half* grad_w,
+                        aig_half* m_w, aig_half* v_w, aig_half* bias, const aig_half* grad_b, aig_half* m_b, aig_half* v_b, float lr, int t,
+                        float weight_decay);
 
 /* First-layer convolutions (3 input channels), CUDA-core/tensor kernels with the input conversion
  * fused into the load.

@@ -197,9 +197,14 @@ const char* aig_layers_last_error(void);
  * arguments in declaration order (sizes that the reference passes as int* go by value).
  * forward = Layer::Forward (Layer.h:7); load/save = Layer::LoadParameters / SaveParameters (Layer.h:10-11) on a
  * file that holds exactly the layer's payload; param_bytes = GetParameterSize() (the staging size, Layer.h:14);
- * out_count = outNCHW_ (Layer.h:18). */
+ * out_count = outNCHW_ (Layer.h:18).
+ * backward = Layer::Backward (Layer.h:8) and update = Layer::UpdateParameters (Layer.h:9): implemented by the kind
+ * "FCLayerTrain" (FCLayer with train = true: FCLayer.cpp:54-70, gradients of the last forward's input, then the AdamW
+ * step on weights and bias); the other kinds hand back a null gradient like the base class. */
 int aig_layer_create(aig_ctx* ctx, const char* kind, const int* iargs, int n_iargs, void** out);
 int aig_layer_forward(void* layer, aig_half* x_dev, const aig_half** out_dev);
+int aig_layer_backward(void* layer, aig_half* grad_dev, const aig_half** grad_in_dev);
+int aig_layer_update(void* layer, float learning_rate);
 int aig_layer_load_file(void* layer, const char* path);
 int aig_layer_save_file(void* layer, const char* path);
 size_t aig_layer_param_bytes(void* layer);

@@ -251,6 +251,34 @@ void orc_fc(const f16* x, const f16* W, const f16* bias, f16* y, int B, int inC,
   }
 }
 
+// FCLayer::Backward (FCLayer.cpp:54-59): two cublasGemmEx calls with fp32 compute and fp16 results, and the bias
+// gradient.  gw[i][o] = h(sum_b x[b][i] * g[b][o]);  gx[b][i] = h(sum_o g[b][o] * W[i][o]);  gb[o] = h(sum_b g[b][o])
+// (the per-channel sum the reference's BiasGradient forms in fp32 before its cross-channel reduction, which is a
+// defect and not restated).  Double accumulation for the products, fp32 in batch order for the bias sum.
+void orc_fc_backward(const f16* x, const f16* g, const f16* W, f16* gw, f16* gb, f16* gx, int B, int inC, int outC) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < inC; ++i) {
+    std::vector<double> acc(outC, 0.0);
+    for (int b = 0; b < B; ++b) {
+      const double xv = h2f(x[(size_t)b * inC + i]);
+      for (int o = 0; o < outC; ++o) acc[o] += xv * (double)h2f(g[(size_t)b * outC + o]);
+    }
+    for (int o = 0; o < outC; ++o) gw[(size_t)i * outC + o] = d2h(acc[o]);
+  }
+  for (int o = 0; o < outC; ++o) {
+    float s = 0.f;
+    for (int b = 0; b < B; ++b) s += h2f(g[(size_t)b * outC + o]);
+    gb[o] = f2h(s);
+  }
+#pragma omp parallel for schedule(static)
+  for (int b = 0; b < B; ++b)
+    for (int i = 0; i < inC; ++i) {
+      double acc = 0.0;
+      for (int o = 0; o < outC; ++o) acc += (double)h2f(g[(size_t)b * outC + o]) * (double)h2f(W[(size_t)i * outC + o]);
+      gx[(size_t)b * inC + i] = d2h(acc);
+    }
+}
+
 // "LayerNorm", reference axis.  CudaStuff.cu:457-515 + LayerNorm.cpp:36-40: statistics per channel
 // c over all n < N and i < HW (population variance), written to mean[C], variance[C];
 // y = h((x - mean_c) / sqrtf(var_c + eps) * gamma_c + beta_c) in fp32 (eps 1e-7 in the reference).

@@ -228,6 +228,18 @@ def fc(x, W, b):
     return y
 
 
+def fc_backward(x, g, W):
+    """FCLayer.cpp:54-59.  x [B][in], g [B][out], W [in][out] -> (grad_w [in][out], grad_b [out], grad_x [B][in])."""
+    x, g, W = _h(x), _h(g), _h(W)
+    B, inC = x.shape
+    outC = W.shape[1]
+    gw = np.empty((inC, outC), np.float16)
+    gb = np.empty(outC, np.float16)
+    gx = np.empty((B, inC), np.float16)
+    lib().orc_fc_backward(_p(x), _p(g), _p(W), _p(gw), _p(gb), _p(gx), _c_int(B), _c_int(inC), _c_int(outC))
+    return gw, gb, gx
+
+
 # ------------------------------------------------------------------ norms / attention / pools
 def layernorm_ref(x, gamma, beta, N, C, HW, eps=1e-7):
     """CudaStuff.cu:457-515 (per channel over N*HW).  Returns (y, mean[C], var[C])."""

@@ -1,6 +1,6 @@
 // ref_layers_hooks.cpp -- C hooks around the REFERENCE'S OWN layer classes (ConvLayer, BatchNorm, Activate,
-// FCLayer, ResConvLayer, ConvLayer3D, LSTMLayer of LSTMLayerv8.cpp, LayerNorm, SpatialAttentionLayer, Swish,
-// LeakyReLU, Sigmoid, NN), compiled from where they lie into oracle/_ref/libaig_reflayers.so together with the
+// FCLayer (forward, and Backward / UpdateParameters in training mode), ResConvLayer, ConvLayer3D, LSTMLayer of
+// LSTMLayerv8.cpp, LayerNorm, SpatialAttentionLayer, Swish, LeakyReLU, Sigmoid, NN), compiled from where they lie into oracle/_ref/libaig_reflayers.so together with the
 // reference's CudaStuff.cu.  TEST INFRASTRUCTURE ONLY: GPU parity tests run these classes (which call cuDNN and
 // cuBLAS exactly as the reference does) beside this repository's kernels on the same inputs, and the benchmark
 // times them as "the reference's call pattern on this GPU".  Nothing here is linked into libaig_b200.so.
@@ -110,6 +110,7 @@ void* ref_layer_create(const char* kind, const int* a, int n) {
     else if (k == "LeakyReLU") { need(1); L = new LeakyReLU(a[0], "LeakyReLU"); }
     else if (k == "Sigmoid") { need(3); L = new Sigmoid(a[0], a[1], a[2], "Sigmoid"); }
     else if (k == "FCLayer") { need(3); L = new FCLayer(g_cudnn, g_cublas, a[0], a[1], a[2], "FCLayer", false, wd); }
+    else if (k == "FCLayerTrain") { need(3); L = new FCLayer(g_cudnn, g_cublas, a[0], a[1], a[2], "FCLayer", true, wd); }
     else if (k == "ResConvLayer") { need(5); int h = a[3], w = a[4]; L = new ResConvLayer(g_cudnn, a[0], a[1], a[2], &h, &w, "ResConvLayer", false); }
     else if (k == "LayerNorm") { need(4); L = new LayerNorm(a[0], a[1], a[2], a[3], "LayerNorm", wd); }
     else if (k == "SpatialAttentionLayer") { need(5); L = new SpatialAttentionLayer(g_cudnn, a[0], a[1], a[2], a[3], a[4], "SpatialAttention", false, wd); }
@@ -120,6 +121,21 @@ void* ref_layer_create(const char* kind, const int* a, int n) {
 }
 const void* ref_layer_forward(void* layer, void* x) {
   return guarded([&]() -> const void* { return static_cast<Layer*>(layer)->Forward(static_cast<__half*>(x)); }, nullptr);
+}
+// FCLayer::Backward (FCLayer.cpp:54-59) on a layer created as "FCLayerTrain" after a Forward (which records the
+// input): returns the input gradient and hands out the layer's weight / bias gradient buffers (device pointers)
+const void* ref_fc_backward(void* layer, void* grad, const void** grad_w, const void** grad_b) {
+  return guarded([&]() -> const void* {
+    FCLayer* L = static_cast<FCLayer*>(layer);
+    const void* gx = L->Backward(static_cast<__half*>(grad));
+    if (grad_w) *grad_w = L->gradWeights_;
+    if (grad_b) *grad_b = L->gradBias_;
+    return gx;
+  }, nullptr);
+}
+// Layer::UpdateParameters (AdamWHalf on weights and bias for FCLayer, FCLayer.cpp:60-70)
+int ref_layer_update(void* layer, float lr) {
+  return guarded([&] { static_cast<Layer*>(layer)->UpdateParameters(lr); return 0; }, -1);
 }
 size_t ref_layer_param_bytes(void* layer) { return static_cast<Layer*>(layer)->GetParameterSize(); }
 int ref_layer_out_count(void* layer) { return static_cast<Layer*>(layer)->outNCHW_; }

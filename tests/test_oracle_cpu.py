@@ -126,6 +126,22 @@ def test_fc_orientation_and_two_roundings():
     assert np.array_equal(got, want)
 
 
+def test_fc_backward_orientation():
+    """FCLayer.cpp:54-59: grad_w = x^T . g in the weights' [in][out] layout, grad_x = g . W^T, grad_b = column sums."""
+    B, I, Oo = 7, 24, 9
+    x = h(RNG.standard_normal((B, I)))
+    g = h(RNG.standard_normal((B, Oo)) * 0.1)
+    W = h(RNG.standard_normal((I, Oo)) * 0.3)
+    gw, gb, gx = O.fc_backward(x, g, W)
+    x64, g64, W64 = x.astype(np.float64), g.astype(np.float64), W.astype(np.float64)
+    assert np.array_equal(gw, (x64.T @ g64).astype(np.float16))
+    assert np.array_equal(gx, (g64 @ W64.T).astype(np.float16))
+    s = np.zeros(Oo, np.float32)
+    for b in range(B):
+        s = s + g[b].astype(np.float32)
+    assert np.array_equal(gb, s.astype(np.float16))
+
+
 def test_layernorm_ref_axis_and_rows():
     N, C, HW = 4, 6, 10
     x = h(RNG.standard_normal((N, C, HW)) * 2 + 0.5)
