@@ -524,33 +524,75 @@ igemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ 
         const int n_tile = tile % p.n_tiles, m_sup = tile / p.n_tiles;
         int seg_n[MS * kMaxSegs], seg_z[MS * kMaxSegs], seg_y[MS * kMaxSegs], seg_x[MS * kMaxSegs];
         const int nseg = MS * p.segs;
-        for (int s = 0; s < nseg; ++s) {
-          const int g = m_sup * nseg + s;  // sub-tile (m_sup*MS + s/segs), run s%segs
-          const int row = g / p.segs_per_row, wseg = g - row * p.segs_per_row;
-          const int n = row / p.DoHo, r2 = row - n * p.DoHo;
-          const int od = r2 / p.Ho, oh = r2 - od * p.Ho;
-          seg_n[s] = n;  // rows past the end give n >= batch: the box is out of range, filled with zeros
-          seg_z[s] = od * p.sd - p.pd;
-          seg_y[s] = oh * p.sh - p.ph;
-          seg_x[s] = wseg * p.tw * p.sw - p.pw;
-        }
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          const int tap = kb / p.cblocks, cb = kb - tap * p.cblocks;
-          const int fd = tap / p.taps_hw, rem = tap - fd * p.taps_hw;
-          const int fr = rem / p.kw, fs = rem - fr * p.kw;
-          if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, s_abort, p.gerr, 101)) { ok = false; break; }
-          if (leader) {
-            mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
-            // the weight block first: every sub-tile's MMAs need it
-            tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
+        {
+          // the first run by division, the following ones by carries (run along W, then output row, depth, image)
+          const int g0 = m_sup * nseg;  // sub-tile (m_sup*MS + s/segs), run s%segs
+          int row = g0 / p.segs_per_row, wseg = g0 - row * p.segs_per_row;
+          int n = row / p.DoHo;
+          const int r2 = row - n * p.DoHo;
+          int od = r2 / p.Ho, oh = r2 - od * p.Ho;
+          const int Do = p.DoHo / p.Ho;
+          for (int s = 0; s < nseg; ++s) {
+            seg_n[s] = n;  // rows past the end give n >= batch: the box is out of range, filled with zeros
+            seg_z[s] = od * p.sd - p.pd;
+            seg_y[s] = oh * p.sh - p.ph;
+            seg_x[s] = wseg * p.tw * p.sw - p.pw;
+            if (++wseg == p.segs_per_row) {
+              wseg = 0;
+              if (++oh == p.Ho) {
+                oh = 0;
+                if (++od == Do) { od = 0; ++n; }
+              }
+            }
           }
-          const uint32_t a_dst = sA + stage * Cfg::kABytes;
-          // one box per run of tw pixels, or per rows_per_box consecutive whole rows of one image plane
-          for (int s = 0; s < nseg; s += p.rows_per_box)
-            if (leader)
-              tma_load_5d(a_dst + s * p.tw * BK * 2, &tmapA, bar_full + 8 * stage, cb * BK, seg_x[s] + fs, seg_y[s] + fr,
-                          seg_z[s] + fd, seg_n[s]);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        // K blocks in the order (tap: depth, row, column of the filter; then channel block), stepped by carries.  The
+        // index arithmetic of this loop, not the loads, bounded short K blocks (a division per index and the
+        // coordinate arrays in local memory cost ~700 clk per block against ~270 clk of MMA issue), so up to four
+        // boxes per block keep their coordinates in registers.
+        const int kh = p.taps_hw / p.kw;
+        const int nbox = nseg / p.rows_per_box;
+        const uint32_t box_bytes = (uint32_t)(p.rows_per_box * p.tw * BK * 2);
+        auto k_loop = [&](auto issue_a) {
+          int cb = 0, fs = 0, fr = 0, fd = 0;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u, s_abort, p.gerr, 101)) { ok = false; break; }
+            if (leader) {
+              mbar_expect_tx(bar_full + 8 * stage, Cfg::kStageBytes);
+              // the weight block first: every sub-tile's MMAs need it
+              tma_load_2d(sB + stage * Cfg::kBBytes, &tmapB, bar_full + 8 * stage, kb * BK, n_tile * NT);
+              // one box per run of tw pixels, or per rows_per_box consecutive whole rows of one image plane
+              issue_a(sA + stage * Cfg::kABytes, bar_full + 8 * stage, cb * BK, fs, fr, fd);
+            }
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            if (++cb == p.cblocks) {
+              cb = 0;
+              if (++fs == p.kw) {
+                fs = 0;
+                if (++fr == kh) { fr = 0; ++fd; }
+              }
+            }
+          }
+        };
+        if (nbox <= 4) {
+          int bx[4], by[4], bz[4], bn[4];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const int s = b < nbox ? b * p.rows_per_box : 0;
+            bx[b] = seg_x[s]; by[b] = seg_y[s]; bz[b] = seg_z[s]; bn[b] = seg_n[s];
+          }
+          k_loop([&](uint32_t a_dst, uint32_t bar, int c0, int fs, int fr, int fd) {
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+              if (b < nbox) tma_load_5d(a_dst + (uint32_t)b * box_bytes, &tmapA, bar, c0, bx[b] + fs, by[b] + fr, bz[b] + fd, bn[b]);
+          });
+        } else {
+          k_loop([&](uint32_t a_dst, uint32_t bar, int c0, int fs, int fr, int fd) {
+            for (int b = 0; b < nbox; ++b) {
+              const int s = b * p.rows_per_box;
+              tma_load_5d(a_dst + (uint32_t)b * box_bytes, &tmapA, bar, c0, seg_x[s] + fs, seg_y[s] + fr, seg_z[s] + fd, seg_n[s]);
+            }
+          });
         }
       }
     }
