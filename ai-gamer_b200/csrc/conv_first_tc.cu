@@ -92,10 +92,21 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
       const bool valid = px < p.total_px;
       int ow = 0, oh = 0, od = 0, n = 0;
       if (valid) {
-        long long t = px;
-        ow = (int)(t % g.Wo); t /= g.Wo;
-        oh = (int)(t % g.Ho); t /= g.Ho;
-        od = (int)(t % g.Do); n = (int)(t / g.Do);
+        if (p.total_px < (1ll << 31)) {  // 32-bit index arithmetic where it suffices
+          const uint32_t t = (uint32_t)px;
+          const uint32_t t1 = t / (uint32_t)g.Wo;
+          ow = (int)(t - t1 * (uint32_t)g.Wo);
+          const uint32_t t2 = t1 / (uint32_t)g.Ho;
+          oh = (int)(t1 - t2 * (uint32_t)g.Ho);
+          const uint32_t t3 = t2 / (uint32_t)g.Do;
+          od = (int)(t2 - t3 * (uint32_t)g.Do);
+          n = (int)t3;
+        } else {
+          long long t = px;
+          ow = (int)(t % g.Wo); t /= g.Wo;
+          oh = (int)(t % g.Ho); t /= g.Ho;
+          od = (int)(t % g.Do); n = (int)(t / g.Do);
+        }
       }
       const int iw0 = ow * g.s - g.pad, ih0 = oh * g.s - g.pad, id0 = od * g.sd - g.pd;
       __align__(16) __half hv[NCH * 8];
