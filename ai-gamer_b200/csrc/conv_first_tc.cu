@@ -25,6 +25,7 @@ struct TcParams {
   const float* scale;
   const float* shift;
   int* gerr;
+  int pair;         // planar fp16 input, k3 s2 p1, even width: the gather loads column pairs (see the producers)
   int s2d, Hb, Wb;  // s2d: store into the 2x2 space-to-depth layout [n][Hb][Wb][4][K] read by a fused down-sampling block
 };
 
@@ -112,6 +113,35 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
       __align__(16) __half hv[NCH * 8];
 #pragma unroll
       for (int i = KTOT; i < NCH * 8; ++i) hv[i] = __ushort_as_half((unsigned short)0);
+      if (!BGRA && KHW == 3 && p.pair) {
+        // k3 s2 p1 over an even width: the taps at columns 2*ow and 2*ow + 1 are one aligned 4-byte load, and the tap
+        // at 2*ow - 1 is the neighbouring output pixel's second half (one lane down), fetched by a shuffle; lane 0
+        // and the first pixel of a row load it themselves.  27 loads in flight per pixel instead of 81: the gather
+        // is bound by the latency of its loads and by the registers that hold them.
+        const __half* src = reinterpret_cast<const __half*>(xin);
+        const size_t plane = (size_t)g.D * g.H * g.W;
+        const bool own_left = lane == 0 || ow == 0;
+#pragma unroll
+        for (int fd = 0; fd < KD; ++fd) {
+          const int id = id0 + fd;
+#pragma unroll
+          for (int fr = 0; fr < 3; ++fr) {
+            const int ih = ih0 + fr;
+            const bool rok = valid && id >= 0 && id < g.D && ih >= 0 && ih < g.H;
+            const size_t off = (((size_t)n * 3) * g.D + id) * g.H * g.W + (size_t)ih * g.W + 2 * ow;
+            const int t0 = (fd * 3 + fr) * 3;
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+              const uint32_t two = rok ? *reinterpret_cast<const uint32_t*>(src + off + c * plane) : 0u;
+              const unsigned short mine = (own_left && rok && ow > 0) ? __half_as_ushort(src[off + c * plane - 1]) : (unsigned short)0;
+              const uint32_t below = __shfl_up_sync(0xffffffffu, two, 1);
+              hv[t0 * 3 + c] = __ushort_as_half(own_left ? mine : (unsigned short)(below >> 16));
+              hv[(t0 + 1) * 3 + c] = __ushort_as_half((unsigned short)(two & 0xFFFFu));
+              hv[(t0 + 2) * 3 + c] = __ushort_as_half((unsigned short)(two >> 16));
+            }
+          }
+        }
+      } else {
 #pragma unroll
       for (int fd = 0; fd < KD; ++fd) {
         const int id = id0 + fd;
@@ -142,6 +172,7 @@ conv_first_tc_kernel(const void* __restrict__ xin, __half* __restrict__ y, const
             }
           }
         }
+      }
       }
       if (!mbar_wait_bounded(bar_aempty + 8 * st, ph ^ 1u, s_abort, p.gerr, 601)) break;
       uint8_t* a = sA + st * kABytes;
@@ -633,6 +664,7 @@ int conv_first_tc_create(aig_ctx* ctx, const ConvFirstGeom& g, const float* scal
   TcParams& p = t->prm;
   p.g = g;
   p.total_px = (long long)g.batch * g.Do * g.Ho * g.Wo;
+  p.pair = g.k == 3 && g.s == 2 && g.pad == 1 && g.W % 2 == 0 && g.Wo == g.W / 2;
   p.tiles = (int)ceil_div_ll(p.total_px, kRows);
   p.NT = ceil_div(g.K, 16) * 16;
   p.scale = scale;

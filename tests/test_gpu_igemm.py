@@ -197,20 +197,20 @@ def test_first_layer_convs(env):
         # the two entry points order the K dimension differently (different kernels): equal up to fp32 summation order
         assert np.abs(got.astype(np.float32) - got2.astype(np.float32)).max() <= 2 * np.abs(want).max() * 2.0 ** -10
         plan.close()
-    # 3-D first layer
-    B, D, H, W, K = 1, 4, 12, 20, 32
-    x = PL.make_clips(1, B, D, H, W)
-    w = PL.he_normal(RNG, (K, 3, 3, 3, 3))
-    b = h(RNG.uniform(-0.2, 0.2, K))
-    want = O.leaky_relu(O.conv3d(x, w, b, 1, 2, 1, 1), 0.01)
-    plan = pk.Conv0Plan(c, B, H, W, K, 3, 2, 1, act=pk.ACT_LEAKY, slope=0.01, in_d=D, kd=3, sd=1, pd=1)
-    plan.set_weights(U.dev(w), U.dev(b))
-    dy = torch.zeros(want.size, dtype=torch.float16, device="cuda")
-    plan.forward_nchw(U.dev(x), dy)
-    c.sync()
-    got = U.nchw(U.host(dy).reshape(B, *want.shape[2:], K))
-    assert U.scaled_err(got, want) < 4e-3
-    plan.close()
+    # 3-D first layer: rows shorter than a warp, rows of exactly one warp, an odd width (no column pairs)
+    for B, D, H, W, K in [(1, 4, 12, 20, 32), (2, 3, 9, 64, 32), (1, 2, 10, 23, 32)]:
+        x = PL.make_clips(1, B, D, H, W)
+        w = PL.he_normal(RNG, (K, 3, 3, 3, 3))
+        b = h(RNG.uniform(-0.2, 0.2, K))
+        want = O.leaky_relu(O.conv3d(x, w, b, 1, 2, 1, 1), 0.01)
+        plan = pk.Conv0Plan(c, B, H, W, K, 3, 2, 1, act=pk.ACT_LEAKY, slope=0.01, in_d=D, kd=3, sd=1, pd=1)
+        plan.set_weights(U.dev(w), U.dev(b))
+        dy = torch.zeros(want.size, dtype=torch.float16, device="cuda")
+        plan.forward_nchw(U.dev(x), dy)
+        c.sync()
+        got = U.nchw(U.host(dy).reshape(B, *want.shape[2:], K))
+        assert U.scaled_err(got, want) < 4e-3, (B, D, H, W)
+        plan.close()
 
 
 def _s2d_host(x_nhwc):
