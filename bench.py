@@ -625,11 +625,11 @@ def reference_call_pattern(env):
                     "46 library launches per step, planar fp16 input already on the device, no head", "layers": layers}
 
 
-def fc_training_round(env):
-    """One Forward / Backward / UpdateParameters round of FCLayer in training mode (FCLayer.cpp:48-70) on the
+def fc_training_step(env):
+    """One Forward / Backward / UpdateParameters step of FCLayer in training mode (FCLayer.cpp:48-70) on the
     reference's own CPU-runnable shape, 64 x 1024 -> 1024: this library's class (`aig_layer_*` hooks, kind
     "FCLayerTrain": tcgen05 GEMMs for the three products, AdamW on fp16 parameters) and, where it was built, the
-    reference's class on cuBLAS beside it.  The 2 MB of weights live in L2 in both; the round is launch-bound."""
+    reference's class on cuBLAS beside it.  The 2 MB of weights live in L2 in both; the step is launch-bound."""
     import ctypes
 
     torch, lib, ctx = env.torch, env.pkg.lib(), env.ctx
@@ -652,7 +652,7 @@ def fc_training_round(env):
     res = env.timer.regions(ours, steps, 10)
     lib.aig_layer_destroy(layer)
     flop = 3 * 2.0 * B * I * N
-    block = {"shape": "batch %d, %d -> %d" % (B, I, N), "value": 1.0 / (res["ms_per_step"] * 1e-3), "unit": "rounds/s", "us_per_round": res["ms_per_step"] * 1e3,
+    block = {"shape": "batch %d, %d -> %d" % (B, I, N), "value": 1.0 / (res["ms_per_step"] * 1e-3), "unit": "steps/s", "us_per_step": res["ms_per_step"] * 1e3,
              "repeats": res["repeats"], "steps": steps, "tflops": flop / (res["ms_per_step"] * 1e-3) / 1e12}
     path = os.path.join(ROOT, "oracle", "_ref", "libaig_reflayers.so")
     if not os.path.exists(path):
@@ -691,7 +691,7 @@ def fc_training_round(env):
         times.append(e0.elapsed_time(e1) / steps)
     ref.ref_layer_destroy(rl)
     ms = float(np.median(times))
-    block["reference_class"] = {"value": 1.0 / (ms * 1e-3), "unit": "rounds/s", "us_per_round": ms * 1e3,
+    block["reference_class"] = {"value": 1.0 / (ms * 1e-3), "unit": "steps/s", "us_per_step": ms * 1e3,
                                 "what": "the reference's FCLayer (cublasGemmEx x3, cudnnAddTensor, BiasGradient, AdamWHalf x2) on the legacy default stream"}
     return block
 
@@ -772,7 +772,7 @@ def main():
         line["workloads"] = extra
         if env.world == 1 and wl == "cnn2d" and args.legs == "all":
             line["reference_call_pattern"] = reference_call_pattern(env)
-            line["fc_training_round"] = fc_training_round(env)
+            line["fc_training_step"] = fc_training_step(env)
         if not args.no_cpu_baseline and env.world == 1:
             line["cpu_baseline"] = cpu_baseline_block(wl, 5 if wl == "cnn2d" else 3)
             for w in extra:

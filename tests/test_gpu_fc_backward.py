@@ -102,9 +102,9 @@ def _ref_lib():
 @gpu
 @pytest.mark.parametrize("B,I,N", [(64, 1024, 1024), (32, 256, 16), (256, 256, 512)])
 def test_fc_training_steps_against_the_reference_class(env, B, I, N):
-    """Three Forward / Backward / UpdateParameters rounds of FCLayer in training mode, the reference's class (cuBLAS +
+    """Three Forward / Backward / UpdateParameters steps of FCLayer in training mode, the reference's class (cuBLAS +
     AdamWHalf) and this library's class side by side from the same payload, inputs and incoming gradients: the input
-    gradient, the weight gradient and the updated weights of every round.  The bias is left out of
+    gradient, the weight gradient and the updated weights of every step.  The bias is left out of
     the comparison: the reference's BiasGradient adds a cross-channel reduction to the per-channel sums
     (CudaStuff.cu:385-389), which this library does not reproduce."""
     U = env
@@ -166,9 +166,9 @@ def test_fc_training_steps_against_the_reference_class(env, B, I, N):
             assert lib.aig_layer_update(ol, lr) == 0
             c.sync()
             # both accumulate in fp32 (CUDA_R_32F compute, FCLayer.cpp:55,57), in different orders
-            # (after the first round the two classes hold weights that may differ in a few last bits)
-            _check(got_gx, ref_gx, "grad_x vs the reference, round %d" % step, frac_exact=0.999 if step == 0 else 0.99, ulps=1)
-            _check(got_gw, ref_gw, "grad_w vs the reference, round %d" % step, frac_exact=0.999, ulps=1)
+            # (after the first step the two classes hold weights that may differ in a few last bits)
+            _check(got_gx, ref_gx, "grad_x vs the reference, step %d" % step, frac_exact=0.999 if step == 0 else 0.99, ulps=1)
+            _check(got_gw, ref_gw, "grad_w vs the reference, step %d" % step, frac_exact=0.999, ulps=1)
             want_w, _, want_x = O.fc_backward(x, g, w_now)
             _check(ref_gx, want_x, "the reference's grad_x vs the oracle")
             _check(ref_gw, want_w, "the reference's grad_w vs the oracle")
@@ -178,13 +178,13 @@ def test_fc_training_steps_against_the_reference_class(env, B, I, N):
             rw = np.frombuffer(open(rp, "rb").read(), f16)[: I * N].reshape(I, N)
             ow = np.frombuffer(open(op, "rb").read(), f16)[: I * N].reshape(I, N)
             same = float((rw == ow).mean())
-            assert same >= 0.999, "weights after round %d: only %.5f identical" % (step, same)
+            assert same >= 0.999, "weights after step %d: only %.5f identical" % (step, same)
             # the few that differ: by one fp16 ulp at the weight's magnitude, or at the step's (lr) for a weight that
             # the update carried to near zero, where an ulp is far below the moments' own rounding
             scale = np.maximum(np.abs(rw.astype(np.float64)), lr)
             ulp = 2.0 ** (np.floor(np.log2(scale)) - 10)
             far = np.abs(rw.astype(np.float64) - ow.astype(np.float64)) > ulp * 1.0001
-            assert not far.any(), "round %d: %d weights beyond one ulp" % (step, far.sum())
+            assert not far.any(), "step %d: %d weights beyond one ulp" % (step, far.sum())
             assert not np.array_equal(ow, w_now), "the update changed nothing"
             w_now = ow.copy()
         plan.close()
